@@ -1,0 +1,190 @@
+/* pet_b200.h -- C ABI of the B200-native PET energy/forces/virial evaluator.
+ *
+ * A drop-in for the evaluation path behind the reference's pet::Calculator
+ * (include/pet/calculator.hpp:174-319 in peterspackman/pet-kokkos).  The
+ * reference has no C ABI of its own: its callers bind the C++ class directly
+ * (python/core.cpp:366-390 via nanobind, lammps/ML-PET/pair_pet.cpp:140-167,
+ * apps/pet_eval.cpp:561-584).  Every entry point below names the C++ member it
+ * replaces; include/pet/calculator.hpp in this repository is a header-only C++
+ * facade with the reference's class and struct names over these calls.
+ *
+ * Conventions (the reference's, calculator.hpp:4-7,120-126): Angstrom, eV,
+ * eV/A; forces[Ntot*3] row-major, F = -dE/dx; virial[B*6] is the symmetric
+ * W = V*stress in Voigt order xx yy zz xy xz yz; cell is 9 doubles, lattice
+ * vectors as rows.  All pointers in these structs are HOST pointers unless a
+ * field says "device".  Every function returns 0 on success, a PET_ERR_* code
+ * otherwise; pet_last_error() returns the message.  One calculator owns one
+ * CUDA device, one stream and its scratch pool; it is not re-entrant
+ * (the reference's is not either: calculator.hpp:9-11, gemm.hpp:88-94).
+ * There is no CPU fallback: creation fails if no CUDA device is present.
+ */
+#ifndef PET_B200_H
+#define PET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct pet_calc pet_calc;
+
+enum {
+  PET_OK = 0,
+  PET_ERR_RUNTIME = 1,       /* std::runtime_error in the reference  */
+  PET_ERR_INVALID = 2,       /* std::invalid_argument                */
+  PET_ERR_LOGIC = 3,         /* std::logic_error                     */
+  PET_ERR_ALLOC = 4,         /* std::bad_alloc / out of device memory */
+  PET_ERR_CUDA = 5           /* a CUDA runtime call failed           */
+};
+
+/* GemmMode / AttentionMode of the reference (include/pet/gemm.hpp:65). */
+enum { PET_GEMM_NATIVE = 0, PET_GEMM_TF32 = 1, PET_GEMM_BF16 = 2, PET_GEMM_TF32X3 = 3 };
+
+/* pet::Options (calculator.hpp:32-117), the subset this path uses. A negative
+ * value means "unset": environment (PET_GEMM, PET_GRAPHS, PET_DEVICE_SEARCH)
+ * then the default. */
+typedef struct pet_options {
+  int device;               /* CUDA device ordinal; -1: the current device          */
+  int gemm_mode;            /* PET_GEMM_*; -1 unset (default native fp32)             */
+  int graphs;               /* replay repeated evaluations as a CUDA graph; -1 unset  */
+  int md_fixed_shapes;      /* Options::md_fixed_shapes; -1 unset                     */
+  size_t memory_budget_bytes; /* 0: ask the device                                     */
+  int max_batch_atoms;      /* 0: none                                                */
+  int reserved[8];
+} pet_options;
+
+/* pet::System (include/pet/neighbors.hpp:15-25). */
+typedef struct pet_system {
+  int n_atoms;
+  const int* atomic_numbers;   /* [n_atoms]     */
+  const double* positions;     /* [n_atoms * 3] */
+  double cell[9];
+  int pbc[3];
+  int charge, spin_multiplicity;
+} pet_system;
+
+/* pet::Results (calculator.hpp:120-142). Caller-allocated; a null pointer skips
+ * that output. edge_gradient is filled by pet_compute_edges/pet_compute_step
+ * when asked for. */
+typedef struct pet_results {
+  double* energy;           /* [B]        */
+  double* per_atom_energy;  /* [Ntot]     */
+  double* forces;           /* [Ntot * 3] */
+  double* virial;           /* [B * 6]    */
+  int* struct_id;           /* [Ntot]     */
+  double* edge_gradient;    /* [n_pairs * 3] */
+} pet_results;
+
+/* pet::EdgeListView (include/pet/device_geometry.hpp:93-110): an MD engine's own
+ * neighbour list. n_local < 0: every atom is owned. */
+typedef struct pet_edge_list {
+  int n_atoms, n_local;
+  const double* positions;      /* [n_atoms * 3]              */
+  const int* atomic_numbers;    /* [n_atoms]                  */
+  const int* offsets;           /* [n_atoms + 1]              */
+  const int* neighbors;         /* [offsets[n_atoms]]         */
+  const int* shifts;            /* [offsets[n_atoms] * 3], optional */
+  const double* cell;           /* [9], with shifts           */
+  int half;
+} pet_edge_list;
+
+/* Calculator::DeviceArrays / Totals (calculator.hpp:248-259): DEVICE pointers,
+ * [n,3] row-major doubles; forces, per_atom_energy and per_atom_virial are
+ * added into. */
+typedef struct pet_device_arrays {
+  const double* positions;
+  double* forces;
+  double* per_atom_energy;
+  double* per_atom_virial;
+  double virial_scale;
+} pet_device_arrays;
+typedef struct pet_totals {
+  double energy;
+  double virial[6];
+} pet_totals;
+
+/* The raw neighbour list of a batch as the device search lists it
+ * (pet::RawEdges, include/pet/device_cell_list.hpp:52-59). Caller-allocated with
+ * capacity `capacity` edges; n_edges receives the count (the call fails with
+ * PET_ERR_INVALID and sets n_edges if capacity is too small). */
+typedef struct pet_raw_edges {
+  int capacity, n_edges;
+  int* i;          /* [E] centre, global atom index    */
+  int* j;          /* [E] neighbour, global atom index */
+  int* shift;      /* [E * 3]                          */
+  double* vec;     /* [E * 3] r_j + shift.cell - r_i   */
+  double* dist;    /* [E]                              */
+  int* reverse;    /* [E] the (j, i, -shift) edge or -1 (optional) */
+  float* cutoff;   /* [E] smooth cutoff factor (optional)           */
+} pet_raw_edges;
+
+/* Calculator::Calculator(model_json, model_weights, opts) (calculator.hpp:179). */
+int pet_calc_create(const char* model_json, const char* model_weights, const pet_options* opts, pet_calc** out);
+/* Calculator::~Calculator. */
+void pet_calc_destroy(pet_calc* c);
+/* The message of the last failed call on `c` (or of a failed create when c is null). */
+const char* pet_last_error(const pet_calc* c);
+
+/* Calculator::compute(const System&, bool) and compute(const std::vector<System>&, bool)
+ * (calculator.hpp:187,192; the batched form is what python/core.cpp:376 exposes as compute_batch). */
+int pet_compute(pet_calc* c, const pet_system* systems, int n_systems, int compute_forces, pet_results* out);
+
+/* Calculator::stage (calculator.hpp:214) and compute_device (:219): structures
+ * staged once in device memory, evaluated there; results stay on the device
+ * until pet_fetch_results. */
+int pet_stage(pet_calc* c, const pet_system* systems, int n_systems);
+int pet_compute_staged(pet_calc* c, int compute_forces);
+int pet_fetch_results(pet_calc* c, pet_results* out);
+/* Moves the staged positions (and cells when non-null) on the device from host arrays. */
+int pet_update_staged(pet_calc* c, const double* positions, const double* cells);
+
+/* Calculator::compute_edges (calculator.hpp:227). */
+int pet_compute_edges(pet_calc* c, const pet_edge_list* list, int compute_forces, int edge_gradients, pet_results* out);
+/* Calculator::set_neighbors(const EdgeListView&) (calculator.hpp:235). */
+int pet_set_neighbors(pet_calc* c, const pet_edge_list* list);
+/* Calculator::compute_step(positions, cell, forces, edge_gradients) (calculator.hpp:238). */
+int pet_compute_step(pet_calc* c, const double* positions, const double* cell, int compute_forces,
+                     int edge_gradients, pet_results* out);
+/* Calculator::compute_step(const DeviceArrays&, cell) (calculator.hpp:259). */
+int pet_compute_step_device(pet_calc* c, const pet_device_arrays* arrays, const double* cell, pet_totals* totals);
+
+/* The device neighbour search alone: build_nef_device's raw list
+ * (src/device_geometry.cpp:356-366, src/device_cell_list.cpp:108-292). */
+int pet_neighbor_list(pet_calc* c, const pet_system* systems, int n_systems, pet_raw_edges* out);
+
+/* Calculator::cutoff, ghost_cutoff, exchange_ghost_cutoff, energy_scale (calculator.hpp:272-288). */
+double pet_cutoff(const pet_calc* c);
+double pet_ghost_cutoff(const pet_calc* c);
+double pet_exchange_ghost_cutoff(const pet_calc* c);
+double pet_energy_scale(const pet_calc* c);
+/* Calculator::supports (calculator.hpp:284). */
+int pet_supports(const pet_calc* c, int atomic_number);
+/* Calculator::workspace_bytes (calculator.hpp:303). */
+size_t pet_workspace_bytes(const pet_calc* c);
+
+/* Shapes of the latest evaluation: atoms, kept edges, max neighbours
+ * (Calculator::memory_plan, calculator.hpp:307). */
+int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neighbors);
+
+/* Kernels launched by this library on this calculator since creation, and the
+ * device time in milliseconds of the latest evaluation (CUDA events on the
+ * calculator's stream). */
+long long pet_kernel_launches(const pet_calc* c);
+double pet_last_device_ms(const pet_calc* c);
+
+/* Copies a named intermediate of the latest evaluation to the host as float32
+ * (testing aid; names follow the reference's workspace keys). Returns the
+ * element count through n; fails if the name is unknown or capacity is short. */
+int pet_debug_fetch(pet_calc* c, const char* name, float* out, size_t capacity, size_t* n);
+
+/* One weight GEMM, C[m,n] = A[m,k] . W^T (W is [n,k]) or A . W (W is [k,n]) in the
+ * given PET_GEMM_* mode, on host arrays (weight_gemm, src/ops.cpp:18-24; pins
+ * tests/test_gemm_modes.cpp:63-103). */
+int pet_gemm_host(pet_calc* c, int mode, int w_transposed, int m, int n, int k, const float* A, const float* W, float* C);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PET_B200_H */

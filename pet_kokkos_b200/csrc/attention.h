@@ -1,0 +1,25 @@
+// Per-atom multi-head attention over neighbour tokens: see attention.cu.
+#pragma once
+
+#include "common.h"
+
+namespace petb {
+
+struct AttnArgs {
+  int N = 0, H = 0, hd = 0, S = 0;  // atoms, heads, head_dim, most tokens of any atom (max neighbours + 1)
+  float sc = 1.f;                   // 1 / (sqrt(head_dim) * temperature)
+  const int* off = nullptr;         // [N+1] each atom's range of edge rows
+  const float* cut = nullptr;       // [E] cutoff factor of each edge token
+  const float* qkv = nullptr;       // [T,3D] columns Q | K | V
+  float* merged = nullptr;          // [T,D] attention output before the output projection
+  float* ml = nullptr;              // [T,H,2] each query's running max and 1/sum (null: not saved)
+  // backward
+  const float* dmerged = nullptr;   // [T,D]
+  float* qkv_adj = nullptr;         // [T,3D]
+  float* cfh = nullptr;             // [T,H] each key's score adjoint summed over its queries
+};
+
+void attention_forward(Stream& st, const AttnArgs& a);
+void attention_backward(Stream& st, const AttnArgs& a);
+
+}  // namespace petb

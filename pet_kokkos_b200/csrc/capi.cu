@@ -1,0 +1,150 @@
+// extern "C" entry points: include/pet_b200.h. Exceptions become status codes.
+#include <new>
+#include <string>
+
+#include "engine.h"
+
+using petb::Engine;
+
+struct pet_calc {
+  Engine* e = nullptr;
+  std::string error;
+};
+
+namespace {
+
+thread_local std::string g_create_error;
+
+template <class F>
+int guarded(pet_calc* c, F&& f) {
+  try {
+    if (!c || !c->e) throw petb::Error(PET_ERR_INVALID, "pet: null calculator");
+    f(*c->e);
+    return PET_OK;
+  } catch (const petb::Error& err) {
+    if (c) c->error = err.what();
+    return err.code;
+  } catch (const std::bad_alloc&) {
+    if (c) c->error = "out of host memory";
+    return PET_ERR_ALLOC;
+  } catch (const std::exception& err) {
+    if (c) c->error = err.what();
+    return PET_ERR_RUNTIME;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int pet_calc_create(const char* model_json, const char* model_weights, const pet_options* opts, pet_calc** out) {
+  if (!out) return PET_ERR_INVALID;
+  *out = nullptr;
+  try {
+    if (!model_json || !model_weights) throw petb::Error(PET_ERR_INVALID, "pet: model paths are required");
+    pet_calc* c = new pet_calc;
+    try {
+      c->e = new Engine(model_json, model_weights, opts);
+    } catch (...) {
+      delete c;
+      throw;
+    }
+    *out = c;
+    return PET_OK;
+  } catch (const petb::Error& err) {
+    g_create_error = err.what();
+    return err.code;
+  } catch (const std::bad_alloc&) {
+    g_create_error = "out of host memory";
+    return PET_ERR_ALLOC;
+  } catch (const std::exception& err) {
+    g_create_error = err.what();
+    return PET_ERR_RUNTIME;
+  }
+}
+
+void pet_calc_destroy(pet_calc* c) {
+  if (!c) return;
+  delete c->e;
+  delete c;
+}
+
+const char* pet_last_error(const pet_calc* c) { return c ? c->error.c_str() : g_create_error.c_str(); }
+
+int pet_compute(pet_calc* c, const pet_system* systems, int n, int forces, pet_results* out) {
+  return guarded(c, [&](Engine& e) { e.compute(systems, n, forces != 0, out); });
+}
+int pet_stage(pet_calc* c, const pet_system* systems, int n) {
+  return guarded(c, [&](Engine& e) { e.stage(systems, n); });
+}
+int pet_compute_staged(pet_calc* c, int forces) {
+  return guarded(c, [&](Engine& e) { e.compute_staged(forces != 0); });
+}
+int pet_fetch_results(pet_calc* c, pet_results* out) {
+  return guarded(c, [&](Engine& e) { e.fetch(out); });
+}
+int pet_update_staged(pet_calc* c, const double* positions, const double* cells) {
+  return guarded(c, [&](Engine& e) { e.update_staged(positions, cells); });
+}
+int pet_compute_edges(pet_calc* c, const pet_edge_list* list, int forces, int edge_gradients, pet_results* out) {
+  return guarded(c, [&](Engine& e) {
+    e.set_neighbors(list);
+    e.compute_step(list->positions, list->cell, forces != 0, edge_gradients != 0, out);
+  });
+}
+int pet_set_neighbors(pet_calc* c, const pet_edge_list* list) {
+  return guarded(c, [&](Engine& e) { e.set_neighbors(list); });
+}
+int pet_compute_step(pet_calc* c, const double* positions, const double* cell, int forces, int edge_gradients,
+                     pet_results* out) {
+  return guarded(c, [&](Engine& e) { e.compute_step(positions, cell, forces != 0, edge_gradients != 0, out); });
+}
+int pet_compute_step_device(pet_calc* c, const pet_device_arrays* arrays, const double* cell, pet_totals* totals) {
+  return guarded(c, [&](Engine& e) { e.compute_step_device(arrays, cell, totals); });
+}
+int pet_neighbor_list(pet_calc* c, const pet_system* systems, int n, pet_raw_edges* out) {
+  return guarded(c, [&](Engine& e) { e.neighbor_list(systems, n, out); });
+}
+
+double pet_cutoff(const pet_calc* c) { return c && c->e ? c->e->ckpt.hypers.cutoff : 0.0; }
+double pet_ghost_cutoff(const pet_calc* c) {
+  // One cutoff per message-passing layer (Calculator::ghost_cutoff, src/calculator.cpp:890-894).
+  return c && c->e ? c->e->ckpt.hypers.num_gnn_layers * c->e->ckpt.hypers.cutoff : 0.0;
+}
+double pet_exchange_ghost_cutoff(const pet_calc* c) { return pet_cutoff(c); }
+double pet_energy_scale(const pet_calc* c) { return c && c->e ? c->e->ckpt.energy_scale : 0.0; }
+int pet_supports(const pet_calc* c, int Z) {
+  if (!c || !c->e) return 0;
+  const auto& m = c->e->ckpt.species_to_index;
+  return Z >= 0 && Z < (int) m.size() && m[Z] >= 0;
+}
+size_t pet_workspace_bytes(const pet_calc* c) {
+  if (!c || !c->e) return 0;
+  const Engine& e = *c->e;
+  return e.geom_arena.capacity() + e.nbr_arena.capacity() + e.save_arena.capacity() + e.tmp_arena.capacity() +
+         e.session_arena.capacity();
+}
+int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neighbors) {
+  if (!c || !c->e) return PET_ERR_INVALID;
+  if (n_atoms) *n_atoms = c->e->last_pk.n_atoms;
+  if (n_edges) *n_edges = c->e->last_pk.E;
+  if (max_neighbors) *max_neighbors = c->e->last_pk.M;
+  return PET_OK;
+}
+long long pet_kernel_launches(const pet_calc* c) { return c && c->e ? c->e->st.launches : 0; }
+double pet_last_device_ms(const pet_calc* c) { return c && c->e ? c->e->last_ms : 0.0; }
+
+int pet_debug_fetch(pet_calc* c, const char* name, float* out, size_t capacity, size_t* n) {
+  return guarded(c, [&](Engine& e) {
+    if (!e.want_taps) {
+      e.want_taps = true;
+      throw petb::Error(PET_ERR_LOGIC, "pet: intermediates are recorded from the next evaluation on");
+    }
+    e.debug_fetch(name, out, capacity, n);
+  });
+}
+int pet_gemm_host(pet_calc* c, int mode, int w_transposed, int m, int n, int k, const float* A, const float* W, float* C) {
+  return guarded(c, [&](Engine& e) { e.gemm_host(mode, w_transposed != 0, m, n, k, A, W, C); });
+}
+
+}  // extern "C"

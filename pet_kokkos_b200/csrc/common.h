@@ -1,0 +1,145 @@
+// Shared plumbing of the evaluator: error type, device scratch pool, launch accounting.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace petb {
+
+// An error that crosses the C ABI as a status code plus a message.
+struct Error : std::runtime_error {
+  int code;
+  Error(int c, const std::string& m) : std::runtime_error(m), code(c) {}
+};
+
+#define PETB_CUDA(expr)                                                                         \
+  do {                                                                                          \
+    cudaError_t err__ = (expr);                                                                 \
+    if (err__ != cudaSuccess)                                                                   \
+      throw ::petb::Error(err__ == cudaErrorMemoryAllocation ? 4 : 5,                           \
+                          std::string(#expr) + ": " + cudaGetErrorString(err__));               \
+  } while (0)
+
+inline int cdiv(long long a, long long b) { return int((a + b - 1) / b); }
+
+// Device scratch for one evaluation: a bump allocator over a few large blocks.
+// The first evaluations grow it (cudaMalloc); later ones of the same shapes
+// allocate nothing, so the pointers repeat and a captured graph stays valid.
+// reset() rewinds; when more than one block was needed the blocks are merged
+// into one of the total size at the next reset, so the layout becomes stable.
+// The reference's counterpart is the Workspace pool (include/pet/kokkos.hpp:84-198).
+class Arena {
+ public:
+  explicit Arena(size_t first_block = size_t(64) << 20) : next_block_(first_block) {}
+  ~Arena() { release(); }
+  Arena(const Arena&) = delete;
+  Arena& operator=(const Arena&) = delete;
+
+  void* alloc_bytes(size_t bytes) {
+    bytes = (bytes + 255) & ~size_t(255);
+    if (bytes == 0) bytes = 256;
+    while (cur_ < blocks_.size()) {
+      Block& b = blocks_[cur_];
+      if (b.used + bytes <= b.size) {
+        void* p = b.ptr + b.used;
+        b.used += bytes;
+        used_total_ += bytes;
+        return p;
+      }
+      ++cur_;
+    }
+    size_t size = next_block_;
+    while (size < bytes) size *= 2;
+    Block b;
+    PETB_CUDA(cudaMalloc(&b.ptr, size));
+    b.size = size;
+    b.used = bytes;
+    blocks_.push_back(b);
+    cur_ = blocks_.size() - 1;
+    used_total_ += bytes;
+    ++generation_;
+    return b.ptr;
+  }
+  template <class T>
+  T* alloc(size_t n) { return static_cast<T*>(alloc_bytes(n * sizeof(T))); }
+
+  // Rewind; merges several blocks into one so the next pass of the same shapes
+  // gets one stable layout. Must not be called while kernels still read the pool.
+  void reset() {
+    if (blocks_.size() > 1) {
+      size_t total = 0;
+      for (auto& b : blocks_) total += b.size;
+      PETB_CUDA(cudaDeviceSynchronize());
+      for (auto& b : blocks_) cudaFree(b.ptr);
+      blocks_.clear();
+      Block b;
+      PETB_CUDA(cudaMalloc(&b.ptr, total));
+      b.size = total;
+      blocks_.push_back(b);
+      ++generation_;
+    }
+    for (auto& b : blocks_) b.used = 0;
+    cur_ = 0;
+    used_total_ = 0;
+  }
+  // A stack discipline for temporaries: everything allocated after mark() is handed
+  // back by rewind(). Kernels run in stream order, so a later pass may reuse it.
+  struct Mark {
+    size_t cur, used, total;
+  };
+  Mark mark() const { return {cur_, cur_ < blocks_.size() ? blocks_[cur_].used : 0, used_total_}; }
+  void rewind(const Mark& m) {
+    for (size_t b = m.cur + 1; b < blocks_.size(); ++b) blocks_[b].used = 0;
+    if (m.cur < blocks_.size()) blocks_[m.cur].used = m.used;
+    cur_ = m.cur;
+    used_total_ = m.total;
+  }
+  void release() {
+    for (auto& b : blocks_) cudaFree(b.ptr);
+    blocks_.clear();
+    cur_ = 0;
+    used_total_ = 0;
+    ++generation_;
+  }
+  size_t capacity() const {
+    size_t t = 0;
+    for (auto& b : blocks_) t += b.size;
+    return t;
+  }
+  size_t used() const { return used_total_; }
+  // Changes whenever device memory was (re)allocated: part of a graph's key.
+  uint64_t generation() const { return generation_; }
+
+ private:
+  struct Block {
+    char* ptr = nullptr;
+    size_t size = 0, used = 0;
+  };
+  std::vector<Block> blocks_;
+  size_t cur_ = 0, next_block_, used_total_ = 0;
+  uint64_t generation_ = 0;
+};
+
+// The stream every kernel of a calculator runs on, with a count of launches.
+struct Stream {
+  cudaStream_t s = nullptr;
+  long long launches = 0;
+};
+
+#define PETB_LAUNCH_CHECK(st)                                     \
+  do {                                                            \
+    ++(st).launches;                                              \
+    cudaError_t err__ = cudaGetLastError();                       \
+    if (err__ != cudaSuccess)                                     \
+      throw ::petb::Error(5, std::string("kernel launch failed at ") + __FILE__ + ":" + \
+                                 std::to_string(__LINE__) + ": " + cudaGetErrorString(err__)); \
+  } while (0)
+
+}  // namespace petb

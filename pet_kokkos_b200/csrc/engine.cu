@@ -1,0 +1,532 @@
+// The calculator behind the C ABI: see engine.h.
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+#include "gemm.h"
+
+namespace petb {
+
+namespace {
+
+int env_int(const char* name, int dflt) {
+  const char* e = std::getenv(name);
+  return e && *e ? std::atoi(e) : dflt;
+}
+
+int env_gemm_mode() {
+  const char* e = std::getenv("PET_GEMM");
+  if (!e) return GEMM_NATIVE;
+  const std::string v(e);
+  if (v == "tf32") return GEMM_TF32;
+  if (v == "bf16") return GEMM_BF16;
+  if (v == "3xtf32" || v == "tf32x3") return GEMM_TF32X3;
+  return GEMM_NATIVE;
+}
+
+// eg(e) = scale * g(packed row of raw edge e), 0 for a dropped edge (the reference's raw_edge_grad).
+__global__ void k_raw_edge_grad(double* __restrict__ eg, const double* __restrict__ grad, const int* __restrict__ packed_of_raw,
+                                int R, double scale) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= R) return;
+  const int p = packed_of_raw[e];
+  for (int c = 0; c < 3; ++c) eg[3 * size_t(e) + c] = p >= 0 ? scale * grad[3 * size_t(p) + c] : 0.0;
+}
+
+// An edge with no partner gives its target's share of the force itself (orphan_forces, src/forces.cpp:400-410).
+__global__ void k_orphan_forces(double* __restrict__ forces, const double* __restrict__ eg, const int* __restrict__ ooff,
+                                const int* __restrict__ oedge, int N) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= N) return;
+  for (int k = ooff[a]; k < ooff[a + 1]; ++k)
+    for (int c = 0; c < 3; ++c) forces[3 * size_t(a) + c] -= eg[3 * size_t(oedge[k]) + c];
+}
+
+__global__ void k_add_arrays(double* __restrict__ f, const double* __restrict__ forces, double* __restrict__ e,
+                             const double* __restrict__ per_atom, int N) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  if (f)
+    for (int c = 0; c < 3; ++c) f[3 * size_t(i) + c] += forces[3 * size_t(i) + c];
+  if (e) e[i] += per_atom[i];
+}
+
+// Each directed edge's sym(v (x) g), half to each end, gathered per atom (md_atom_virial, src/calculator.cpp:846-868).
+__global__ void k_atom_virial(double* __restrict__ w, const double* __restrict__ eg, const double* __restrict__ vec,
+                              const int* __restrict__ roff, const int* __restrict__ rrev, const int* __restrict__ ooff,
+                              const int* __restrict__ oedge, int N, double scale) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  double s[6] = {0, 0, 0, 0, 0, 0};
+  auto add = [&](int e) {
+    const double* v = vec + 3 * size_t(e);
+    const double* g = eg + 3 * size_t(e);
+    s[0] += v[0] * g[0], s[1] += v[1] * g[1], s[2] += v[2] * g[2];
+    s[3] += 0.5 * (v[0] * g[1] + v[1] * g[0]);
+    s[4] += 0.5 * (v[0] * g[2] + v[2] * g[0]);
+    s[5] += 0.5 * (v[1] * g[2] + v[2] * g[1]);
+  };
+  for (int e = roff[i]; e < roff[i + 1]; ++e) {
+    add(e);
+    if (rrev[e] >= 0) add(rrev[e]);
+  }
+  if (ooff)
+    for (int k = ooff[i]; k < ooff[i + 1]; ++k) add(oedge[k]);
+  for (int k = 0; k < 6; ++k) w[6 * size_t(i) + k] += scale * s[k];
+}
+
+}  // namespace
+
+Engine::Engine(const std::string& json, const std::string& weights, const pet_options* opts)
+    : ckpt(json, weights), geom_arena(size_t(1) << 20), nbr_arena(size_t(16) << 20), save_arena(size_t(64) << 20),
+      tmp_arena(size_t(64) << 20), session_arena(size_t(4) << 20) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+    throw Error(5, "no CUDA device: this evaluator has no CPU path");
+  device = opts && opts->device >= 0 ? opts->device : -1;
+  if (device >= 0) PETB_CUDA(cudaSetDevice(device));
+  else PETB_CUDA(cudaGetDevice(&device));
+  gemm_mode = opts && opts->gemm_mode >= 0 ? opts->gemm_mode : env_gemm_mode();
+  graphs = (opts && opts->graphs >= 0 ? opts->graphs : env_int("PET_GRAPHS", 1)) != 0;
+  PETB_CUDA(cudaStreamCreateWithFlags(&st.s, cudaStreamNonBlocking));
+  PETB_CUDA(cudaEventCreate(&ev0));
+  PETB_CUDA(cudaEventCreate(&ev1));
+  PETB_CUDA(cudaMallocHost(&pinned, 64 * sizeof(int)));
+  model.reset(new Model(ckpt));
+}
+
+Engine::~Engine() {
+  cudaSetDevice(device);
+  cudaDeviceSynchronize();
+  model.reset();
+  if (pinned) cudaFreeHost(pinned);
+  if (host_stage) cudaFreeHost(host_stage);
+  if (ev0) cudaEventDestroy(ev0);
+  if (ev1) cudaEventDestroy(ev1);
+  if (st.s) cudaStreamDestroy(st.s);
+}
+
+void* Engine::staging(size_t bytes) {
+  if (bytes > host_stage_bytes) {
+    if (host_stage) cudaFreeHost(host_stage);
+    host_stage = nullptr;
+    size_t cap = host_stage_bytes ? host_stage_bytes : size_t(1) << 20;
+    while (cap < bytes) cap *= 2;
+    PETB_CUDA(cudaMallocHost(&host_stage, cap));
+    host_stage_bytes = cap;
+  }
+  return host_stage;
+}
+
+int Engine::species_index(int Z) const {
+  const int s = (Z >= 0 && Z < (int) ckpt.species_to_index.size()) ? ckpt.species_to_index[Z] : -1;
+  if (s < 0) throw Error(1, "pet: unsupported atomic number " + std::to_string(Z));
+  return s;
+}
+
+// ---- staging (stage_systems, src/device_geometry.cpp:368-401) -------------------
+
+void Engine::stage(const pet_system* systems, int B) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (B < 0 || (B > 0 && !systems)) throw Error(2, "pet: no systems given");
+  long long Nll = 0;
+  for (int b = 0; b < B; ++b) {
+    if (systems[b].n_atoms < 0) throw Error(2, "pet: negative atom count");
+    Nll += systems[b].n_atoms;
+  }
+  if (Nll >= (1LL << 24)) throw Error(1, "pet: too many atoms for the edge key");
+  const int N = int(Nll);
+  // One host block, one copy: doubles first, then ints.
+  const size_t nd = size_t(N) * 3 + size_t(B) * 18, ni = size_t(N) * 2 + size_t(B) * 9 + 2;
+  char* hb = static_cast<char*>(staging(nd * 8 + ni * 4));
+  double* h_pos = reinterpret_cast<double*>(hb);
+  double* h_cell = h_pos + size_t(N) * 3;
+  double* h_cinv = h_cell + size_t(B) * 9;
+  int* h_sid = reinterpret_cast<int*>(h_cinv + size_t(B) * 9);
+  int* h_spec = h_sid + N;
+  int* h_soff = h_spec + N;
+  int* h_sper = h_soff + B + 1;
+  int* h_gnc = h_sper + B;
+  int* h_gnr = h_gnc + 3 * B;
+  int* h_goff = h_gnr + 3 * B;
+  h_cells.assign(size_t(B) * 9, 0.0);
+  h_natoms.assign(B, 0);
+  h_per.assign(B, 0);
+  int gi = 0, bins = 0;
+  for (int b = 0; b < B; ++b) {
+    const pet_system& s = systems[b];
+    h_soff[b] = gi;
+    h_natoms[b] = s.n_atoms;
+    h_per[b] = h_sper[b] = (s.pbc[0] ? 1 : 0) | (s.pbc[1] ? 2 : 0) | (s.pbc[2] ? 4 : 0);
+    for (int e = 0; e < 9; ++e) h_cells[size_t(b) * 9 + e] = h_cell[size_t(b) * 9 + e] = s.cell[e];
+    invert_cell(s.cell, h_cinv + size_t(b) * 9);
+    grid_for_cell(s.cell, h_sper[b], s.n_atoms, ckpt.hypers.cutoff, h_gnc + 3 * b, h_gnr + 3 * b);
+    h_goff[b] = bins;
+    bins += h_gnc[3 * b] * h_gnc[3 * b + 1] * h_gnc[3 * b + 2];
+    for (int i = 0; i < s.n_atoms; ++i, ++gi) {
+      for (int d = 0; d < 3; ++d) h_pos[size_t(gi) * 3 + d] = s.positions[size_t(i) * 3 + d];
+      h_sid[gi] = b;
+      h_spec[gi] = species_index(s.atomic_numbers[i]);
+    }
+  }
+  h_soff[B] = gi;
+  h_goff[B] = bins;
+  PETB_CUDA(cudaStreamSynchronize(st.s));  // the previous evaluation may still read the staged block
+  geom_arena.reset();
+  char* db = static_cast<char*>(geom_arena.alloc_bytes(nd * 8 + ni * 4));
+  PETB_CUDA(cudaMemcpyAsync(db, hb, nd * 8 + ni * 4, cudaMemcpyHostToDevice, st.s));
+  Geom g;
+  g.Ntot = N, g.B = B, g.nbins = bins;
+  g.pos = reinterpret_cast<double*>(db);
+  g.scell = g.pos + size_t(N) * 3;
+  g.cinv = g.scell + size_t(B) * 9;
+  g.sid = reinterpret_cast<int*>(g.cinv + size_t(B) * 9);
+  g.spec = g.sid + N;
+  g.soff = g.spec + N;
+  g.sper = g.soff + B + 1;
+  g.gnc = g.sper + B;
+  g.gnr = g.gnc + 3 * B;
+  g.goff = g.gnr + 3 * B;
+  geom = g;
+  // the copy must finish before the staging block is reused by another stage()
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+}
+
+void Engine::update_staged(const double* positions, const double* cells) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (geom.Ntot == 0 && geom.B == 0) throw Error(3, "pet: nothing is staged");
+  if (positions)
+    PETB_CUDA(cudaMemcpyAsync(geom.pos, positions, sizeof(double) * 3 * size_t(geom.Ntot), cudaMemcpyHostToDevice, st.s));
+  if (cells) {
+    const int B = geom.B;
+    std::vector<double> hc(size_t(B) * 18);
+    std::vector<int> gi(size_t(B) * 7 + 1);
+    int bins = 0;
+    for (int b = 0; b < B; ++b) {
+      for (int e = 0; e < 9; ++e) h_cells[size_t(b) * 9 + e] = hc[size_t(b) * 9 + e] = cells[size_t(b) * 9 + e];
+      invert_cell(cells + size_t(b) * 9, hc.data() + size_t(B) * 9 + size_t(b) * 9);
+      grid_for_cell(cells + size_t(b) * 9, h_per[b], h_natoms[b], ckpt.hypers.cutoff, gi.data() + 3 * b, gi.data() + 3 * B + 3 * b);
+      gi[6 * B + b] = bins;
+      bins += gi[3 * b] * gi[3 * b + 1] * gi[3 * b + 2];
+    }
+    gi[7 * B] = bins;
+    geom.nbins = bins;
+    PETB_CUDA(cudaMemcpyAsync(geom.scell, hc.data(), sizeof(double) * 18 * size_t(B), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(geom.gnc, gi.data(), sizeof(int) * (7 * size_t(B) + 1), cudaMemcpyHostToDevice, st.s));
+  }
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+}
+
+// ---- one evaluation -----------------------------------------------------------------
+
+void Engine::run_model(const PackedEdges& pk, bool forces) {
+  taps.clear();
+  last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, want_taps ? &taps : nullptr);
+  last_pk = pk;
+  have_out = true;
+}
+
+void Engine::compute_staged(bool forces) {
+  PETB_CUDA(cudaSetDevice(device));
+  have_out = false;
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  nbr_arena.reset();
+  save_arena.reset();
+  tmp_arena.reset();
+  PETB_CUDA(cudaEventRecord(ev0, st.s));
+  const Geom& g = geom;
+  posw = nbr_arena.alloc<double>(3 * size_t(g.Ntot > 0 ? g.Ntot : 1));
+  wrap_positions(st, g, posw);
+  RawEdges re = cell_list_search(st, nbr_arena, g, posw, ckpt.hypers.cutoff);
+  find_reverse(st, re, g.Ntot);
+  PackedEdges pk = pack_edges(st, nbr_arena, re, g.Ntot, g.spec, model->cutoff_spec(), pinned);
+  pk.n_atoms = g.Ntot, pk.n_local = g.Ntot, pk.B = g.B, pk.sid = g.sid, pk.soff = g.soff;
+  last_B = g.B, last_N = g.Ntot;
+  if (g.Ntot > 0 && g.B > 0) run_model(pk, forces);
+  else last_pk = pk;
+  PETB_CUDA(cudaEventRecord(ev1, st.s));
+}
+
+void Engine::fetch(pet_results* out) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (!out) throw Error(2, "pet: no results struct given");
+  const int B = last_B, N = last_N;
+  if (have_out) {
+    const PassOut& o = last_out;
+    if (out->energy) PETB_CUDA(cudaMemcpyAsync(out->energy, o.f.energy, sizeof(double) * B, cudaMemcpyDeviceToHost, st.s));
+    if (out->per_atom_energy)
+      PETB_CUDA(cudaMemcpyAsync(out->per_atom_energy, o.per_atom, sizeof(double) * N, cudaMemcpyDeviceToHost, st.s));
+    if (o.has_forces) {
+      if (out->forces) PETB_CUDA(cudaMemcpyAsync(out->forces, o.f.forces, sizeof(double) * 3 * N, cudaMemcpyDeviceToHost, st.s));
+      if (out->virial) PETB_CUDA(cudaMemcpyAsync(out->virial, o.f.vir6, sizeof(double) * 6 * B, cudaMemcpyDeviceToHost, st.s));
+    }
+    if (out->struct_id && last_pk.sid)
+      PETB_CUDA(cudaMemcpyAsync(out->struct_id, last_pk.sid, sizeof(int) * N, cudaMemcpyDeviceToHost, st.s));
+  }
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  float ms = 0.f;
+  if (cudaEventElapsedTime(&ms, ev0, ev1) == cudaSuccess) last_ms = ms;
+}
+
+void Engine::compute(const pet_system* systems, int B, bool forces, pet_results* out) {
+  stage(systems, B);
+  compute_staged(forces);
+  fetch(out);
+}
+
+void Engine::neighbor_list(const pet_system* systems, int B, pet_raw_edges* out) {
+  if (!out) throw Error(2, "pet: no edge struct given");
+  stage(systems, B);
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  nbr_arena.reset();
+  const Geom& g = geom;
+  posw = nbr_arena.alloc<double>(3 * size_t(g.Ntot > 0 ? g.Ntot : 1));
+  wrap_positions(st, g, posw);
+  RawEdges re = cell_list_search(st, nbr_arena, g, posw, ckpt.hypers.cutoff);
+  find_reverse(st, re, g.Ntot);
+  out->n_edges = re.E;
+  if (re.E > out->capacity) throw Error(2, "pet: " + std::to_string(re.E) + " edges, above the given capacity");
+  const size_t E = re.E;
+  if (E) {
+    if (out->i) PETB_CUDA(cudaMemcpyAsync(out->i, re.i, 4 * E, cudaMemcpyDeviceToHost, st.s));
+    if (out->j) PETB_CUDA(cudaMemcpyAsync(out->j, re.j, 4 * E, cudaMemcpyDeviceToHost, st.s));
+    if (out->shift) PETB_CUDA(cudaMemcpyAsync(out->shift, re.shift, 12 * E, cudaMemcpyDeviceToHost, st.s));
+    if (out->vec) PETB_CUDA(cudaMemcpyAsync(out->vec, re.vec, 24 * E, cudaMemcpyDeviceToHost, st.s));
+    if (out->dist) PETB_CUDA(cudaMemcpyAsync(out->dist, re.dist, 8 * E, cudaMemcpyDeviceToHost, st.s));
+    if (out->reverse) PETB_CUDA(cudaMemcpyAsync(out->reverse, re.reverse, 4 * E, cudaMemcpyDeviceToHost, st.s));
+    if (out->cutoff) {
+      PackedEdges pk = pack_edges(st, nbr_arena, re, g.Ntot, g.spec, model->cutoff_spec(), pinned);
+      if (pk.E != re.E) throw Error(3, "pet: a raw edge lies past the cutoff");
+      PETB_CUDA(cudaMemcpyAsync(out->cutoff, pk.cut, 4 * E, cudaMemcpyDeviceToHost, st.s));
+    }
+  }
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+}
+
+// ---- an engine's own list (EdgeSession, src/device_geometry.cpp:410-454,673-778) --------
+
+void Engine::set_neighbors(const pet_edge_list* v) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (!v || v->n_atoms < 0 || (v->n_atoms > 0 && (!v->offsets || !v->atomic_numbers)))
+    throw Error(2, "pet: an edge list needs offsets and atomic numbers");
+  const int N = v->n_atoms, L = N > 0 ? v->offsets[N] : 0;
+  if (N >= (1 << 24)) throw Error(1, "pet: too many atoms for the edge key");
+  std::vector<int> sp(N);
+  for (int i = 0; i < N; ++i) sp[i] = species_index(v->atomic_numbers[i]);
+  // Directed edges grouped by centre: each atom's listed pairs, then the mirrors of the pairs that list it.
+  std::vector<int> off(N + 1, 0);
+  for (int i = 0; i < N; ++i) {
+    off[i + 1] += v->offsets[i + 1] - v->offsets[i];
+    if (v->half)
+      for (int e = v->offsets[i]; e < v->offsets[i + 1]; ++e) ++off[v->neighbors[e] + 1];
+  }
+  for (int i = 0; i < N; ++i) off[i + 1] += off[i];
+  const int E = off[N];
+  std::vector<int> ri(E), rj(E), sh(3 * size_t(E), 0), cur(off.begin(), off.end() - 1);
+  Session& s = md;
+  s.src.assign(E, 0), s.dir.assign(E, 1);
+  auto put = [&](int c, int n, int e, int sign) {
+    const int k = cur[c]++;
+    ri[k] = c, rj[k] = n, s.src[k] = e, s.dir[k] = sign;
+    if (!v->shifts) return;
+    for (int d = 0; d < 3; ++d) {
+      sh[3 * size_t(k) + d] = sign * v->shifts[3 * size_t(e) + d];
+      if (std::abs(sh[3 * size_t(k) + d]) > 15) throw Error(1, "pet: cell shift too large for the edge key");
+    }
+  };
+  for (int i = 0; i < N; ++i)
+    for (int e = v->offsets[i]; e < v->offsets[i + 1]; ++e) {
+      if (v->neighbors[e] < 0 || v->neighbors[e] >= N) throw Error(2, "pet: a neighbour index is out of range");
+      put(i, v->neighbors[e], e, 1);
+    }
+  if (v->half)
+    for (int i = 0; i < N; ++i)
+      for (int e = v->offsets[i]; e < v->offsets[i + 1]; ++e) put(v->neighbors[e], i, e, -1);
+
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  session_arena.reset();
+  Arena& A = session_arena;
+  const size_t Ea = E > 0 ? E : 1, Na = N > 0 ? N : 1;
+  s.valid = false;
+  s.n_atoms = N, s.n_local = v->n_local < 0 ? N : v->n_local, s.n_pairs = L, s.E = E;
+  s.shifted = v->shifts != nullptr, s.half = v->half != 0;
+  s.species = A.alloc<int>(Na);
+  s.sid = A.alloc<int>(Na);
+  s.soff = A.alloc<int>(2);
+  s.pos = A.alloc<double>(3 * Na);
+  s.cell = A.alloc<double>(9);
+  s.re = RawEdges();
+  s.re.E = E;
+  s.re.i = A.alloc<int>(Ea), s.re.j = A.alloc<int>(Ea), s.re.shift = A.alloc<int>(3 * Ea);
+  s.re.vec = A.alloc<double>(3 * Ea), s.re.dist = A.alloc<double>(Ea);
+  s.re.off = A.alloc<int>(N + 1), s.re.reverse = A.alloc<int>(Ea);
+  const int soff[2] = {0, N};
+  PETB_CUDA(cudaMemcpyAsync(s.species, sp.data(), 4 * size_t(N), cudaMemcpyHostToDevice, st.s));
+  PETB_CUDA(cudaMemsetAsync(s.sid, 0, 4 * Na, st.s));
+  PETB_CUDA(cudaMemcpyAsync(s.soff, soff, 8, cudaMemcpyHostToDevice, st.s));
+  PETB_CUDA(cudaMemsetAsync(s.cell, 0, 72, st.s));
+  PETB_CUDA(cudaMemcpyAsync(s.re.off, off.data(), 4 * size_t(N + 1), cudaMemcpyHostToDevice, st.s));
+  std::vector<int> rrev(E, -1);
+  if (E) {
+    PETB_CUDA(cudaMemcpyAsync(s.re.i, ri.data(), 4 * size_t(E), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(s.re.j, rj.data(), 4 * size_t(E), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(s.re.shift, sh.data(), 12 * size_t(E), cudaMemcpyHostToDevice, st.s));
+    find_reverse(st, s.re, N);
+    PETB_CUDA(cudaMemcpyAsync(rrev.data(), s.re.reverse, 4 * size_t(E), cudaMemcpyDeviceToHost, st.s));
+  }
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  // Partnerless edges by target atom, each atom's in edge order.
+  std::vector<int> ooff(N + 1, 0), oedge;
+  for (int e = 0; e < E; ++e)
+    if (rrev[e] < 0) ++ooff[rj[e] + 1];
+  for (int i = 0; i < N; ++i) ooff[i + 1] += ooff[i];
+  s.n_orphan = ooff[N];
+  s.ooff = s.oedge = nullptr;
+  if (s.n_orphan > 0) {
+    oedge.resize(s.n_orphan);
+    std::vector<int> at(ooff.begin(), ooff.end() - 1);
+    for (int e = 0; e < E; ++e)
+      if (rrev[e] < 0) oedge[at[rj[e]]++] = e;
+    s.ooff = A.alloc<int>(N + 1), s.oedge = A.alloc<int>(s.n_orphan);
+    PETB_CUDA(cudaMemcpyAsync(s.ooff, ooff.data(), 4 * size_t(N + 1), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(s.oedge, oedge.data(), 4 * size_t(s.n_orphan), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaStreamSynchronize(st.s));
+  }
+  s.valid = true;
+}
+
+namespace {
+
+struct StepOut {
+  double* eg_raw = nullptr;  // [E_raw,3] scaled edge gradients in the session's edge order
+};
+
+}  // namespace
+
+static StepOut session_step(Engine& I, const double* positions, bool on_device, const double* cell, bool forces) {
+  Session& s = I.md;
+  Stream& st = I.st;
+  if (!s.valid) throw Error(1, "pet: no neighbour list set");
+  if (s.shifted && !cell) throw Error(1, "pet: an edge list with shifts needs the cell");
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  I.have_out = false;
+  I.nbr_arena.reset();
+  I.save_arena.reset();
+  I.tmp_arena.reset();
+  PETB_CUDA(cudaEventRecord(I.ev0, st.s));
+  const int N = s.n_atoms;
+  if (N)
+    PETB_CUDA(cudaMemcpyAsync(s.pos, positions, 24 * size_t(N), on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st.s));
+  if (cell) PETB_CUDA(cudaMemcpyAsync(s.cell, cell, 72, cudaMemcpyHostToDevice, st.s));
+  edge_vectors(st, s.re, s.pos, s.cell);
+  PackedEdges pk = pack_edges(st, I.nbr_arena, s.re, N, s.species, I.model->cutoff_spec(), I.pinned);
+  pk.n_atoms = N, pk.n_local = s.n_local, pk.B = 1, pk.sid = s.sid, pk.soff = s.soff;
+  I.last_B = 1, I.last_N = N;
+  StepOut so;
+  if (N == 0) return so;
+  I.taps.clear();
+  I.last_out = I.model->run(st, I.save_arena, I.tmp_arena, pk, forces, I.gemm_mode, I.want_taps ? &I.taps : nullptr);
+  I.last_pk = pk;
+  I.have_out = true;
+  if (forces && s.E > 0) {
+    so.eg_raw = I.save_arena.alloc<double>(3 * size_t(s.E));
+    k_raw_edge_grad<<<cdiv(s.E, 256), 256, 0, st.s>>>(so.eg_raw, I.last_out.f.edge_grad, pk.packed_of_raw, s.E,
+                                                      I.model->energy_scale());
+    PETB_LAUNCH_CHECK(st);
+    if (s.n_orphan > 0) {
+      k_orphan_forces<<<cdiv(N, 256), 256, 0, st.s>>>(I.last_out.f.forces, so.eg_raw, s.ooff, s.oedge, N);
+      PETB_LAUNCH_CHECK(st);
+    }
+  }
+  PETB_CUDA(cudaEventRecord(I.ev1, st.s));
+  return so;
+}
+
+void Engine::compute_step(const double* positions, const double* cell, bool forces, bool edge_gradients, pet_results* out) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (!positions && md.n_atoms > 0) throw Error(2, "pet: no positions given");
+  const StepOut so = session_step(*this, positions, false, cell, forces);
+  std::vector<double> g;
+  if (forces && edge_gradients && out && out->edge_gradient && so.eg_raw) {
+    g.resize(3 * size_t(md.E));
+    PETB_CUDA(cudaMemcpyAsync(g.data(), so.eg_raw, 24 * size_t(md.E), cudaMemcpyDeviceToHost, st.s));
+  }
+  fetch(out);
+  if (forces && edge_gradients && out && out->edge_gradient) {
+    // A half list's pair gets both directions: g(i -> j) - g(j -> i)  (src/calculator.cpp:689-699).
+    std::fill(out->edge_gradient, out->edge_gradient + 3 * size_t(md.n_pairs), 0.0);
+    for (size_t e = 0; e < g.size() / 3; ++e)
+      for (int c = 0; c < 3; ++c) out->edge_gradient[size_t(md.src[e]) * 3 + c] += md.dir[e] * g[e * 3 + c];
+  }
+}
+
+void Engine::compute_step_device(const pet_device_arrays* a, const double* cell, pet_totals* totals) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (!a || !a->positions) throw Error(2, "pet: no device positions given");
+  const bool forces = a->forces != nullptr;
+  const StepOut so = session_step(*this, a->positions, true, cell, forces);
+  const int N = md.n_atoms;
+  pet_totals t{};
+  if (have_out && N > 0) {
+    k_add_arrays<<<cdiv(N, 256), 256, 0, st.s>>>(a->forces, last_out.f.forces, a->per_atom_energy, last_out.per_atom, N);
+    PETB_LAUNCH_CHECK(st);
+    if (a->per_atom_virial && forces && so.eg_raw) {
+      k_atom_virial<<<cdiv(N, 256), 256, 0, st.s>>>(a->per_atom_virial, so.eg_raw, md.re.vec, md.re.off, md.re.reverse,
+                                                    md.n_orphan > 0 ? md.ooff : nullptr, md.oedge, N, 0.5 * a->virial_scale);
+      PETB_LAUNCH_CHECK(st);
+    }
+    double* h = reinterpret_cast<double*>(pinned + 16);
+    PETB_CUDA(cudaMemcpyAsync(h, last_out.f.energy, 8, cudaMemcpyDeviceToHost, st.s));
+    if (forces) PETB_CUDA(cudaMemcpyAsync(h + 1, last_out.f.vir6, 48, cudaMemcpyDeviceToHost, st.s));
+    PETB_CUDA(cudaStreamSynchronize(st.s));
+    t.energy = h[0];
+    if (forces)
+      for (int k = 0; k < 6; ++k) t.virial[k] = h[1 + k];
+  }
+  if (totals) *totals = t;
+}
+
+// ---- testing aids ---------------------------------------------------------------------
+
+void Engine::debug_fetch(const char* name, float* out, size_t capacity, size_t* n) {
+  PETB_CUDA(cudaSetDevice(device));
+  const auto it = taps.find(name ? name : "");
+  if (it == taps.end()) throw Error(2, std::string("pet: no intermediate named '") + (name ? name : "") + "'");
+  if (n) *n = it->second.second;
+  if (!out) return;
+  if (capacity < it->second.second) throw Error(2, "pet: the buffer is too small for this intermediate");
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  PETB_CUDA(cudaMemcpy(out, it->second.first, 4 * it->second.second, cudaMemcpyDeviceToHost));
+}
+
+void Engine::gemm_host(int mode, bool w_transposed, int m, int n, int k, const float* A, const float* W, float* C) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (m <= 0 || n <= 0 || k <= 0 || !A || !W || !C) throw Error(2, "pet: bad GEMM arguments");
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  tmp_arena.reset();
+  float* dA = tmp_arena.alloc<float>(size_t(m) * k);
+  float* dW = tmp_arena.alloc<float>(size_t(n) * k);
+  float* dC = tmp_arena.alloc<float>(size_t(m) * n);
+  PETB_CUDA(cudaMemcpyAsync(dA, A, 4 * size_t(m) * k, cudaMemcpyHostToDevice, st.s));
+  // The kernels take the weight K-major, [n, k]; the other orientation is transposed here, as a
+  // loaded weight is kept in both.
+  std::vector<float> wt;
+  const float* hw = W;
+  if (!w_transposed) {
+    wt.resize(size_t(n) * k);
+    for (int p = 0; p < k; ++p)
+      for (int j = 0; j < n; ++j) wt[size_t(j) * k + p] = W[size_t(p) * n + j];
+    hw = wt.data();
+  }
+  PETB_CUDA(cudaMemcpyAsync(dW, hw, 4 * size_t(n) * k, cudaMemcpyHostToDevice, st.s));
+  GemmArgs a;
+  a.A = dA, a.lda = k, a.B = dW, a.ldb = k, a.C = dC, a.ldc = n, a.M = m, a.N = n, a.K = k;
+  gemm(st, tmp_arena, a, mode);
+  PETB_CUDA(cudaMemcpyAsync(C, dC, 4 * size_t(m) * n, cudaMemcpyDeviceToHost, st.s));
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+}
+
+}  // namespace petb

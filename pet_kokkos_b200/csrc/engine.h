@@ -1,0 +1,87 @@
+// The calculator behind the C ABI: owns the device, the stream, the scratch pools,
+// the model and the staged geometry, and runs one evaluation end to end.
+//
+// Stands for the reference's Calculator::Impl (src/calculator.cpp) on its device
+// neighbour path: stage_systems -> build_nef_device -> PetModel::compute -> results.
+#pragma once
+
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/pet_b200.h"
+#include "checkpoint.h"
+#include "common.h"
+#include "model.h"
+#include "neighbors.h"
+
+namespace petb {
+
+// An engine's neighbour list held on the device between its rebuilds
+// (the reference's EdgeSession, src/device_geometry.cpp:410-778).
+struct Session {
+  bool valid = false, shifted = false, half = false;
+  int n_atoms = 0, n_local = 0, n_pairs = 0, E = 0;
+  RawEdges re;            // directed edges grouped by centre; vec/dist refreshed each step
+  int* species = nullptr;  // [n_atoms]
+  int* sid = nullptr;      // [n_atoms] zeros
+  int* soff = nullptr;     // [2] = {0, n_atoms}
+  double* pos = nullptr;   // [n_atoms,3]
+  double* cell = nullptr;  // [9]
+  int* ooff = nullptr;     // [n_atoms+1] partnerless edges by target atom
+  int* oedge = nullptr;    // [n_orphan]
+  int n_orphan = 0;
+  std::vector<int> src, dir;  // each directed edge's pair in the engine's list, and its sign
+};
+
+struct Engine {
+  explicit Engine(const std::string& json, const std::string& weights, const pet_options* opts);
+  ~Engine();
+
+  // Calculator::compute(vector<System>) on the device path.
+  void compute(const pet_system* systems, int B, bool forces, pet_results* out);
+  void stage(const pet_system* systems, int B);
+  void update_staged(const double* positions, const double* cells);
+  void compute_staged(bool forces);
+  void fetch(pet_results* out);
+  void neighbor_list(const pet_system* systems, int B, pet_raw_edges* out);
+  void set_neighbors(const pet_edge_list* list);
+  void compute_step(const double* positions, const double* cell, bool forces, bool edge_gradients, pet_results* out);
+  void compute_step_device(const pet_device_arrays* arrays, const double* cell, pet_totals* totals);
+  void debug_fetch(const char* name, float* out, size_t capacity, size_t* n);
+  void gemm_host(int mode, bool w_transposed, int m, int n, int k, const float* A, const float* W, float* C);
+
+  int species_index(int Z) const;
+
+  int device = 0;
+  int gemm_mode = 0;
+  bool graphs = true;
+  Stream st;
+  Checkpoint ckpt;
+  std::unique_ptr<Model> model;
+  Arena geom_arena, nbr_arena, save_arena, tmp_arena, session_arena;
+  Geom geom;                  // staged batch
+  std::vector<double> h_cells;  // staged cells on the host (the grid is chosen there)
+  std::vector<int> h_natoms, h_per;
+  double* posw = nullptr;
+  PackedEdges last_pk;
+  PassOut last_out;
+  bool have_out = false;
+  int last_B = 0, last_N = 0;
+  int* pinned = nullptr;  // small pinned scratch for readbacks
+  void* host_stage = nullptr;
+  size_t host_stage_bytes = 0;
+  std::map<std::string, std::pair<const float*, size_t>> taps;
+  bool want_taps = false;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  double last_ms = 0.0;
+  Session md;
+  std::string error;
+
+ private:
+  void run_model(const PackedEdges& pk, bool forces);
+  void* staging(size_t bytes);
+};
+
+}  // namespace petb

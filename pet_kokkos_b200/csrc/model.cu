@@ -1,0 +1,502 @@
+// The PET network: see model.h.
+#include "model.h"
+
+#include <algorithm>
+#include <cmath>
+
+#include "attention.h"
+#include "gemm.h"
+
+namespace petb {
+
+using Taps = std::map<std::string, std::pair<const float*, size_t>>;
+
+// ---- weights -----------------------------------------------------------------
+
+void Model::put_mat(const std::string& name, int rows, int cols, const double* d) {
+  std::vector<float> w(size_t(rows) * cols), wt(size_t(rows) * cols);
+  for (int a = 0; a < rows; ++a)
+    for (int b = 0; b < cols; ++b) {
+      const float v = float(d[size_t(a) * cols + b]);
+      w[size_t(a) * cols + b] = v;
+      wt[size_t(b) * rows + a] = v;
+    }
+  float* dev = nullptr;
+  PETB_CUDA(cudaMalloc(&dev, 2 * w.size() * sizeof(float)));
+  owned_.push_back(dev);
+  PETB_CUDA(cudaMemcpy(dev, w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice));
+  PETB_CUDA(cudaMemcpy(dev + w.size(), wt.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice));
+  mat_[name] = Mat{dev, dev + w.size(), rows, cols};
+}
+
+void Model::put_vec(const std::string& name, int len, const double* d) {
+  std::vector<float> v(len);
+  for (int a = 0; a < len; ++a) v[a] = float(d[a]);
+  float* dev = nullptr;
+  PETB_CUDA(cudaMalloc(&dev, (len > 0 ? len : 1) * sizeof(float)));
+  owned_.push_back(dev);
+  PETB_CUDA(cudaMemcpy(dev, v.data(), len * sizeof(float), cudaMemcpyHostToDevice));
+  vec_[name] = dev;
+}
+
+const Mat& Model::mat(const std::string& name) const {
+  auto it = mat_.find(name);
+  if (it == mat_.end()) throw Error(1, "model: missing matrix '" + name + "'");
+  return it->second;
+}
+const float* Model::vec(const std::string& name) const {
+  auto it = vec_.find(name);
+  if (it == vec_.end()) throw Error(1, "model: missing vector '" + name + "'");
+  return it->second;
+}
+
+Model::Model(const Checkpoint& ck) : h_(ck.hypers), scale_(ck.energy_scale) {
+  const int G = h_.num_gnn_layers, A = h_.num_attention_layers, R = h_.num_readout_layers;
+  const bool ff = h_.feedforward, ln = h_.layernorm, expanded = h_.expanded_node(), swiglu = h_.swiglu;
+
+  // The two families the reference implements (src/model.cpp:314-334); anything else is refused by name.
+  if (ff && (!h_.preln || ln || !swiglu || !expanded))
+    throw Error(1, "model: the feedforward featurizer needs PreLN + RMSNorm + SwiGLU with d_node != d_pet");
+  if (!ff && (h_.preln || !ln || swiglu || expanded))
+    throw Error(1, "model: the residual featurizer needs PostLN + LayerNorm + SiLU with d_node == d_pet");
+  if (A < 1) throw Error(1, "model: num_attention_layers must be >= 1");
+  if (h_.head_dim * h_.num_heads != h_.d_pet) throw Error(1, "model: num_heads * head_dim must equal d_pet");
+  if (h_.d_pet % 4 || h_.d_node % 4 || h_.d_head % 4 || h_.d_feedforward % 4)
+    throw Error(1, "model: layer widths must be multiples of 4");
+
+  auto load_mat = [&](const std::string& n) {
+    const Tensor& t = ck.at(n);
+    if (t.shape.size() != 2) throw Error(1, "model: expected a 2-D tensor '" + n + "'");
+    put_mat(n, int(t.dim(0)), int(t.dim(1)), t.data.data());
+  };
+  auto load_vec = [&](const std::string& n) { put_vec(n, int(ck.at(n).numel()), ck.at(n).data.data()); };
+  auto load_linear = [&](const std::string& p) { load_mat(p + ".weight"), load_vec(p + ".bias"); };
+  // A SwiGLU w_in's [v ; g] output rows interleaved to (v_j, g_j), so a pair meets in one
+  // GEMM thread's run of columns (src/model.cpp:211-222).
+  auto load_swiglu_in = [&](const std::string& p) {
+    const Tensor &W = ck.at(p + ".weight"), &b = ck.at(p + ".bias");
+    const int F = int(W.dim(0)) / 2, K = int(W.dim(1));
+    std::vector<double> w(W.data.size()), bi(b.data.size());
+    for (int j = 0; j < 2 * F; ++j) {
+      const int src = j % 2 ? F + j / 2 : j / 2;
+      std::copy_n(&W.data[size_t(src) * K], K, &w[size_t(j) * K]);
+      bi[j] = b.data[src];
+    }
+    put_mat(p + ".weight", 2 * F, K, w.data());
+    put_vec(p + ".bias", 2 * F, bi.data());
+  };
+  auto load_mlp_in = [&](const std::string& p) { swiglu ? load_swiglu_in(p) : load_linear(p); };
+  auto load_norm = [&](const std::string& p) {
+    load_vec(p + ".weight");
+    if (ln) load_vec(p + ".bias");
+  };
+  // compress.0 folded in double (src/model.cpp:233-254): its input columns are
+  // [edge embedding of (v,|v|) | species block | input_edge].
+  auto fold_compress = [&](int L) {
+    const std::string g = "gnn_layers." + std::to_string(L), c0 = g + ".compress.0";
+    const Tensor &W = ck.at(c0 + ".weight"), &b0 = ck.at(c0 + ".bias");
+    const Tensor &We = ck.at(g + ".edge_embedder.weight"), &be = ck.at(g + ".edge_embedder.bias");
+    const Tensor& T = ck.at(L == 0 ? "edge_embedder.weight" : g + ".neighbor_embedder.weight");
+    const int D = int(W.dim(0)), K = int(W.dim(1)), ns = int(T.dim(0));
+    auto w = [&](int d, int j) { return W.data[size_t(d) * K + j]; };
+    std::vector<double> wx(size_t(D) * 4, 0.0), b(b0.data), tab(size_t(ns) * D, 0.0), wi;
+    for (int d = 0; d < D; ++d)
+      for (int j = 0; j < D; ++j) {
+        for (int c = 0; c < 4; ++c) wx[d * 4 + c] += w(d, j) * We.data[j * 4 + c];
+        b[d] += w(d, j) * be.data[j];
+        for (int s = 0; s < ns; ++s) tab[size_t(s) * D + d] += T.data[size_t(s) * D + j] * w(d, D + j);
+      }
+    put_mat(c0 + "@x4", D, 4, wx.data());
+    put_vec(c0 + "@b", D, b.data());
+    put_mat(c0 + "@tab", ns, D, tab.data());
+    if (L == 0) return;
+    for (int d = 0; d < D; ++d)
+      for (int j = 0; j < D; ++j) wi.push_back(w(d, 2 * D + j));
+    put_mat(c0 + "@in", D, D, wi.data());
+  };
+
+  for (int L = 0; L < G; ++L) {
+    const std::string g = "gnn_layers." + std::to_string(L), ls = std::to_string(L);
+    fold_compress(L);
+    load_linear(g + ".compress.2");
+    for (int a = 0; a < A; ++a) {
+      const std::string tl = g + ".trans.layers." + std::to_string(a);
+      load_linear(tl + ".attention.input_linear");
+      load_linear(tl + ".attention.output_linear");
+      load_norm(tl + ".norm_attention");
+      load_norm(tl + ".norm_mlp");
+      load_mlp_in(tl + ".mlp.w_in");
+      load_linear(tl + ".mlp.w_out");
+      if (expanded) {
+        load_linear(tl + ".center_contraction");
+        load_linear(tl + ".center_expansion");
+        load_norm(tl + ".norm_center_features");
+        load_mlp_in(tl + ".center_mlp.w_in");
+        load_linear(tl + ".center_mlp.w_out");
+      }
+    }
+    if (ff) {
+      load_vec("combination_norms." + ls + ".weight");
+      load_vec("combination_norms." + ls + ".bias");
+      load_linear("combination_mlps." + ls + ".0");
+      load_linear("combination_mlps." + ls + ".2");
+    }
+  }
+  load_mat("edge_embedder.weight");
+  for (int i = 0; i < R; ++i) {
+    const std::string si = std::to_string(i);
+    load_mat("node_embedders." + si + ".weight");
+    load_linear("node_heads.energy." + si + ".0");
+    load_linear("node_heads.energy." + si + ".2");
+    load_linear("edge_heads.energy." + si + ".0");
+    load_linear("edge_heads.energy." + si + ".2");
+    load_linear("node_last_layers.energy." + si + ".energy___0");
+    load_linear("edge_last_layers.energy." + si + ".energy___0");
+  }
+  const size_t ns = ck.composition_energies.size();
+  PETB_CUDA(cudaMalloc(&comp_, (ns ? ns : 1) * sizeof(double)));
+  PETB_CUDA(cudaMemcpy(comp_, ck.composition_energies.data(), ns * sizeof(double), cudaMemcpyHostToDevice));
+}
+
+Model::~Model() {
+  for (void* p : owned_) cudaFree(p);
+  cudaFree(comp_);
+}
+
+// ---- the GEMM calls, by role ------------------------------------------------------
+
+namespace {
+
+struct Gemms {
+  Stream& st;
+  Arena& tmp;
+  int mode;
+
+  // out[M, W.rows] = in[M, W.cols] . W^T + bias (+ res for rows >= res_row0)
+  void linear(float* out, const float* in, const Mat& W, const float* bias, int M, const float* res = nullptr,
+              int res_row0 = 0) const {
+    GemmArgs a;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.C = out, a.ldc = W.rows;
+    a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.res = res, a.ldr = W.rows, a.res_row0 = res_row0;
+    gemm(st, tmp, a, mode);
+  }
+  // out = silu(pre), pre = in . W^T + bias, kept when `pre` is given
+  void linear_silu(float* out, float* pre, const float* in, const Mat& W, const float* bias, int M) const {
+    GemmArgs a;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.C = out, a.ldc = W.rows;
+    a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.pre = pre, a.ldp = W.rows, a.epi = EPI_SILU;
+    gemm(st, tmp, a, mode);
+  }
+  // pre[M, 2F] = in . W^T + bias (interleaved v, g); h[M, F] = v * sigmoid(g)
+  void swiglu_in(float* h, float* pre, const float* in, const Mat& W, const float* bias, int M) const {
+    GemmArgs a;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.C = h, a.ldc = W.rows / 2;
+    a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.pre = pre, a.ldp = W.rows, a.epi = EPI_SWIGLU;
+    gemm(st, tmp, a, mode);
+  }
+  // in_adj[M, W.cols] (+)= out_adj[M, W.rows] . W
+  void linear_bwd(float* in_adj, const float* out_adj, const Mat& W, int M, bool acc) const {
+    GemmArgs a;
+    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.C = in_adj, a.ldc = W.cols;
+    a.M = M, a.N = W.cols, a.K = W.rows, a.res = acc ? in_adj : nullptr, a.ldr = W.cols;
+    gemm(st, tmp, a, mode);
+  }
+  // grad[M, W.cols] = (out_adj . W) * silu'(pre)
+  void linear_silu_bwd(float* grad, const float* out_adj, const Mat& W, const float* pre, int M) const {
+    GemmArgs a;
+    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.C = grad, a.ldc = W.cols;
+    a.M = M, a.N = W.cols, a.K = W.rows, a.pre = const_cast<float*>(pre), a.ldp = W.cols, a.epi = EPI_SILU_BWD;
+    gemm(st, tmp, a, mode);
+  }
+  // pre_adj[M, 2F] from h_adj = out_adj . W_out and the saved pre
+  void swiglu_out_bwd(float* pre_adj, const float* out_adj, const Mat& w_out, const float* pre, int M) const {
+    GemmArgs a;
+    a.A = out_adj, a.lda = w_out.rows, a.B = w_out.wt, a.ldb = w_out.rows, a.C = pre_adj, a.ldc = 2 * w_out.cols;
+    a.M = M, a.N = w_out.cols, a.K = w_out.rows, a.pre = const_cast<float*>(pre), a.ldp = 2 * w_out.cols;
+    a.epi = EPI_SWIGLU_BWD;
+    gemm(st, tmp, a, mode);
+  }
+};
+
+struct Scope {
+  Arena& a;
+  Arena::Mark m;
+  explicit Scope(Arena& ar) : a(ar), m(ar.mark()) {}
+  ~Scope() { a.rewind(m); }
+};
+
+void tap(Taps* taps, const std::string& name, const float* p, size_t n) {
+  if (taps) (*taps)[name] = {p, n};
+}
+
+}  // namespace
+
+// ---- the tail shared by both featurizers ------------------------------------------
+
+PassOut Model::finish(Stream& st, Arena& save, const PackedEdges& pk, bool grad, float* x4_adj, const float* cutoff_adj,
+                      float* cf_adj, double* per_atom) {
+  PassOut out;
+  out.per_atom = per_atom;
+  out.f.energy = save.alloc<double>(pk.B);
+  structure_energy(st, out.f.energy, per_atom, pk.soff, pk.B);
+  if (!grad) return out;
+  out.has_forces = true;
+  out.f.edge_grad = save.alloc<double>(3 * size_t(pk.E > 0 ? pk.E : 1));
+  out.f.forces = save.alloc<double>(3 * size_t(pk.n_atoms));
+  out.f.vir_atom = save.alloc<double>(9 * size_t(pk.n_atoms));
+  out.f.vir9 = save.alloc<double>(9 * size_t(pk.B));
+  out.f.vir6 = save.alloc<double>(6 * size_t(pk.B));
+  forces_and_virial(st, out.f, pk, x4_adj, cutoff_adj, cf_adj, cutoff_spec(), scale_);
+  return out;
+}
+
+PassOut Model::run(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode, Taps* taps) {
+  if (h_.feedforward) return run_feedforward(st, save, tmp, pk, grad, mode, taps);
+  return run_residual(st, save, tmp, pk, grad, mode, taps);
+}
+
+// ---- the feedforward featurizer ---------------------------------------------------
+
+PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode, Taps* taps) {
+  const int N = pk.N, E = pk.E, T = N + E, S = pk.M + 1;
+  const int D = h_.d_pet, Dn = h_.d_node, Dh = h_.d_head, H = h_.num_heads, hd = h_.head_dim;
+  const int G = h_.num_gnn_layers, A = h_.num_attention_layers;
+  const Gemms gm{st, tmp, mode};
+  const float sc = float(1.0 / (std::sqrt(double(hd)) * h_.attention_temperature));
+  const size_t Ea = E > 0 ? E : 1, Ta = T > 0 ? T : 1, Na = N > 0 ? N : 1;
+
+  struct Block {
+    float *tok, *qkv, *merged, *ml, *eps, *node_res, *pre_c, *pre_e;
+  };
+  struct Layer {
+    float *cpre, *cph_pre, *out_edge;
+    std::vector<Block> blk;
+  };
+  std::vector<Layer> sav(G);
+
+  float* node = save.alloc<float>(Na * Dn);
+  float* input_edge = save.alloc<float>(Ea * D);
+  gather_rows(st, node, mat("node_embedders.0.weight").w, pk.atom_species, N, Dn);
+  gather_rows(st, input_edge, mat("edge_embedder.weight").w, pk.species, E, D);
+
+  for (int L = 0; L < G; ++L) {
+    const std::string g = "gnn_layers." + std::to_string(L), ls = std::to_string(L), c0 = g + ".compress.0";
+    Layer& sl = sav[L];
+    sl.blk.resize(A);
+    // Token buffers: block a's tokens are [input_node ; edge_cur]; its edge output is written
+    // straight into the edge rows of block a+1's, the last one's being the layer's out_edge.
+    std::vector<float*> tokbuf(A + 1);
+    for (int a = 0; a <= A; ++a) tokbuf[a] = save.alloc<float>(Ta * D);
+    sl.cpre = save.alloc<float>(Ea * D);
+    {
+      Scope s0(tmp);
+      float* cact = tmp.alloc<float>(Ea * D);
+      if (L == 0) {
+        compress0(st, cact, sl.cpre, vec(c0 + "@b"), mat(c0 + "@tab").w, mat(c0 + "@x4").w, pk, D);
+      } else {
+        const Mat& wi = mat(c0 + "@in");
+        GemmArgs a;
+        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
+        a.bias = vec(c0 + "@b"), a.pre = sl.cpre, a.ldp = D, a.tab = mat(c0 + "@tab").w, a.sp = pk.species;
+        a.wx = mat(c0 + "@x4").w, a.vec = pk.vec, a.dist = pk.dist, a.epi = EPI_COMPRESS;
+        gemm(st, tmp, a, mode);
+      }
+      gm.linear(tokbuf[0] + size_t(N) * D, cact, mat(g + ".compress.2.weight"), vec(g + ".compress.2.bias"), E);
+    }
+    tap(taps, "et" + ls, tokbuf[0] + size_t(N) * D, size_t(E) * D);
+
+    float* node_cur = node;
+    for (int a = 0; a < A; ++a) {
+      const std::string tl = g + ".trans.layers." + std::to_string(a), tag = ls + "_" + std::to_string(a);
+      Block& b = sl.blk[a];
+      b.tok = tokbuf[a];
+      b.qkv = save.alloc<float>(Ta * 3 * D);
+      b.merged = save.alloc<float>(Ta * D);
+      b.ml = save.alloc<float>(Ta * H * 2);
+      b.eps = save.alloc<float>(Ta * D);  // rows < N: the attention output's atom rows; rows >= N: eps
+      b.node_res = save.alloc<float>(Na * Dn);
+      const Mat &w_cin = mat(tl + ".center_mlp.w_in.weight"), &w_ein = mat(tl + ".mlp.w_in.weight");
+      b.pre_c = save.alloc<float>(Na * w_cin.rows);
+      b.pre_e = save.alloc<float>(Ea * w_ein.rows);
+      float* node_next = save.alloc<float>(Na * Dn);
+      float* edge_cur = b.tok + size_t(N) * D;
+      float* edge_next = tokbuf[a + 1] + size_t(N) * D;
+
+      gm.linear(b.tok, node_cur, mat(tl + ".center_contraction.weight"), vec(tl + ".center_contraction.bias"), N);
+      {
+        Scope s1(tmp);
+        float* attn_in = tmp.alloc<float>(Ta * D);
+        norm_fwd(st, attn_in, b.tok, nullptr, vec(tl + ".norm_attention.weight"), nullptr, T, D);
+        gm.linear(b.qkv, attn_in, mat(tl + ".attention.input_linear.weight"), vec(tl + ".attention.input_linear.bias"), T);
+      }
+      AttnArgs at;
+      at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+      at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml;
+      attention_forward(st, at);
+      tap(taps, "merged" + tag, b.merged, size_t(T) * D);
+      // attn_out = merged W_out^T + b; its edge rows take the residual: eps = attn_out + edge_cur.
+      gm.linear(b.eps, b.merged, mat(tl + ".attention.output_linear.weight"), vec(tl + ".attention.output_linear.bias"), T,
+                b.tok, N);
+      // node_res = node_cur + expansion(atom rows of attn_out)
+      gm.linear(b.node_res, b.eps, mat(tl + ".center_expansion.weight"), vec(tl + ".center_expansion.bias"), N, node_cur, 0);
+      {
+        Scope s2(tmp);
+        float* node_norm = tmp.alloc<float>(Na * Dn);
+        float* hc = tmp.alloc<float>(Na * (w_cin.rows / 2));
+        norm_fwd(st, node_norm, b.node_res, nullptr, vec(tl + ".norm_center_features.weight"), nullptr, N, Dn);
+        gm.swiglu_in(hc, b.pre_c, node_norm, w_cin, vec(tl + ".center_mlp.w_in.bias"), N);
+        gm.linear(node_next, hc, mat(tl + ".center_mlp.w_out.weight"), vec(tl + ".center_mlp.w_out.bias"), N, b.node_res, 0);
+      }
+      {
+        Scope s3(tmp);
+        float* eps_e = b.eps + size_t(N) * D;
+        float* edge_norm = tmp.alloc<float>(Ea * D);
+        float* he = tmp.alloc<float>(Ea * (w_ein.rows / 2));
+        norm_fwd(st, edge_norm, eps_e, nullptr, vec(tl + ".norm_mlp.weight"), nullptr, E, D);
+        gm.swiglu_in(he, b.pre_e, edge_norm, w_ein, vec(tl + ".mlp.w_in.bias"), E);
+        gm.linear(edge_next, he, mat(tl + ".mlp.w_out.weight"), vec(tl + ".mlp.w_out.bias"), E, eps_e, 0);
+      }
+      (void) edge_cur;
+      node_cur = node_next;
+      tap(taps, "node" + tag, node_cur, size_t(N) * Dn);
+      tap(taps, "edge" + tag, edge_next, size_t(E) * D);
+    }
+    node = node_cur;
+    sl.out_edge = tokbuf[A] + size_t(N) * D;
+    sl.cph_pre = save.alloc<float>(Ea * 2 * D);
+    {
+      Scope s4(tmp);
+      float* comb = tmp.alloc<float>(Ea * 2 * D);
+      float* cph = tmp.alloc<float>(Ea * 2 * D);
+      concat_norm_fwd(st, comb, sl.out_edge, pk.reverse, input_edge, vec("combination_norms." + ls + ".weight"),
+                      vec("combination_norms." + ls + ".bias"), E, D);
+      gm.linear_silu(cph, sl.cph_pre, comb, mat("combination_mlps." + ls + ".0.weight"), vec("combination_mlps." + ls + ".0.bias"), E);
+      gm.linear(input_edge, cph, mat("combination_mlps." + ls + ".2.weight"), vec("combination_mlps." + ls + ".2.bias"), E,
+                input_edge, 0);
+    }
+    tap(taps, "input_edge" + ls, input_edge, size_t(E) * D);
+  }
+
+  // ---- readout (src/model.cpp:656-691) ----
+  float* nh0_pre = save.alloc<float>(Na * Dh);
+  float* nh1_pre = save.alloc<float>(Na * Dh);
+  float* eh0_pre = save.alloc<float>(Ea * Dh);
+  float* eh1_pre = save.alloc<float>(Ea * Dh);
+  float* node_pred = save.alloc<float>(Na);
+  float* edge_pred = save.alloc<float>(Ea);
+  float* net = save.alloc<float>(Na);
+  double* per_atom = save.alloc<double>(pk.n_atoms > 0 ? pk.n_atoms : 1);
+  {
+    Scope s5(tmp);
+    float* nh0 = tmp.alloc<float>(Na * Dh);
+    float* nh1 = tmp.alloc<float>(Na * Dh);
+    float* eh0 = tmp.alloc<float>(Ea * Dh);
+    float* eh1 = tmp.alloc<float>(Ea * Dh);
+    gm.linear_silu(nh0, nh0_pre, node, mat("node_heads.energy.0.0.weight"), vec("node_heads.energy.0.0.bias"), N);
+    gm.linear_silu(nh1, nh1_pre, nh0, mat("node_heads.energy.0.2.weight"), vec("node_heads.energy.0.2.bias"), N);
+    gemv_rows(st, nh1, Dh, mat("node_last_layers.energy.0.energy___0.weight").w, vec("node_last_layers.energy.0.energy___0.bias"),
+              node_pred, N, Dh);
+    gm.linear_silu(eh0, eh0_pre, input_edge, mat("edge_heads.energy.0.0.weight"), vec("edge_heads.energy.0.0.bias"), E);
+    gm.linear_silu(eh1, eh1_pre, eh0, mat("edge_heads.energy.0.2.weight"), vec("edge_heads.energy.0.2.bias"), E);
+    gemv_rows(st, eh1, Dh, mat("edge_last_layers.energy.0.energy___0.weight").w, vec("edge_last_layers.energy.0.energy___0.bias"),
+              edge_pred, E, Dh);
+  }
+  tap(taps, "node_pred", node_pred, N);
+  tap(taps, "edge_pred", edge_pred, E);
+  PETB_CUDA(cudaMemsetAsync(per_atom, 0, sizeof(double) * size_t(pk.n_atoms > 0 ? pk.n_atoms : 1), st.s));
+  readout_energy(st, net, per_atom, node_pred, edge_pred, pk, comp_, scale_, false, true);
+  if (!grad) return finish(st, save, pk, false, nullptr, nullptr, nullptr, per_atom);
+
+  // ---- backward (src/model.cpp:749-778, src/feedforward.cpp:199-336) ----
+  float* x4_adj = save.alloc<float>(Ea * 4);
+  float* cf_adj = save.alloc<float>(Ea);
+  PETB_CUDA(cudaMemsetAsync(x4_adj, 0, sizeof(float) * Ea * 4, st.s));
+  PETB_CUDA(cudaMemsetAsync(cf_adj, 0, sizeof(float) * Ea, st.s));
+  float* node_adj = save.alloc<float>(Na * Dn);
+  float* ie_adj = save.alloc<float>(Ea * D);
+  float* tok_adj = save.alloc<float>(Ta * D);
+  float* edge_adj = tok_adj + size_t(N) * D;
+  {
+    Scope s6(tmp);
+    float* nh1_adj = tmp.alloc<float>(Na * Dh);
+    float* nh0_adj = tmp.alloc<float>(Na * Dh);
+    float* eh1_adj = tmp.alloc<float>(Ea * Dh);
+    float* eh0_adj = tmp.alloc<float>(Ea * Dh);
+    readout_seed_bwd(st, nh1_adj, mat("node_last_layers.energy.0.energy___0.weight").w, nh1_pre, nullptr, nullptr, pk.n_local, N, Dh);
+    gm.linear_silu_bwd(nh0_adj, nh1_adj, mat("node_heads.energy.0.2.weight"), nh0_pre, N);
+    gm.linear_bwd(node_adj, nh0_adj, mat("node_heads.energy.0.0.weight"), N, false);
+    readout_seed_bwd(st, eh1_adj, mat("edge_last_layers.energy.0.energy___0.weight").w, eh1_pre, pk.cut, pk.center, pk.n_local, E, Dh);
+    gm.linear_silu_bwd(eh0_adj, eh1_adj, mat("edge_heads.energy.0.2.weight"), eh0_pre, E);
+    gm.linear_bwd(ie_adj, eh0_adj, mat("edge_heads.energy.0.0.weight"), E, false);
+  }
+  for (int L = G - 1; L >= 0; --L) {
+    const std::string g = "gnn_layers." + std::to_string(L), ls = std::to_string(L), c0 = g + ".compress.0";
+    const Layer& sl = sav[L];
+    {
+      Scope s7(tmp);
+      float* cph_adj = tmp.alloc<float>(Ea * 2 * D);
+      float* cnorm_adj = tmp.alloc<float>(Ea * 2 * D);
+      gm.linear_silu_bwd(cph_adj, ie_adj, mat("combination_mlps." + ls + ".2.weight"), sl.cph_pre, E);
+      gm.linear_bwd(cnorm_adj, cph_adj, mat("combination_mlps." + ls + ".0.weight"), E, false);
+      concat_norm_bwd(st, edge_adj, cnorm_adj, sl.out_edge, pk.reverse, ie_adj, vec("combination_norms." + ls + ".weight"), E, D);
+    }
+    for (int a = A - 1; a >= 0; --a) {
+      const std::string tl = g + ".trans.layers." + std::to_string(a);
+      const Block& b = sl.blk[a];
+      const Mat &w_cin = mat(tl + ".center_mlp.w_in.weight"), &w_ein = mat(tl + ".mlp.w_in.weight");
+      {  // the two MLPs: afterwards edge_adj and node_adj are eps's and node_res's
+        Scope s8(tmp);
+        float* pre_adj = tmp.alloc<float>(Ea * w_ein.rows);
+        float* enorm_adj = tmp.alloc<float>(Ea * D);
+        gm.swiglu_out_bwd(pre_adj, edge_adj, mat(tl + ".mlp.w_out.weight"), b.pre_e, E);
+        gm.linear_bwd(enorm_adj, pre_adj, w_ein, E, false);
+        norm_bwd(st, edge_adj, enorm_adj, b.eps + size_t(N) * D, vec(tl + ".norm_mlp.weight"), false, E, D, 0);
+      }
+      {
+        Scope s9(tmp);
+        float* prec_adj = tmp.alloc<float>(Na * w_cin.rows);
+        float* cnorm_adj = tmp.alloc<float>(Na * Dn);
+        gm.swiglu_out_bwd(prec_adj, node_adj, mat(tl + ".center_mlp.w_out.weight"), b.pre_c, N);
+        gm.linear_bwd(cnorm_adj, prec_adj, w_cin, N, false);
+        norm_bwd(st, node_adj, cnorm_adj, b.node_res, vec(tl + ".norm_center_features.weight"), false, N, Dn, 0);
+      }
+      {  // attention: the output adjoint is [expansion's input adjoint ; eps adjoint] = tok_adj
+        Scope s10(tmp);
+        float* dmerged = tmp.alloc<float>(Ta * D);
+        float* qkv_adj = tmp.alloc<float>(Ta * 3 * D);
+        float* cfh = tmp.alloc<float>(Ta * H);
+        float* attn_in_adj = tmp.alloc<float>(Ta * D);
+        gm.linear_bwd(tok_adj, node_adj, mat(tl + ".center_expansion.weight"), N, false);
+        gm.linear_bwd(dmerged, tok_adj, mat(tl + ".attention.output_linear.weight"), T, false);
+        AttnArgs at;
+        at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+        at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml, at.dmerged = dmerged, at.qkv_adj = qkv_adj, at.cfh = cfh;
+        attention_backward(st, at);
+        cutoff_share(st, cf_adj, cfh, pk.cut, N, E, H);
+        gm.linear_bwd(attn_in_adj, qkv_adj, mat(tl + ".attention.input_linear.weight"), T, false);
+        // through the norm, back to where the tokens came from: atom rows to the contraction's
+        // output adjoint (written), edge rows onto the edge residual (accumulated)
+        norm_bwd(st, tok_adj, attn_in_adj, b.tok, vec(tl + ".norm_attention.weight"), false, T, D, N);
+      }
+      gm.linear_bwd(node_adj, tok_adj, mat(tl + ".center_contraction.weight"), N, true);
+    }
+    {  // edge_adj is now et's
+      Scope s11(tmp);
+      float* gz = tmp.alloc<float>(Ea * D);
+      gm.linear_silu_bwd(gz, edge_adj, mat(g + ".compress.2.weight"), sl.cpre, E);
+      compress_geometry_bwd(st, x4_adj, gz, mat(c0 + "@x4").w, E, D);
+      if (L > 0) gm.linear_bwd(ie_adj, gz, mat(c0 + "@in"), E, true);
+    }
+  }
+  tap(taps, "x4_adj", x4_adj, size_t(E) * 4);
+  tap(taps, "cf_adj", cf_adj, E);
+  return finish(st, save, pk, true, x4_adj, edge_pred, cf_adj, per_atom);
+}
+
+// ---- the residual featurizer ------------------------------------------------------
+
+PassOut Model::run_residual(Stream&, Arena&, Arena&, const PackedEdges&, bool, int, Taps*) {
+  throw Error(1, "model: the residual featurizer is not built yet");
+}
+
+}  // namespace petb

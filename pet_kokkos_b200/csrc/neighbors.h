@@ -1,0 +1,93 @@
+// The device neighbour pipeline: staged geometry -> wrapped positions -> cell-list
+// raw edges (ordered, deterministic) -> reverse map -> packed model edges.
+//
+// It replaces the reference's stage_systems / wrap_positions / search
+// (src/device_geometry.cpp:72-161,368-401), build_raw_edges_cells
+// (src/device_cell_list.cpp:108-292), edge_topology / edge_geometry
+// (src/device_neighbors.cpp:140-324) and pack_edges (src/model.cpp:499-584).
+// The edge set, each atom's edge order and the fp64 vectors are the reference's:
+// the distance test is evaluated in the same association order without fused
+// multiply-adds (this file's kernels are compiled with -fmad=false).
+#pragma once
+
+#include "common.h"
+
+namespace petb {
+
+// One batch of B structures, Ntot atoms, staged on the device (the reference's DeviceGeom).
+struct Geom {
+  int Ntot = 0, B = 0;
+  double* pos = nullptr;    // [Ntot,3] unwrapped
+  int* sid = nullptr;       // [Ntot] owning structure
+  int* spec = nullptr;      // [Ntot] species index
+  int* soff = nullptr;      // [B+1] first atom of each structure
+  int* sper = nullptr;      // [B] periodic bits
+  double* scell = nullptr;  // [B,9]
+  double* cinv = nullptr;   // [B,9]
+  int* gnc = nullptr;       // [B,3] bins per axis
+  int* gnr = nullptr;       // [B,3] search reach in bins
+  int* goff = nullptr;      // [B+1] first bin of each structure
+  int nbins = 0;
+};
+
+// Directed edges grouped by centre atom, in the search's fixed order.
+struct RawEdges {
+  int E = 0;
+  int* i = nullptr;        // [E]
+  int* j = nullptr;        // [E]
+  int* shift = nullptr;    // [E,3]
+  double* vec = nullptr;   // [E,3]
+  double* dist = nullptr;  // [E]
+  int* off = nullptr;      // [N+1]
+  int* reverse = nullptr;  // [E] partner (j,i,-shift) or -1
+};
+
+// The kept edges as the network reads them (the reference's PackedEdges).
+struct PackedEdges {
+  int N = 0;          // centre atoms (token rows 0..N-1)
+  int n_atoms = 0;    // all atoms, ghosts included
+  int n_local = 0;    // atoms whose energy counts
+  int E = 0;          // kept edges
+  int M = 0;          // most kept edges of any atom
+  int B = 1;          // structures
+  int* off = nullptr;       // [N+1]
+  int* center = nullptr;    // [E]
+  int* nbr = nullptr;       // [E] neighbour atom
+  int* species = nullptr;   // [E] neighbour species
+  int* reverse = nullptr;   // [E] packed partner or -1
+  double* vec = nullptr;    // [E,3]
+  double* dist = nullptr;   // [E]
+  float* cut = nullptr;     // [E] smooth cutoff factor
+  int* raw_of = nullptr;    // [E] the raw edge this row came from
+  int* packed_of_raw = nullptr;  // [E_raw] or -1
+  const int* atom_species = nullptr;  // [n_atoms]
+  const int* sid = nullptr;           // [n_atoms]
+  const int* soff = nullptr;          // [B+1]
+};
+
+struct CutoffSpec {
+  double cutoff, width;
+  int kind;  // 0 bump, 1 cosine
+};
+
+// Host-side grid choice for one structure (bins per axis, reach), the reference's cl_grid.
+void grid_for_cell(const double cell[9], int periodic_bits, int n_atoms, double cutoff, int nc[3], int nr[3]);
+// Host-side inverse cell (rows = lattice vectors), the reference's pet_cellinv.
+void invert_cell(const double c[9], double inv[9]);
+
+// Wrapped positions for the search: posw [Ntot,3].
+void wrap_positions(Stream& st, const Geom& g, double* posw);
+// The cell-list search. Allocates from `arena`; reads back the edge count once.
+RawEdges cell_list_search(Stream& st, Arena& arena, const Geom& g, const double* posw, double cutoff);
+// Each raw edge's partner, by a search of the neighbour's own range.
+void find_reverse(Stream& st, const RawEdges& re, int N);
+// Edge vectors of an engine-supplied list from positions, shifts and the cell (the reference's md_vectors).
+void edge_vectors(Stream& st, const RawEdges& re, const double* pos, const double* cell9);
+// Keep test, cutoff factors, slots and packing. n_centres <= n_atoms atoms have edges.
+PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int n_centres, const int* atom_species,
+                       const CutoffSpec& cs, int* pinned_scratch);
+
+// int exclusive scan: out[0..n] (n+1 values, out[n] = total).
+void exclusive_scan(Stream& st, Arena& arena, const int* in, int* out, int n);
+
+}  // namespace petb

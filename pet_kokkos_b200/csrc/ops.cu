@@ -1,0 +1,455 @@
+// The network's non-GEMM passes: see ops.h.
+#include "ops.h"
+
+#include "epilogue.cuh"
+
+namespace petb {
+
+namespace {
+
+constexpr float kRmsEps = 1.1920928955078125e-07f;  // the reference's kRmsNormEps (src/ops.hpp:195)
+constexpr float kLnEps = 1e-5f;                     // kLayerNormEps (:196)
+constexpr unsigned kFull = 0xffffffffu;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+  return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+  return v;
+}
+
+__global__ void k_gather_rows(float* __restrict__ out, const float* __restrict__ table, const int* __restrict__ idx, int R,
+                              int D4) {
+  const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= size_t(R) * D4) return;
+  const int r = int(t / D4), q = int(t % D4);
+  reinterpret_cast<float4*>(out)[t] = reinterpret_cast<const float4*>(table)[size_t(idx[r]) * D4 + q];
+}
+
+__global__ void k_compress0(GemmArgs p) {
+  const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int D4 = p.N / 4;
+  if (t >= size_t(p.M) * D4) return;
+  const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+  epilogue_run4<EPI_COMPRESS>(p, int(t / D4), int(t % D4) * 4, zero);
+}
+
+// One warp per row. x = in (+ add, stored back); out = (x - mu) inv w + b.
+__global__ void __launch_bounds__(256) k_norm_fwd(float* __restrict__ out, float* __restrict__ in, const float* __restrict__ add,
+                                                  const float* __restrict__ w, const float* __restrict__ bias, int R, int D) {
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (r >= R) return;
+  float* x = in + size_t(r) * D;
+  const bool ln = bias != nullptr;
+  if (add) {
+    const float* a = add + size_t(r) * D;
+    for (int d = lane; d < D; d += 32) x[d] += a[d];
+  }
+  float mu = 0.f;
+  if (ln) {
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s += x[d];
+    mu = warp_sum(s) / D;
+  }
+  float v = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float c = x[d] - mu;
+    v += c * c;
+  }
+  v = warp_sum(v);
+  const float inv = 1.0f / sqrtf(v / D + (ln ? kLnEps : kRmsEps));
+  float* o = out + size_t(r) * D;
+  for (int d = lane; d < D; d += 32) o[d] = (x[d] - mu) * inv * w[d] + (ln ? bias[d] : 0.f);
+}
+
+__global__ void __launch_bounds__(256) k_concat_norm_fwd(float* __restrict__ out, const float* __restrict__ oe,
+                                                         const int* __restrict__ rev, float* __restrict__ ie,
+                                                         const float* __restrict__ w, const float* __restrict__ bias, int E,
+                                                         int D) {
+  const int k = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (k >= E) return;
+  const int r = rev[k], W = 2 * D;
+  const float* a = oe + size_t(k) * D;
+  const float* b = r >= 0 ? oe + size_t(r) * D : nullptr;
+  float s = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float v = a[d];
+    ie[size_t(k) * D + d] += v;
+    s += v + (b ? b[d] : 0.f);
+  }
+  const float mu = warp_sum(s) / W;
+  float v = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float c0 = a[d] - mu, c1 = (b ? b[d] : 0.f) - mu;
+    v += c0 * c0 + c1 * c1;
+  }
+  v = warp_sum(v);
+  const float inv = 1.0f / sqrtf(v / W + kLnEps);
+  float* o = out + size_t(k) * W;
+  for (int d = lane; d < D; d += 32) {
+    o[d] = (a[d] - mu) * inv * w[d] + bias[d];
+    o[D + d] = ((b ? b[d] : 0.f) - mu) * inv * w[D + d] + bias[D + d];
+  }
+}
+
+struct RowStats {
+  float mu, inv, mg, mgx;
+};
+
+__global__ void __launch_bounds__(256) k_norm_bwd(float* __restrict__ in_adj, const float* __restrict__ out_adj,
+                                                  const float* __restrict__ in, const float* __restrict__ w, bool ln, int R, int D,
+                                                  int acc_row0, float* __restrict__ also) {
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (r >= R) return;
+  const float* x = in + size_t(r) * D;
+  const float* ga = out_adj + size_t(r) * D;
+  float mu = 0.f;
+  if (ln) {
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s += x[d];
+    mu = warp_sum(s) / D;
+  }
+  float sq = 0.f, sg = 0.f, sgx = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float c = x[d] - mu, gw = ga[d] * w[d];
+    sq += c * c, sg += gw, sgx += gw * c;
+  }
+  sq = warp_sum(sq), sg = warp_sum(sg), sgx = warp_sum(sgx);
+  const float inv = 1.0f / sqrtf(sq / D + (ln ? kLnEps : kRmsEps));
+  const float mg = ln ? sg / D : 0.f, mgx = sgx * inv / D;
+  float* o = in_adj + size_t(r) * D;
+  const bool acc = r >= acc_row0;
+  for (int d = lane; d < D; d += 32) {
+    const float g = inv * (ga[d] * w[d] - mg - (x[d] - mu) * inv * mgx);
+    const float v = acc ? o[d] + g : g;
+    o[d] = v;
+    if (also) also[size_t(r) * D + d] = v;
+  }
+}
+
+__global__ void __launch_bounds__(256) k_concat_norm_bwd(float* __restrict__ edge_adj, const float* __restrict__ out_adj,
+                                                         const float* __restrict__ oe, const int* __restrict__ rev,
+                                                         const float* __restrict__ ie_adj, const float* __restrict__ w, int E,
+                                                         int D) {
+  const int k = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (k >= E) return;
+  const int W = 2 * D, r = rev[k];
+  // Row q of the concat is [oe(q) | oe(rev q) or 0].
+  auto stats = [&](int q) {
+    const int pq = rev[q];
+    const float* a = oe + size_t(q) * D;
+    const float* b = pq >= 0 ? oe + size_t(pq) * D : nullptr;
+    const float* ga = out_adj + size_t(q) * W;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s += a[d] + (b ? b[d] : 0.f);
+    const float mu = warp_sum(s) / W;
+    float sq = 0.f, sg = 0.f, sgx = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      const float c0 = a[d] - mu, c1 = (b ? b[d] : 0.f) - mu;
+      const float g0 = ga[d] * w[d], g1 = ga[D + d] * w[D + d];
+      sq += c0 * c0 + c1 * c1, sg += g0 + g1, sgx += g0 * c0 + g1 * c1;
+    }
+    sq = warp_sum(sq), sg = warp_sum(sg), sgx = warp_sum(sgx);
+    const float inv = 1.0f / sqrtf(sq / W + kLnEps);
+    return RowStats{mu, inv, sg / W, sgx * inv / W};
+  };
+  const RowStats sk = stats(k);
+  RowStats sr = sk;
+  const float* xr2 = nullptr;  // the second half of row r: oe(rev r)
+  if (r >= 0) {
+    sr = stats(r);
+    const int pr = rev[r];
+    xr2 = pr >= 0 ? oe + size_t(pr) * D : nullptr;
+  }
+  for (int d = lane; d < D; d += 32) {
+    const float gk = sk.inv * (out_adj[size_t(k) * W + d] * w[d] - sk.mg - (oe[size_t(k) * D + d] - sk.mu) * sk.inv * sk.mgx);
+    float back = 0.f;
+    if (r >= 0) {
+      const float x = (xr2 ? xr2[d] : 0.f) - sr.mu;
+      back = sr.inv * (out_adj[size_t(r) * W + D + d] * w[D + d] - sr.mg - x * sr.inv * sr.mgx);
+    }
+    edge_adj[size_t(k) * D + d] = ie_adj[size_t(k) * D + d] + gk + back;
+  }
+}
+
+__global__ void __launch_bounds__(256) k_compress_geometry_bwd(float* __restrict__ x4_adj, const float* __restrict__ g,
+                                                               const float* __restrict__ wx, int E, int D) {
+  const int k = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (k >= E) return;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float gd = g[size_t(k) * D + d];
+    const float4 ww = ld4(wx + 4 * d);
+    a0 += gd * ww.x, a1 += gd * ww.y, a2 += gd * ww.z, a3 += gd * ww.w;
+  }
+  a0 = warp_sum(a0), a1 = warp_sum(a1), a2 = warp_sum(a2), a3 = warp_sum(a3);
+  if (lane == 0) {
+    float4 v = ld4(x4_adj + 4 * size_t(k));
+    v.x += a0, v.y += a1, v.z += a2, v.w += a3;
+    st4(x4_adj + 4 * size_t(k), v);
+  }
+}
+
+__global__ void k_readout_energy(float* __restrict__ net, double* __restrict__ per_atom, const float* __restrict__ node_pred,
+                                 const float* __restrict__ edge_pred, PackedEdges pk, const double* __restrict__ comp,
+                                 double scale, bool acc, bool assemble) {
+  const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (n >= pk.N) return;
+  double s = 0.0;
+  for (int k = pk.off[n] + lane; k < pk.off[n + 1]; k += 32) s += (double) pk.cut[k] * (double) edge_pred[k];
+  s = warp_sum(s);
+  if (lane == 0) {
+    s += (double) node_pred[n];
+    const float v = acc ? (float) ((double) net[n] + s) : (float) s;
+    net[n] = v;
+    if (assemble) per_atom[n] = n < pk.n_local ? scale * (double) v + comp[pk.atom_species[n]] : 0.0;
+  }
+}
+
+__global__ void k_readout_seed_bwd(float* __restrict__ out, const float* __restrict__ w, const float* __restrict__ pre,
+                                   const float* __restrict__ cut, const int* __restrict__ center, int n_local, int R, int Dh4) {
+  const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= size_t(R) * Dh4) return;
+  const int r = int(t / Dh4), q = int(t % Dh4);
+  float seed;
+  if (cut) seed = center[r] < n_local ? cut[r] : 0.f;
+  else seed = r < n_local ? 1.f : 0.f;
+  const float4 x = reinterpret_cast<const float4*>(pre)[t], ww = reinterpret_cast<const float4*>(w)[q];
+  reinterpret_cast<float4*>(out)[t] = make_float4(seed * ww.x * dsilu_f(x.x), seed * ww.y * dsilu_f(x.y),
+                                                  seed * ww.z * dsilu_f(x.z), seed * ww.w * dsilu_f(x.w));
+}
+
+__global__ void k_cutoff_share(float* __restrict__ cf_adj, const float* __restrict__ cfh, const float* __restrict__ cut, int N,
+                               int E, int H) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= E) return;
+  const float cf = cut[k];
+  if (cf <= 0.f) return;
+  float total = 0.f;
+  for (int h = 0; h < H; ++h) total += cfh[size_t(N + k) * H + h];
+  cf_adj[k] += total / cf;
+}
+
+__global__ void k_add_inplace(float* __restrict__ a, const float* __restrict__ b, size_t n4) {
+  const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= n4) return;
+  float4 x = reinterpret_cast<float4*>(a)[t];
+  const float4 y = reinterpret_cast<const float4*>(b)[t];
+  x.x += y.x, x.y += y.y, x.z += y.z, x.w += y.w;
+  reinterpret_cast<float4*>(a)[t] = x;
+}
+
+__global__ void k_message_average(float* __restrict__ ie, const float* __restrict__ oe, const int* __restrict__ rev, int E,
+                                  int D4) {
+  const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= size_t(E) * D4) return;
+  const int k = int(t / D4), q = int(t % D4), r = rev[k];
+  float4 x = reinterpret_cast<float4*>(ie)[t];
+  const float4 y = r >= 0 ? reinterpret_cast<const float4*>(oe)[size_t(r) * D4 + q] : make_float4(0, 0, 0, 0);
+  reinterpret_cast<float4*>(ie)[t] = make_float4(0.5f * (x.x + y.x), 0.5f * (x.y + y.y), 0.5f * (x.z + y.z), 0.5f * (x.w + y.w));
+}
+
+// The adjoint of message_average: ie_adj_out(k) = 0.5 ie_adj_in(k); oe_adj(k) += 0.5 ie_adj_in(rev k).
+__global__ void k_message_average_bwd(float* __restrict__ ie_out, float* __restrict__ oe_adj, const float* __restrict__ ie_in,
+                                      const int* __restrict__ rev, int E, int D4) {
+  const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= size_t(E) * D4) return;
+  const int k = int(t / D4), q = int(t % D4), r = rev[k];
+  const float4 x = reinterpret_cast<const float4*>(ie_in)[t];
+  float4 o = reinterpret_cast<float4*>(oe_adj)[t];
+  if (r >= 0) {
+    const float4 y = reinterpret_cast<const float4*>(ie_in)[size_t(r) * D4 + q];
+    o.x += 0.5f * y.x, o.y += 0.5f * y.y, o.z += 0.5f * y.z, o.w += 0.5f * y.w;
+  }
+  reinterpret_cast<float4*>(oe_adj)[t] = o;
+  reinterpret_cast<float4*>(ie_out)[t] = make_float4(0.5f * x.x, 0.5f * x.y, 0.5f * x.z, 0.5f * x.w);
+}
+
+// The smooth cutoff's derivative in the distance, in float like the factor itself
+// (bump_ddist / cosine_ddist, src/forces.cpp:22-35).
+__device__ inline double cutoff_ddist(double d, double rc, double w, int kind) {
+  const float pi = (float) 3.14159265358979323846;
+  const float x = (float) ((d - (rc - w)) / w);
+  if (x <= 0.f || x >= 1.f) return 0.0;
+  if (kind == 0) {
+    const float si = sinf(pi * x);
+    const float t = tanhf(cosf(pi * x) / si);
+    const float du = (-pi / (si * si)) / (float) w;
+    return 0.5 * (1.0 - (double) (t * t)) * (double) du;
+  }
+  return 0.5 * (double) (-pi * sinf(pi * x)) / w;
+}
+
+__global__ void k_edge_grad(double* __restrict__ grad, PackedEdges pk, const float* __restrict__ x4_adj,
+                            const float* __restrict__ cutoff_adj, const float* __restrict__ cf_adj, CutoffSpec cs) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= pk.E) return;
+  const bool own = pk.center[k] < pk.n_local;
+  const double cutoff_total = (own ? (double) cutoff_adj[k] : 0.0) + (double) cf_adj[k];
+  const double d = pk.dist[k];
+  const double dist_adj = (double) x4_adj[4 * size_t(k) + 3] + cutoff_total * cutoff_ddist(d, cs.cutoff, cs.width, cs.kind);
+  const double invd = d > 0.0 ? 1.0 / d : 0.0;
+  for (int c = 0; c < 3; ++c) grad[3 * size_t(k) + c] = (double) x4_adj[4 * size_t(k) + c] + dist_adj * pk.vec[3 * size_t(k) + c] * invd;
+}
+
+// One warp per atom: F(i) = scale sum_k [g(k) - g(rev k)], W(i) = scale sum_k v (x) g, lanes striding
+// the atom's edges and combining in a fixed tree.
+__global__ void __launch_bounds__(256) k_fold_forces(ForceOut out, PackedEdges pk, double scale) {
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (i >= pk.n_atoms) return;
+  double f[3] = {0, 0, 0}, w[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (i < pk.N)
+    for (int k = pk.off[i] + lane; k < pk.off[i + 1]; k += 32) {
+      const double* g = out.edge_grad + 3 * size_t(k);
+      const double* v = pk.vec + 3 * size_t(k);
+      const int r = pk.reverse[k];
+      for (int c = 0; c < 3; ++c) f[c] += g[c] - (r >= 0 ? out.edge_grad[3 * size_t(r) + c] : 0.0);
+      for (int a = 0; a < 3; ++a)
+        for (int b = 0; b < 3; ++b) w[a * 3 + b] += v[a] * g[b];
+    }
+  for (int c = 0; c < 3; ++c) f[c] = warp_sum(f[c]);
+  for (int t = 0; t < 9; ++t) w[t] = warp_sum(w[t]);
+  if (lane == 0) {
+    for (int c = 0; c < 3; ++c) out.forces[3 * size_t(i) + c] = scale * f[c];
+    for (int t = 0; t < 9; ++t) out.vir_atom[9 * size_t(i) + t] = scale * w[t];
+  }
+}
+
+// One warp per (structure, component): lane l sums every 32nd atom from the l-th, then a fixed tree.
+__global__ void k_struct_sum(double* __restrict__ out, const double* __restrict__ x, const int* __restrict__ soff, int B, int T) {
+  const int u = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (u >= B * T) return;
+  const int b = u / T, t = u % T;
+  double s = 0.0;
+  for (int a = soff[b] + lane; a < soff[b + 1]; a += 32) s += x[size_t(a) * T + t];
+  s = warp_sum(s);
+  if (lane == 0) out[u] = s;
+}
+
+__global__ void k_voigt(double* __restrict__ w6, const double* __restrict__ w9, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const double* w = w9 + 9 * b;
+  double* o = w6 + 6 * b;
+  o[0] = w[0], o[1] = w[4], o[2] = w[8];
+  o[3] = 0.5 * (w[1] + w[3]), o[4] = 0.5 * (w[2] + w[6]), o[5] = 0.5 * (w[5] + w[7]);
+}
+
+inline unsigned blocks_for(size_t n, int per) { return (unsigned) ((n + per - 1) / per); }
+
+}  // namespace
+
+void gather_rows(Stream& st, float* out, const float* table, const int* idx, int R, int D) {
+  if (R == 0) return;
+  k_gather_rows<<<blocks_for(size_t(R) * (D / 4), 256), 256, 0, st.s>>>(out, table, idx, R, D / 4);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void compress0(Stream& st, float* out, float* pre, const float* b, const float* tab, const float* wx, const PackedEdges& pk,
+               int D) {
+  if (pk.E == 0) return;
+  GemmArgs p;
+  p.M = pk.E, p.N = D, p.C = out, p.ldc = D, p.pre = pre, p.ldp = D, p.bias = b, p.tab = tab, p.wx = wx, p.sp = pk.species;
+  p.vec = pk.vec, p.dist = pk.dist, p.epi = EPI_COMPRESS;
+  k_compress0<<<blocks_for(size_t(pk.E) * (D / 4), 256), 256, 0, st.s>>>(p);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void norm_fwd(Stream& st, float* out, float* in, const float* add, const float* w, const float* bias, int R, int D) {
+  if (R == 0) return;
+  k_norm_fwd<<<blocks_for(size_t(R) * 32, 256), 256, 0, st.s>>>(out, in, add, w, bias, R, D);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void concat_norm_fwd(Stream& st, float* out, const float* oe, const int* rev, float* ie, const float* w, const float* bias,
+                     int E, int D) {
+  if (E == 0) return;
+  k_concat_norm_fwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(out, oe, rev, ie, w, bias, E, D);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void norm_bwd(Stream& st, float* in_adj, const float* out_adj, const float* in, const float* w, bool layernorm, int R, int D,
+              int acc_row0, float* also) {
+  if (R == 0) return;
+  k_norm_bwd<<<blocks_for(size_t(R) * 32, 256), 256, 0, st.s>>>(in_adj, out_adj, in, w, layernorm, R, D, acc_row0, also);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void concat_norm_bwd(Stream& st, float* edge_adj, const float* out_adj, const float* oe, const int* rev, const float* ie_adj,
+                     const float* w, int E, int D) {
+  if (E == 0) return;
+  k_concat_norm_bwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E, D);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void compress_geometry_bwd(Stream& st, float* x4_adj, const float* g, const float* wx, int E, int D) {
+  if (E == 0) return;
+  k_compress_geometry_bwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(x4_adj, g, wx, E, D);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void readout_energy(Stream& st, float* net, double* per_atom, const float* node_pred, const float* edge_pred,
+                    const PackedEdges& pk, const double* composition, double scale, bool acc, bool assemble) {
+  if (pk.N == 0) return;
+  k_readout_energy<<<blocks_for(size_t(pk.N) * 32, 256), 256, 0, st.s>>>(net, per_atom, node_pred, edge_pred, pk, composition,
+                                                                        scale, acc, assemble);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void readout_seed_bwd(Stream& st, float* out, const float* w, const float* pre, const float* cut, const int* center,
+                      int n_local, int R, int Dh) {
+  if (R == 0) return;
+  k_readout_seed_bwd<<<blocks_for(size_t(R) * (Dh / 4), 256), 256, 0, st.s>>>(out, w, pre, cut, center, n_local, R, Dh / 4);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void cutoff_share(Stream& st, float* cf_adj, const float* cfh, const float* cut, int N, int E, int H) {
+  if (E == 0) return;
+  k_cutoff_share<<<blocks_for(E, 256), 256, 0, st.s>>>(cf_adj, cfh, cut, N, E, H);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void add_inplace(Stream& st, float* a, const float* b, size_t n) {
+  if (n == 0) return;
+  k_add_inplace<<<blocks_for(n / 4, 256), 256, 0, st.s>>>(a, b, n / 4);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void message_average(Stream& st, float* ie, const float* oe, const int* rev, int E, int D) {
+  if (E == 0) return;
+  k_message_average<<<blocks_for(size_t(E) * (D / 4), 256), 256, 0, st.s>>>(ie, oe, rev, E, D / 4);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void message_average_bwd(Stream& st, float* ie_adj_out, float* oe_adj, const float* ie_adj_in, const int* rev, int E, int D) {
+  if (E == 0) return;
+  k_message_average_bwd<<<blocks_for(size_t(E) * (D / 4), 256), 256, 0, st.s>>>(ie_adj_out, oe_adj, ie_adj_in, rev, E, D / 4);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void forces_and_virial(Stream& st, const ForceOut& out, const PackedEdges& pk, const float* x4_adj, const float* cutoff_adj,
+                       const float* cf_adj, const CutoffSpec& cs, double scale) {
+  if (pk.E > 0) {
+    k_edge_grad<<<blocks_for(pk.E, 256), 256, 0, st.s>>>(out.edge_grad, pk, x4_adj, cutoff_adj, cf_adj, cs);
+    PETB_LAUNCH_CHECK(st);
+  }
+  if (pk.n_atoms > 0) {
+    k_fold_forces<<<blocks_for(size_t(pk.n_atoms) * 32, 256), 256, 0, st.s>>>(out, pk, scale);
+    PETB_LAUNCH_CHECK(st);
+  }
+  k_struct_sum<<<blocks_for(size_t(pk.B) * 9 * 32, 256), 256, 0, st.s>>>(out.vir9, out.vir_atom, pk.soff, pk.B, 9);
+  PETB_LAUNCH_CHECK(st);
+  k_voigt<<<blocks_for(pk.B, 128), 128, 0, st.s>>>(out.vir6, out.vir9, pk.B);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void structure_energy(Stream& st, double* energy, const double* per_atom, const int* soff, int B) {
+  k_struct_sum<<<blocks_for(size_t(B) * 32, 256), 256, 0, st.s>>>(energy, per_atom, soff, B, 1);
+  PETB_LAUNCH_CHECK(st);
+}
+
+}  // namespace petb
