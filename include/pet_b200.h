@@ -174,6 +174,20 @@ int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neig
 long long pet_kernel_launches(const pet_calc* c);
 double pet_last_device_ms(const pet_calc* c);
 
+/* Per-class device timing of evaluations (no counterpart in the reference's API; its
+ * kernels are timed through Kokkos Tools labels, tools/roofline.py:431-441).
+ * pet_profile(c, 1) starts bracketing launches with CUDA events on the calculator's
+ * stream, pet_profile(c, 0) stops; pet_profile_read synchronizes and returns, per
+ * kernel class, the brackets seen, their summed milliseconds and the algorithmic flops
+ * and bytes of the work inside them, then clears the record. */
+typedef struct pet_profile_entry {
+  char name[32];
+  int launches;
+  double ms, flops, bytes;
+} pet_profile_entry;
+int pet_profile(pet_calc* c, int enable);
+int pet_profile_read(pet_calc* c, pet_profile_entry* out, int capacity, int* n);
+
 /* Copies a named intermediate of the latest evaluation to the host as float32
  * (testing aid; names follow the reference's workspace keys). Returns the
  * element count through n; fails if the name is unknown or capacity is short. */

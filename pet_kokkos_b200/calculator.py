@@ -54,6 +54,11 @@ class PetTotals(C.Structure):
     _fields_ = [("energy", C.c_double), ("virial", C.c_double * 6)]
 
 
+class PetProfileEntry(C.Structure):
+    _fields_ = [("name", C.c_char * 32), ("launches", C.c_int), ("ms", C.c_double), ("flops", C.c_double),
+                ("bytes", C.c_double)]
+
+
 class PetRawEdges(C.Structure):
     _fields_ = [("capacity", C.c_int), ("n_edges", C.c_int), ("i", C.POINTER(C.c_int)), ("j", C.POINTER(C.c_int)),
                 ("shift", C.POINTER(C.c_int)), ("vec", C.POINTER(C.c_double)), ("dist", C.POINTER(C.c_double)),
@@ -85,6 +90,8 @@ SIGNATURES = {
     "pet_last_shapes": (C.c_int, [C.c_void_p, _P(C.c_int), _P(C.c_int), _P(C.c_int)]),
     "pet_kernel_launches": (C.c_longlong, [C.c_void_p]),
     "pet_last_device_ms": (C.c_double, [C.c_void_p]),
+    "pet_profile": (C.c_int, [C.c_void_p, C.c_int]),
+    "pet_profile_read": (C.c_int, [C.c_void_p, _P(PetProfileEntry), C.c_int, _P(C.c_int)]),
     "pet_debug_fetch": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_float), C.c_size_t, _P(C.c_size_t)]),
     "pet_gemm_host": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P(C.c_float), _P(C.c_float),
                                 _P(C.c_float)]),
@@ -370,6 +377,18 @@ class Calculator:
                 continue
             self._check(rc)
             return {k: v[:re.n_edges] for k, v in out.items()}
+
+    # ---- per-class device timing ----
+    def profile(self, enable=True):
+        self._check(self._lib.pet_profile(self._h, int(enable)))
+
+    def profile_read(self):
+        """{class: dict(launches, ms, flops, bytes)} since the last read."""
+        arr = (PetProfileEntry * 16)()
+        n = C.c_int()
+        self._check(self._lib.pet_profile_read(self._h, arr, 16, C.byref(n)))
+        return {arr[i].name.decode(): dict(launches=arr[i].launches, ms=arr[i].ms, flops=arr[i].flops, bytes=arr[i].bytes)
+                for i in range(n.value)}
 
     # ---- testing aids ----
     def enable_taps(self):

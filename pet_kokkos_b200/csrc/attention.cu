@@ -221,6 +221,10 @@ void bwd_hd(Stream& st, const AttnArgs& p) {
 
 void attention_forward(Stream& st, const AttnArgs& p) {
   if (p.N == 0) return;
+  // The reference's own count (tools/roofline.py:188-202): 4 sum(cnt^2) D flops forward, 10 backward;
+  // qkv read and the output written once.
+  const double D = double(p.H) * p.hd;
+  const ProfScope ps(st, PC_ATTN_FWD, 4.0 * p.pairs * D, 4.0 * p.T * (4.0 * D + 2.0 * p.H));
   switch (p.hd) {
     case 16: return fwd_hd<16>(st, p);
     case 32: return fwd_hd<32>(st, p);
@@ -234,6 +238,8 @@ void attention_forward(Stream& st, const AttnArgs& p) {
 
 void attention_backward(Stream& st, const AttnArgs& p) {
   if (p.N == 0) return;
+  const double D = double(p.H) * p.hd;
+  const ProfScope ps(st, PC_ATTN_BWD, 10.0 * p.pairs * D, 4.0 * p.T * (8.0 * D + 3.0 * p.H));
   switch (p.hd) {
     case 16: return bwd_hd<16>(st, p);
     case 32: return bwd_hd<32>(st, p);

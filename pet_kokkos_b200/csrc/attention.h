@@ -8,6 +8,8 @@ namespace petb {
 struct AttnArgs {
   int N = 0, H = 0, hd = 0, S = 0;  // atoms, heads, head_dim, most tokens of any atom (max neighbours + 1)
   float sc = 1.f;                   // 1 / (sqrt(head_dim) * temperature)
+  double pairs = 0.0;               // sum over atoms of tokens^2 (work accounting only)
+  double T = 0.0;                   // token rows (work accounting only)
   const int* off = nullptr;         // [N+1] each atom's range of edge rows
   const float* cut = nullptr;       // [E] cutoff factor of each edge token
   const float* qkv = nullptr;       // [T,3D] columns Q | K | V

@@ -134,6 +134,38 @@ int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neig
 long long pet_kernel_launches(const pet_calc* c) { return c && c->e ? c->e->st.launches : 0; }
 double pet_last_device_ms(const pet_calc* c) { return c && c->e ? c->e->last_ms : 0.0; }
 
+int pet_profile(pet_calc* c, int enable) {
+  return guarded(c, [&](Engine& e) {
+    e.st.prof = &e.prof;
+    e.prof.on = enable != 0;
+  });
+}
+int pet_profile_read(pet_calc* c, pet_profile_entry* out, int capacity, int* n) {
+  return guarded(c, [&](Engine& e) {
+    PETB_CUDA(cudaSetDevice(e.device));
+    PETB_CUDA(cudaStreamSynchronize(e.st.s));
+    pet_profile_entry acc[petb::PC_COUNT] = {};
+    for (auto& r : e.prof.recs) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, r.a, r.b);
+      pet_profile_entry& a = acc[r.cls];
+      a.launches += 1, a.ms += ms, a.flops += r.flops, a.bytes += r.bytes;
+      e.prof.pool.push_back(r.a), e.prof.pool.push_back(r.b);
+    }
+    e.prof.recs.clear();
+    int k = 0;
+    for (int cls = 0; cls < petb::PC_COUNT; ++cls) {
+      if (!acc[cls].launches) continue;
+      if (out && k < capacity) {
+        out[k] = acc[cls];
+        snprintf(out[k].name, sizeof(out[k].name), "%s", petb::prof_class_name(cls));
+      }
+      ++k;
+    }
+    if (n) *n = k;
+  });
+}
+
 int pet_debug_fetch(pet_calc* c, const char* name, float* out, size_t capacity, size_t* n) {
   return guarded(c, [&](Engine& e) {
     if (!e.want_taps) {

@@ -127,10 +127,63 @@ class Arena {
   uint64_t generation_ = 0;
 };
 
+// Kernel classes for the per-class timing a profiling pass collects; the names are
+// the classes the reference's own roofline model reports (tools/roofline.md:16-24).
+enum ProfClass { PC_GEMM = 0, PC_ATTN_FWD, PC_ATTN_BWD, PC_NORM, PC_ELEMENTWISE, PC_GATHER, PC_GEOMETRY, PC_FORCES, PC_COUNT };
+inline const char* prof_class_name(int c) {
+  static const char* names[] = {"gemm", "attention_fwd", "attention_bwd", "norm", "elementwise", "gather", "geometry", "forces"};
+  return c >= 0 && c < PC_COUNT ? names[c] : "?";
+}
+
+// CUDA-event brackets around launches, on the launching stream, summed per class after a
+// synchronize. Off by default: an evaluation records nothing unless a profiling pass asked.
+struct Profiler {
+  struct Rec {
+    cudaEvent_t a, b;
+    int cls;
+    double flops, bytes;
+  };
+  bool on = false;
+  std::vector<Rec> recs;
+  std::vector<cudaEvent_t> pool;
+  cudaEvent_t get() {
+    if (!pool.empty()) {
+      cudaEvent_t e = pool.back();
+      pool.pop_back();
+      return e;
+    }
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    return e;
+  }
+  ~Profiler() {
+    for (auto& r : recs) cudaEventDestroy(r.a), cudaEventDestroy(r.b);
+    for (auto e : pool) cudaEventDestroy(e);
+  }
+};
+
 // The stream every kernel of a calculator runs on, with a count of launches.
 struct Stream {
   cudaStream_t s = nullptr;
   long long launches = 0;
+  Profiler* prof = nullptr;
+};
+
+// Brackets the launches made in its lifetime; `flops` and `bytes` are the algorithmic work
+// of those launches (2MNK for a GEMM, the tensors an op must read and write once).
+struct ProfScope {
+  Stream& st;
+  int idx = -1;
+  ProfScope(Stream& s, int cls, double flops, double bytes) : st(s) {
+    if (!s.prof || !s.prof->on) return;
+    Profiler::Rec r{s.prof->get(), s.prof->get(), cls, flops, bytes};
+    cudaEventRecord(r.a, s.s);
+    s.prof->recs.push_back(r);
+    idx = int(s.prof->recs.size()) - 1;
+  }
+  ~ProfScope() {
+    if (idx >= 0) cudaEventRecord(st.prof->recs[idx].b, st.s);
+  }
 };
 
 #define PETB_LAUNCH_CHECK(st)                                     \

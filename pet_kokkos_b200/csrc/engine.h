@@ -58,6 +58,7 @@ struct Engine {
   int gemm_mode = 0;
   bool graphs = true;
   Stream st;
+  Profiler prof;
   Checkpoint ckpt;
   std::unique_ptr<Model> model;
   Arena geom_arena, nbr_arena, save_arena, tmp_arena, session_arena;

@@ -111,6 +111,13 @@ void gemm(Stream& st, Arena& arena, const GemmArgs& a, int mode) {
   if (a.M <= 0 || a.N <= 0) return;
   if (a.N % 4 || a.K % 4 || a.lda % 4 || a.ldb % 4 || a.ldc % 2)
     throw Error(2, "gemm: widths must be multiples of 4 (N=" + std::to_string(a.N) + ", K=" + std::to_string(a.K) + ")");
+  // Algorithmic work: 2MNK flops; A, B, C once each, plus what the epilogue reads and writes.
+  double bytes = 4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.M) * a.N);
+  if (a.res) bytes += 4.0 * a.M * a.N;
+  if (a.pre) bytes += 4.0 * a.M * a.N * (a.epi == EPI_SWIGLU_BWD ? 2.0 : 1.0);
+  if (a.epi == EPI_SWIGLU) bytes -= 2.0 * a.M * a.N;      // h is half as wide as the product
+  if (a.epi == EPI_SWIGLU_BWD) bytes += 4.0 * a.M * a.N;  // pre_adj is twice as wide
+  const ProfScope ps(st, PC_GEMM, 2.0 * a.M * a.N * a.K, bytes);
   if (mode != GEMM_NATIVE && gemm_tensor_usable(a, mode)) return gemm_tensor(st, arena, a, mode);
   switch (a.epi) {
     case EPI_PLAIN: return launch_native<EPI_PLAIN>(st, a);
@@ -125,6 +132,7 @@ void gemm(Stream& st, Arena& arena, const GemmArgs& a, int mode) {
 
 void gemv_rows(Stream& st, const float* A, int lda, const float* w, const float* bias, float* out, int M, int K) {
   if (M <= 0) return;
+  const ProfScope ps(st, PC_GEMM, 2.0 * M * K, 4.0 * (double(M) * K + K + M));
   k_gemv_rows<<<cdiv((long long) M * 32, 256), 256, 0, st.s>>>(A, lda, w, bias, out, M, K);
   PETB_LAUNCH_CHECK(st);
 }

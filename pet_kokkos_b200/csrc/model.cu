@@ -331,6 +331,7 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
       }
       AttnArgs at;
       at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+      at.pairs = pk.pairs, at.T = T;
       at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml;
       attention_forward(st, at);
       tap(taps, "merged" + tag, b.merged, size_t(T) * D);
@@ -470,6 +471,7 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
         gm.linear_bwd(dmerged, tok_adj, mat(tl + ".attention.output_linear.weight"), T, false);
         AttnArgs at;
         at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+        at.pairs = pk.pairs, at.T = T;
         at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml, at.dmerged = dmerged, at.qkv_adj = qkv_adj, at.cfh = cfh;
         attention_backward(st, at);
         cutoff_share(st, cf_adj, cfh, pk.cut, N, E, H);

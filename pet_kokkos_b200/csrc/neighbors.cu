@@ -348,7 +348,7 @@ __device__ inline double cutoff_value(double d, double rc, double width, int kin
 
 // One warp per centre atom: its kept-edge count (d <= rc), and the largest count.
 __global__ void k_keep_count(int NC, const int* __restrict__ roff, const double* __restrict__ dist, double rc,
-                             int* __restrict__ kcnt, int* __restrict__ maxm) {
+                             int* __restrict__ kcnt, int* __restrict__ maxm, unsigned long long* __restrict__ pairs) {
   const int a = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (a >= NC) return;
   int c = 0;
@@ -358,6 +358,7 @@ __global__ void k_keep_count(int NC, const int* __restrict__ roff, const double*
   if (lane == 0) {
     kcnt[a] = c;
     atomicMax(maxm, c);
+    atomicAdd(pairs, (unsigned long long) (c + 1) * (unsigned long long) (c + 1));  // tokens^2, an integer sum
   }
 }
 
@@ -408,6 +409,8 @@ void wrap_positions(Stream& st, const Geom& g, double* posw) {
 
 RawEdges cell_list_search(Stream& st, Arena& arena, const Geom& g, const double* posw, double cutoff) {
   const int N = g.Ntot, nbins = g.nbins > 0 ? g.nbins : 1;
+  // 52 bytes per raw edge and 56 per atom: the reference's own count (tools/roofline.py:308-309).
+  const ProfScope ps(st, PC_GEOMETRY, 0.0, 56.0 * N);
   RawEdges re;
   re.off = arena.alloc<int>(N + 1);
   if (N == 0) {
@@ -454,6 +457,7 @@ RawEdges cell_list_search(Stream& st, Arena& arena, const Geom& g, const double*
 
 void find_reverse(Stream& st, const RawEdges& re, int) {
   if (re.E == 0) return;
+  const ProfScope ps(st, PC_GEOMETRY, 0.0, 52.0 * re.E);
   k_reverse<<<cdiv(re.E, 256), 256, 0, st.s>>>(re);
   PETB_LAUNCH_CHECK(st);
 }
@@ -470,19 +474,24 @@ PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int NC, con
   pk.N = NC;
   pk.atom_species = atom_species;
   pk.off = arena.alloc<int>(NC + 1);
-  int* kcnt = arena.alloc<int>(NC + 1);
+  const ProfScope ps(st, PC_GEOMETRY, 0.0, 60.0 * double(re.E) + 8.0 * NC);
+  int* kcnt = arena.alloc<int>(NC + 4);
   int* maxm = kcnt + NC;
+  unsigned long long* pairs = reinterpret_cast<unsigned long long*>(arena.alloc_bytes(8));
   PETB_CUDA(cudaMemsetAsync(maxm, 0, sizeof(int), st.s));
+  PETB_CUDA(cudaMemsetAsync(pairs, 0, 8, st.s));
   if (NC > 0) {
-    k_keep_count<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re.off, re.dist, cs.cutoff, kcnt, maxm);
+    k_keep_count<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re.off, re.dist, cs.cutoff, kcnt, maxm, pairs);
     PETB_LAUNCH_CHECK(st);
   }
   exclusive_scan(st, arena, kcnt, pk.off, NC);
   PETB_CUDA(cudaMemcpyAsync(pinned, pk.off + NC, sizeof(int), cudaMemcpyDeviceToHost, st.s));
   PETB_CUDA(cudaMemcpyAsync(pinned + 1, maxm, sizeof(int), cudaMemcpyDeviceToHost, st.s));
+  PETB_CUDA(cudaMemcpyAsync(pinned + 2, pairs, 8, cudaMemcpyDeviceToHost, st.s));
   PETB_CUDA(cudaStreamSynchronize(st.s));
   pk.E = pinned[0];
   pk.M = pinned[1] > 1 ? pinned[1] : 1;
+  pk.pairs = double(*reinterpret_cast<unsigned long long*>(pinned + 2));
   const size_t Ea = pk.E > 0 ? pk.E : 1, Er = re.E > 0 ? re.E : 1;
   pk.center = arena.alloc<int>(Ea);
   pk.nbr = arena.alloc<int>(Ea);

@@ -50,6 +50,7 @@ struct PackedEdges {
   int E = 0;          // kept edges
   int M = 0;          // most kept edges of any atom
   int B = 1;          // structures
+  double pairs = 0.0; // sum over centre atoms of (kept edges + 1)^2: the attention's pair count
   int* off = nullptr;       // [N+1]
   int* center = nullptr;    // [E]
   int* nbr = nullptr;       // [E] neighbour atom

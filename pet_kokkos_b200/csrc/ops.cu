@@ -345,6 +345,7 @@ inline unsigned blocks_for(size_t n, int per) { return (unsigned) ((n + per - 1)
 
 void gather_rows(Stream& st, float* out, const float* table, const int* idx, int R, int D) {
   if (R == 0) return;
+  const ProfScope ps(st, PC_GATHER, 0.0, 8.0 * double(R) * D);
   k_gather_rows<<<blocks_for(size_t(R) * (D / 4), 256), 256, 0, st.s>>>(out, table, idx, R, D / 4);
   PETB_LAUNCH_CHECK(st);
 }
@@ -352,6 +353,7 @@ void gather_rows(Stream& st, float* out, const float* table, const int* idx, int
 void compress0(Stream& st, float* out, float* pre, const float* b, const float* tab, const float* wx, const PackedEdges& pk,
                int D) {
   if (pk.E == 0) return;
+  const ProfScope ps(st, PC_ELEMENTWISE, 12.0 * double(pk.E) * D, 8.0 * double(pk.E) * D);
   GemmArgs p;
   p.M = pk.E, p.N = D, p.C = out, p.ldc = D, p.pre = pre, p.ldp = D, p.bias = b, p.tab = tab, p.wx = wx, p.sp = pk.species;
   p.vec = pk.vec, p.dist = pk.dist, p.epi = EPI_COMPRESS;
@@ -361,6 +363,7 @@ void compress0(Stream& st, float* out, float* pre, const float* b, const float* 
 
 void norm_fwd(Stream& st, float* out, float* in, const float* add, const float* w, const float* bias, int R, int D) {
   if (R == 0) return;
+  const ProfScope ps(st, PC_NORM, 6.0 * double(R) * D, (add ? 16.0 : 8.0) * double(R) * D);
   k_norm_fwd<<<blocks_for(size_t(R) * 32, 256), 256, 0, st.s>>>(out, in, add, w, bias, R, D);
   PETB_LAUNCH_CHECK(st);
 }
@@ -368,6 +371,7 @@ void norm_fwd(Stream& st, float* out, float* in, const float* add, const float* 
 void concat_norm_fwd(Stream& st, float* out, const float* oe, const int* rev, float* ie, const float* w, const float* bias,
                      int E, int D) {
   if (E == 0) return;
+  const ProfScope ps(st, PC_NORM, 12.0 * double(E) * D, 24.0 * double(E) * D);
   k_concat_norm_fwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(out, oe, rev, ie, w, bias, E, D);
   PETB_LAUNCH_CHECK(st);
 }
@@ -375,6 +379,7 @@ void concat_norm_fwd(Stream& st, float* out, const float* oe, const int* rev, fl
 void norm_bwd(Stream& st, float* in_adj, const float* out_adj, const float* in, const float* w, bool layernorm, int R, int D,
               int acc_row0, float* also) {
   if (R == 0) return;
+  const ProfScope ps(st, PC_NORM, 10.0 * double(R) * D, (acc_row0 < R ? 16.0 : 12.0) * double(R) * D);
   k_norm_bwd<<<blocks_for(size_t(R) * 32, 256), 256, 0, st.s>>>(in_adj, out_adj, in, w, layernorm, R, D, acc_row0, also);
   PETB_LAUNCH_CHECK(st);
 }
@@ -382,12 +387,14 @@ void norm_bwd(Stream& st, float* in_adj, const float* out_adj, const float* in, 
 void concat_norm_bwd(Stream& st, float* edge_adj, const float* out_adj, const float* oe, const int* rev, const float* ie_adj,
                      const float* w, int E, int D) {
   if (E == 0) return;
+  const ProfScope ps(st, PC_NORM, 20.0 * double(E) * D, 24.0 * double(E) * D);
   k_concat_norm_bwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E, D);
   PETB_LAUNCH_CHECK(st);
 }
 
 void compress_geometry_bwd(Stream& st, float* x4_adj, const float* g, const float* wx, int E, int D) {
   if (E == 0) return;
+  const ProfScope ps(st, PC_ELEMENTWISE, 8.0 * double(E) * D, 4.0 * double(E) * D);
   k_compress_geometry_bwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(x4_adj, g, wx, E, D);
   PETB_LAUNCH_CHECK(st);
 }
@@ -395,6 +402,7 @@ void compress_geometry_bwd(Stream& st, float* x4_adj, const float* g, const floa
 void readout_energy(Stream& st, float* net, double* per_atom, const float* node_pred, const float* edge_pred,
                     const PackedEdges& pk, const double* composition, double scale, bool acc, bool assemble) {
   if (pk.N == 0) return;
+  const ProfScope ps(st, PC_GATHER, 2.0 * pk.E, 8.0 * double(pk.E) + 16.0 * pk.N);
   k_readout_energy<<<blocks_for(size_t(pk.N) * 32, 256), 256, 0, st.s>>>(net, per_atom, node_pred, edge_pred, pk, composition,
                                                                         scale, acc, assemble);
   PETB_LAUNCH_CHECK(st);
@@ -403,36 +411,42 @@ void readout_energy(Stream& st, float* net, double* per_atom, const float* node_
 void readout_seed_bwd(Stream& st, float* out, const float* w, const float* pre, const float* cut, const int* center,
                       int n_local, int R, int Dh) {
   if (R == 0) return;
+  const ProfScope ps(st, PC_ELEMENTWISE, 8.0 * double(R) * Dh, 8.0 * double(R) * Dh);
   k_readout_seed_bwd<<<blocks_for(size_t(R) * (Dh / 4), 256), 256, 0, st.s>>>(out, w, pre, cut, center, n_local, R, Dh / 4);
   PETB_LAUNCH_CHECK(st);
 }
 
 void cutoff_share(Stream& st, float* cf_adj, const float* cfh, const float* cut, int N, int E, int H) {
   if (E == 0) return;
+  const ProfScope ps(st, PC_ELEMENTWISE, double(E) * H, 4.0 * double(E) * (H + 2));
   k_cutoff_share<<<blocks_for(E, 256), 256, 0, st.s>>>(cf_adj, cfh, cut, N, E, H);
   PETB_LAUNCH_CHECK(st);
 }
 
 void add_inplace(Stream& st, float* a, const float* b, size_t n) {
   if (n == 0) return;
+  const ProfScope ps(st, PC_ELEMENTWISE, double(n), 12.0 * double(n));
   k_add_inplace<<<blocks_for(n / 4, 256), 256, 0, st.s>>>(a, b, n / 4);
   PETB_LAUNCH_CHECK(st);
 }
 
 void message_average(Stream& st, float* ie, const float* oe, const int* rev, int E, int D) {
   if (E == 0) return;
+  const ProfScope ps(st, PC_GATHER, 2.0 * double(E) * D, 12.0 * double(E) * D);
   k_message_average<<<blocks_for(size_t(E) * (D / 4), 256), 256, 0, st.s>>>(ie, oe, rev, E, D / 4);
   PETB_LAUNCH_CHECK(st);
 }
 
 void message_average_bwd(Stream& st, float* ie_adj_out, float* oe_adj, const float* ie_adj_in, const int* rev, int E, int D) {
   if (E == 0) return;
+  const ProfScope ps(st, PC_GATHER, 2.0 * double(E) * D, 20.0 * double(E) * D);
   k_message_average_bwd<<<blocks_for(size_t(E) * (D / 4), 256), 256, 0, st.s>>>(ie_adj_out, oe_adj, ie_adj_in, rev, E, D / 4);
   PETB_LAUNCH_CHECK(st);
 }
 
 void forces_and_virial(Stream& st, const ForceOut& out, const PackedEdges& pk, const float* x4_adj, const float* cutoff_adj,
                        const float* cf_adj, const CutoffSpec& cs, double scale) {
+  const ProfScope ps(st, PC_FORCES, 40.0 * pk.E, 100.0 * double(pk.E) + 96.0 * pk.n_atoms);
   if (pk.E > 0) {
     k_edge_grad<<<blocks_for(pk.E, 256), 256, 0, st.s>>>(out.edge_grad, pk, x4_adj, cutoff_adj, cf_adj, cs);
     PETB_LAUNCH_CHECK(st);
@@ -448,6 +462,7 @@ void forces_and_virial(Stream& st, const ForceOut& out, const PackedEdges& pk, c
 }
 
 void structure_energy(Stream& st, double* energy, const double* per_atom, const int* soff, int B) {
+  const ProfScope ps(st, PC_FORCES, 0.0, 8.0 * B);
   k_struct_sum<<<blocks_for(size_t(B) * 32, 256), 256, 0, st.s>>>(energy, per_atom, soff, B, 1);
   PETB_LAUNCH_CHECK(st);
 }

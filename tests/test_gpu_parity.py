@@ -1,0 +1,133 @@
+"""Energy, forces and virial of the CUDA path against the CPU oracle and the committed goldens.
+
+Tolerances (the north star's): energies 1e-6 relative, forces 1e-5 eV/A, virial
+1e-5 relative to the virial's scale (the reference's own path-agreement tests use
+1e-5 relative, tests/test_cell_list.cpp:186-189), all against the float64 oracle;
+fp32 rounding of either fp32 path is inside those bands.
+"""
+import copy
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pet_oracle as po
+from pet_kokkos_b200 import checkpoint as ck, structures as st
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+sys.path.insert(0, str(GOLDEN))
+import make_golden  # noqa: E402
+
+E_REL, F_ABS, W_REL = 1e-6, 1e-5, 1e-5
+
+
+def check(r, ref, f_abs=F_ABS):
+    assert np.abs(r.energy - ref["energy"]).max() <= E_REL * np.abs(ref["energy"]).max()
+    assert np.abs(r.per_atom_energy - ref["per_atom_energy"]).max() <= E_REL * np.abs(ref["energy"]).max()
+    assert np.abs(r.forces - ref["forces"]).max() <= f_abs
+    assert np.abs(r.virial - ref["virial"]).max() <= W_REL * max(1.0, np.abs(ref["virial"]).max())
+
+
+@pytest.mark.parametrize("name", sorted(make_golden.CASES))
+def test_goldens(name, tmp_path, lib_path):
+    from pet_kokkos_b200 import Calculator
+    if "res" in name:
+        pytest.importorskip("pet_kokkos_b200")
+    g = np.load(GOLDEN / f"{name}.npz")
+    jp, sp, meta, tens, systems = make_golden.build_case(name, tmp_path)
+    assert make_golden.weights_digest(tens) == str(g["digest"])
+    c = Calculator(jp, sp)
+    r = c.compute(systems)
+    # forces here are O(10) eV/A for the "scaled" models: the absolute band is scaled accordingly
+    scale = max(1.0, np.abs(g["forces"]).max())
+    check(r, {k: g[k] for k in ("energy", "per_atom_energy", "forces", "virial")}, f_abs=F_ABS * scale)
+    assert c.last_shapes()[1] == int(g["n_edges"]) and c.last_shapes()[2] == int(g["max_neighbors"])
+    c.close()
+
+
+@pytest.mark.parametrize("shape,workload", [("xs", "diamond64"), ("s", "water648"), ("s", "diamond1728")])
+def test_benchmark_configs_match_oracle(models, lib_path, shape, workload):
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models(shape)
+    meta, tens = ck.load_checkpoint(jp, sp)
+    systems = st.workload(workload)
+    ref = po.evaluate(meta, tens, systems, dtype=torch.float64)
+    c = Calculator(jp, sp)
+    r = c.compute(systems)
+    check(r, ref)
+    assert np.abs(r.forces).max() > 100 * F_ABS, "the force tolerance must bite"
+    c.close()
+
+
+def test_bit_identical_repeats_and_batch_independence(models, lib_path):
+    """tests/test_determinism.cpp:42-63,350-380: same bits run to run, and in a batch as alone (native GEMMs)."""
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("xs"))
+    a, b = st.diamond(2, jitter=0.05, seed=0), st.random_mixture(64, 9.0, seed=3)
+    r1, r2 = c.compute([a, b]), c.compute([a, b])
+    for k in ("energy", "forces", "virial", "per_atom_energy"):
+        assert (getattr(r1, k) == getattr(r2, k)).all()
+    ra, rb = c.compute(a), c.compute(b)
+    assert (r1.energy == np.concatenate([ra.energy, rb.energy])).all()
+    assert (r1.forces == np.concatenate([ra.forces, rb.forces])).all()
+    assert (r1.virial == np.concatenate([ra.virial, rb.virial])).all()
+    c.close()
+
+
+def test_forces_match_finite_differences_on_device(models, lib_path):
+    """tests/test_fd.cpp:61-112 on the CUDA path: analytic forces against central differences of its own energies."""
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("tiny", "feedforward", "scaled", 1))
+    s = st.diamond(2, jitter=0.05, seed=0)
+    F = c.compute(s).forces
+    h = 1e-2  # fp32 energies: a large step, as the reference's sweep starts with
+    for i, comp in [(0, 0), (17, 2), (40, 1)]:
+        sp, sm = copy.deepcopy(s), copy.deepcopy(s)
+        sp["positions"][i, comp] += h
+        sm["positions"][i, comp] -= h
+        fd = -(c.compute(sp, False).energy[0] - c.compute(sm, False).energy[0]) / (2 * h)
+        assert abs(fd - F[i, comp]) <= 3e-3 * max(1.0, abs(fd))
+    c.close()
+
+
+def test_energy_only_equals_energy_with_forces(models, lib_path):
+    """tests/test_golden.cpp:188-204: the forward alone gives the same energy bits."""
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("xs"))
+    s = st.diamond(2, jitter=0.05, seed=0)
+    assert (c.compute(s, False).energy == c.compute(s, True).energy).all()
+    c.close()
+
+
+def test_full_size_properties(models, lib_path):
+    """At the benchmark's size: momentum conservation and invariance under a lattice translation and an atom permutation."""
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("s"))
+    s = st.workload("diamond1728")[0]
+    r = c.compute(s)
+    assert np.abs(r.forces.sum(0)).max() <= 1e-5 * len(r.forces) ** 0.5
+    moved = copy.deepcopy(s)
+    moved["positions"] = s["positions"] + s["cell"][0] * 2 - s["cell"][2]
+    r2 = c.compute(moved)
+    assert abs(r2.energy[0] - r.energy[0]) <= E_REL * abs(r.energy[0])
+    assert np.abs(r2.forces - r.forces).max() <= F_ABS
+    perm = np.random.default_rng(0).permutation(s["n_atoms"])
+    ps = st.make_system(s["atomic_numbers"][perm], s["positions"][perm], s["cell"])
+    r3 = c.compute(ps)
+    assert abs(r3.energy[0] - r.energy[0]) <= E_REL * abs(r.energy[0])
+    assert np.abs(r3.forces - r.forces[perm]).max() <= F_ABS
+    c.close()
+
+
+def test_errors_are_reported(models, lib_path):
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("tiny"))
+    bad = st.make_system([200], [[0, 0, 0]], np.eye(3) * 10)
+    with pytest.raises(RuntimeError, match="unsupported atomic number"):
+        c.compute(bad)
+    r = c.compute(st.diamond(1))  # still usable afterwards
+    assert np.isfinite(r.energy).all()
+    c.close()
