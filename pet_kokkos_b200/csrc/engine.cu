@@ -269,6 +269,8 @@ void Engine::fetch(pet_results* out) {
   PETB_CUDA(cudaStreamSynchronize(st.s));
   float ms = 0.f;
   if (cudaEventElapsedTime(&ms, ev0, ev1) == cudaSuccess) last_ms = ms;
+  if (gemm_mode != GEMM_NATIVE && gemm_tensor_error(st))
+    throw Error(5, "pet: a tensor-core GEMM gave up waiting on its pipeline; the results of this evaluation are invalid");
 }
 
 void Engine::compute(const pet_system* systems, int B, bool forces, pet_results* out) {
@@ -527,6 +529,7 @@ void Engine::gemm_host(int mode, bool w_transposed, int m, int n, int k, const f
   gemm(st, tmp_arena, a, mode);
   PETB_CUDA(cudaMemcpyAsync(C, dC, 4 * size_t(m) * n, cudaMemcpyDeviceToHost, st.s));
   PETB_CUDA(cudaStreamSynchronize(st.s));
+  if (mode != GEMM_NATIVE && gemm_tensor_error(st)) throw Error(5, "pet: a tensor-core GEMM gave up waiting on its pipeline");
 }
 
 }  // namespace petb

@@ -60,6 +60,10 @@ void gemm(Stream& st, Arena& arena, const GemmArgs& a, int mode);
 // out[M] = A[M,K] . w[K] + b (a one-column linear layer), one warp per row.
 void gemv_rows(Stream& st, const float* A, int lda, const float* w, const float* bias, float* out, int M, int K);
 
+// Non-zero if a tensor-core kernel launched on this stream gave up on a bounded wait since the
+// last call (synchronizes the stream; clears the flag).
+int gemm_tensor_error(Stream& st);
+
 // True once the tensor-core path has been initialised on this device (driver entry point found).
 bool tensor_gemm_available();
 

@@ -1,8 +1,371 @@
-// Tensor-core GEMM path (placeholder until the tcgen05 kernel lands).
-#include "gemm.h"
+// The tensor-core GEMM: tcgen05.mma with TMA-fed shared-memory tiles and the accumulator in
+// tensor memory (sm_100a). See gemm.h for the interface and the epilogues.
+//
+// One CTA computes a 128 x BN tile of C = A . B^T (A [M,K], B [N,K], both K-major fp32):
+//   warp 0   producer: one thread issues cp.async.bulk.tensor (TMA) loads of a 128 x 32 slab of
+//            A and a BN x 32 slab of B per stage, 128-byte swizzled, completing on an mbarrier;
+//   warp 1   issuer: one thread issues tcgen05.mma kind::tf32 (M = 128, N = BN, K = 8) four times
+//            per stage, accumulating in tensor memory, and releases the stage with tcgen05.commit;
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (a thread owns a row), stage it through shared
+//            memory so that a warp then walks one row at a time with its lanes across columns,
+//            and run the fused epilogue with coalesced 16-byte accesses.
+// In the 3xTF32 mode the issuer's products are split: each fp32 operand x is used as
+// hi = its leading tf32 bits and lo = x - hi (made in shared memory by the epilogue warps while
+// they wait), and hi.hi + hi.lo + lo.hi accumulate in fp32 -- fp32-class accuracy on the tensor
+// cores without reading the operands from L2 a second time.
+// No TMA load here uses cluster multicast. Every wait is bounded: a wait that runs out sets an
+// error word the host checks, and the CTA still reaches its tensor-memory release.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "epilogue.cuh"
 
 namespace petb {
-bool gemm_tensor_usable(const GemmArgs&, int) { return false; }
-void gemm_tensor(Stream&, Arena&, const GemmArgs&, int) { throw Error(3, "gemm: tensor path not built"); }
-bool tensor_gemm_available() { return false; }
+
+namespace {
+
+constexpr int TBM = 128, TBK = 32;  // rows per tile; fp32 elements per 128-byte swizzled row
+constexpr unsigned long long kSpinLimit = 1ull << 31;  // clock64 ticks (~1 s) before a wait gives up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false once kSpinLimit clock ticks have passed or another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((unsigned long long) (clock64() - t0) > kSpinLimit) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address >> 4 in bits 0-13,
+// leading byte offset (unused for swizzled K-major: 1) in 16-29, stride byte offset (1024 B between
+// 8-row groups) >> 4 in 32-45, descriptor version 1 in 46-47, layout type 2 (SWIZZLE_128B) in 61-63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return uint64_t((addr & 0x3FFFF) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+         (uint64_t(2) << 61);
+}
+// Instruction descriptor, kind::tf32: D fp32 (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2), both
+// K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t idesc_tf32(int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(TBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN, int STAGES, bool X3>
+struct Smem {
+  static constexpr int kA = TBM * TBK * 4, kB = BN * TBK * 4;       // bytes per stage
+  static constexpr int kStage = (kA + kB) * (X3 ? 2 : 1);            // with the lo tiles in the 3x mode
+  static constexpr int kTiles = STAGES * kStage;
+  static constexpr int kStagePad = BN + 4;                            // floats per staged accumulator row
+  static constexpr int kEpi = TBM * kStagePad * 4;
+  static constexpr int kData = kTiles > kEpi ? kTiles : kEpi;
+  static constexpr int kTotal = kData + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int EPI, int BN, int STAGES, bool X3>
+__global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ CUtensorMap map_a,
+                                                     const __grid_constant__ CUtensorMap map_b, GemmArgs p, int* err) {
+  using L = Smem<BN, STAGES, X3>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::kData);  // [STAGES] TMA landed
+  uint64_t* empty = full + STAGES;                                 // [STAGES] MMAs of the stage done
+  uint64_t* split = empty + STAGES;                                // [STAGES] lo tiles written (3x mode)
+  uint64_t* accum = split + STAGES;                                // accumulator complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int m0 = (blockIdx.x / tiles_n) * TBM, n0 = (blockIdx.x % tiles_n) * BN;
+  const int nkb = (p.K + TBK - 1) / TBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+      mbar_init(split + s, 128);
+    }
+    mbar_init(accum, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // tensor memory for the accumulator: BN fp32 columns x 128 lanes
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(empty + s, ((kb / STAGES) - 1) & 1, abort_flag)) break;
+        uint8_t* sa = tiles + size_t(s) * L::kStage;
+        mbar_expect_tx(full + s, L::kA + L::kB);
+        tma_load_2d(sa, &map_a, full + s, kb * TBK, m0);
+        tma_load_2d(sa + L::kA, &map_b, full + s, kb * TBK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(BN);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (!mbar_wait(X3 ? split + s : full + s, ph, abort_flag)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(tiles + size_t(s) * L::kStage), b0 = a0 + L::kA;
+#pragma unroll
+        for (int k = 0; k < TBK / 8; ++k) {  // 8 tf32 = 32 bytes along K per instruction
+          const uint64_t da = smem_desc(a0 + 32 * k), db = smem_desc(b0 + 32 * k);
+          mma_tf32(tmem, da, db, idesc, (kb | k) != 0);
+          if (X3) {
+            const uint64_t dal = smem_desc(a0 + L::kA + L::kB + 32 * k), dbl = smem_desc(b0 + L::kA + L::kB + 32 * k);
+            mma_tf32(tmem, da, dbl, idesc, 1);
+            mma_tf32(tmem, dal, db, idesc, 1);
+          }
+        }
+        mma_commit(empty + s);
+      }
+      mma_commit(accum);
+    }
+  } else {
+    const int ew = warp - 2;  // 0..3
+    if (X3) {
+      // lo = x - (x with the 13 low mantissa bits cleared), written beside the stage's tiles in the same
+      // swizzled positions, so the same descriptors (offset by the stage's hi size) address them.
+      const int t = threadIdx.x - 64;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(full + s, (kb / STAGES) & 1, abort_flag)) break;
+        float4* hi = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage);
+        float4* lo = hi + (L::kA + L::kB) / 16;
+        for (int i = t; i < (L::kA + L::kB) / 16; i += 128) {
+          const float4 x = hi[i];
+          float4 y;
+          y.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+          y.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+          y.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+          y.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+          lo[i] = y;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes visible to the tensor core
+        mbar_arrive(split + s);
+      }
+    }
+    const bool ok = mbar_wait(accum, 0, abort_flag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float* stage = reinterpret_cast<float*>(tiles);
+    if (ok) {
+      // A warp may read the 32 lanes of its own quarter: warps 2,3,4,5 -> lanes 64-95, 96-127, 0-31, 32-63.
+      const int q = warp & 3, row = q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem + (uint32_t(q * 32) << 16) + c0, v);
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(stage + row * L::kStagePad + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (ok) {
+      for (int r = ew; r < TBM; r += 4) {
+        const int row = m0 + r;
+        if (row >= p.M) break;
+#pragma unroll
+        for (int c = lane * 4; c < BN; c += 128) {
+          const int col = n0 + c;
+          if (col < p.N) {
+            const float4 a = *reinterpret_cast<const float4*>(stage + r * L::kStagePad + c);
+            const float acc[4] = {a.x, a.y, a.z, a.w};
+            epilogue_run4<EPI>(p, row, col, acc);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(err, 1);
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct TensorState {
+  EncodeFn encode = nullptr;
+  int* err = nullptr;       // device error word
+  int* err_host = nullptr;  // pinned mirror
+  bool ok = false;
+};
+
+TensorState& state() {
+  static TensorState s;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return;
+    int dev = 0, major = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (major != 10) return;
+    if (cudaMalloc(&s.err, sizeof(int)) != cudaSuccess) return;
+    cudaMemset(s.err, 0, sizeof(int));
+    if (cudaMallocHost(&s.err_host, sizeof(int)) != cudaSuccess) return;
+    *s.err_host = 0;
+    s.encode = reinterpret_cast<EncodeFn>(fn);
+    s.ok = true;
+  });
+  return s;
+}
+
+// A [rows, K] fp32 row-major matrix as a 2-D tensor map with a 32 x box_rows box, 128-byte swizzle,
+// zero fill outside the matrix.
+CUtensorMap make_map(const float* base, int rows, int K, int ld, int box_rows) {
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(ld) * 4};
+  const cuuint32_t box[2] = {TBK, cuuint32_t(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = state().encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw Error(5, "gemm: cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+  return m;
+}
+
+template <int EPI, int BN, int STAGES, bool X3>
+void launch_tc(Stream& st, const GemmArgs& a) {
+  using L = Smem<BN, STAGES, X3>;
+  static bool opted = false;
+  auto kernel = k_gemm_tc<EPI, BN, STAGES, X3>;
+  if (!opted) {
+    PETB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    opted = true;
+  }
+  // TMA box rows are limited to 256; a box taller than the matrix is fine (rows past it read as zero).
+  const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM), mb = make_map(a.B, a.N, a.K, a.ldb, BN);
+  const long long tiles = (long long) cdiv(a.M, TBM) * cdiv(a.N, BN);
+  kernel<<<(unsigned) tiles, 192, L::kTotal, st.s>>>(ma, mb, a, state().err);
+  PETB_LAUNCH_CHECK(st);
+}
+
+template <int EPI>
+void dispatch_tc(Stream& st, const GemmArgs& a, int mode) {
+  const bool x3 = mode == GEMM_TF32X3;
+  if (a.N % 256 == 0) {
+    if (x3) return launch_tc<EPI, 256, 2, true>(st, a);
+    return launch_tc<EPI, 256, 4, false>(st, a);
+  }
+  if (x3) return launch_tc<EPI, 128, 3, true>(st, a);
+  return launch_tc<EPI, 128, 4, false>(st, a);
+}
+
+}  // namespace
+
+bool tensor_gemm_available() { return state().ok; }
+
+bool gemm_tensor_usable(const GemmArgs& a, int mode) {
+  if (mode != GEMM_TF32 && mode != GEMM_TF32X3 && mode != GEMM_BF16) return false;
+  if (!state().ok) return false;
+  // TMA: 16-byte aligned bases and row strides; the staged epilogue wants N % 4 == 0 (checked by gemm()).
+  if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B)) & 15) return false;
+  if (a.lda % 4 || a.ldb % 4 || a.K % 8) return false;
+  if (a.M < 64 || a.N < 32) return false;  // too small to be worth a 128-row tensor tile
+  return true;
+}
+
+void gemm_tensor(Stream& st, Arena&, const GemmArgs& a, int mode) {
+  if (mode == GEMM_BF16) mode = GEMM_TF32;  // operands are kept in fp32: the bf16 mode runs the tf32 kernel
+  switch (a.epi) {
+    case EPI_PLAIN: return dispatch_tc<EPI_PLAIN>(st, a, mode);
+    case EPI_SILU: return dispatch_tc<EPI_SILU>(st, a, mode);
+    case EPI_SWIGLU: return dispatch_tc<EPI_SWIGLU>(st, a, mode);
+    case EPI_SILU_BWD: return dispatch_tc<EPI_SILU_BWD>(st, a, mode);
+    case EPI_SWIGLU_BWD: return dispatch_tc<EPI_SWIGLU_BWD>(st, a, mode);
+    case EPI_COMPRESS: return dispatch_tc<EPI_COMPRESS>(st, a, mode);
+    default: throw Error(3, "gemm: unknown epilogue");
+  }
+}
+
+// Non-zero once a tensor-core kernel gave up on a wait; cleared by the read.
+int gemm_tensor_error(Stream& st) {
+  TensorState& s = state();
+  if (!s.ok) return 0;
+  cudaMemcpyAsync(s.err_host, s.err, sizeof(int), cudaMemcpyDeviceToHost, st.s);
+  cudaStreamSynchronize(st.s);
+  const int e = *s.err_host;
+  if (e) cudaMemsetAsync(s.err, 0, sizeof(int), st.s);
+  return e;
+}
+
 }  // namespace petb

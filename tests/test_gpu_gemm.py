@@ -1,0 +1,51 @@
+"""The weight GEMM in each mode against a float64 product (the reference's tests/test_gemm_modes.cpp:34-103)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def random_matrix(r, c, seed):
+    """Activation-like: unit normal entries, a few eight times larger (test_gemm_modes.cpp:34-44)."""
+    rng = np.random.default_rng(seed)
+    m = rng.normal(size=(r, c))
+    i, j = np.meshgrid(np.arange(r), np.arange(c), indexing="ij")
+    m[(i + j) % 97 == 0] *= 8.0
+    return m.astype(np.float32)
+
+
+def rel_error(C, A, W, transposed):
+    ref = A.astype(np.float64) @ (W.T if transposed else W).astype(np.float64)
+    return np.abs(C - ref).max() / np.abs(ref).max()
+
+
+@pytest.fixture(scope="module")
+def calc(lib_path, models):
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("tiny"))
+    yield c
+    c.close()
+
+
+@pytest.mark.parametrize("transposed", [True, False])
+@pytest.mark.parametrize("shape", [(300, 256, 192), (1000, 512, 1024), (129, 64, 40)])
+def test_mode_error_bands(calc, transposed, shape):
+    m, k, n = shape
+    A = random_matrix(m, k, 1)
+    W = random_matrix(n, k, 2) if transposed else random_matrix(k, n, 2)
+    native = rel_error(calc.gemm(A, W, "native", transposed), A, W, transposed)
+    tf32 = rel_error(calc.gemm(A, W, "tf32", transposed), A, W, transposed)
+    x3 = rel_error(calc.gemm(A, W, "3xtf32", transposed), A, W, transposed)
+    print(f"{shape} {'A W^T' if transposed else 'A W'}: native {native:.2e} tf32 {tf32:.2e} 3xtf32 {x3:.2e}")
+    assert native < 1e-6                      # test_gemm_modes.cpp:88
+    assert 10 * native < tf32 < 1e-2          # :89-90: as accurate as its precision, and no more
+    assert x3 < 2e-5 and x3 < tf32 / 20       # fp32-class: the split recovers the bits tf32 drops
+
+
+def test_native_rows_do_not_depend_on_the_batch(calc):
+    """A row's bits are the same whatever the number of rows (the reference's batch-invariant GEMMs)."""
+    A = random_matrix(700, 256, 3)
+    W = random_matrix(512, 256, 4)
+    full = calc.gemm(A, W, "native")
+    part = calc.gemm(A[:77], W, "native")
+    assert (full[:77] == part).all()
