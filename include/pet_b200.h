@@ -198,6 +198,22 @@ int pet_debug_fetch(pet_calc* c, const char* name, float* out, size_t capacity, 
  * tests/test_gemm_modes.cpp:63-103). */
 int pet_gemm_host(pet_calc* c, int mode, int w_transposed, int m, int n, int k, const float* A, const float* W, float* C);
 
+/* C[m,n] = A[m,k] . W^T, W [n,k], fp32 on the CUDA cores, on host arrays, WITHOUT allocating
+ * device memory. It has no counterpart in the reference. It exists for callers that cannot
+ * call cudaMalloc: plug-ins of a host program that owns all device memory through its own
+ * pool, code that runs while a stream of the process is being captured, loops that may not
+ * take the driver's allocation lock. Operands are staged in a fixed 12 MiB array inside the
+ * library image (resident on every GPU that loads the library until the process exits), on
+ * the current device and its default stream. Limits and rules:
+ *   - round64(m*k) + round64(n*k) + round64(m*n) floats must fit 3 Mi floats, n % 4 == 0 and
+ *     k % 4 == 0; a larger problem is refused with PET_ERR_INVALID and a message in errbuf;
+ *   - the first call on each device resolves the array's device address (cudaGetSymbolAddress):
+ *     make that first call before any stream capture starts;
+ *   - every call uses the same array, which keeps the previous call's contents (the kernel
+ *     overwrites all of C, so nothing needs clearing); calls that overlap on one GPU race.
+ * errbuf (optional) receives the message of a failure. */
+int pet_gemm_host_static(int m, int n, int k, const float* A, const float* W, float* C, char* errbuf, size_t errbuf_len);
+
 #ifdef __cplusplus
 }
 #endif

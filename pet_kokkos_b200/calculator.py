@@ -93,6 +93,8 @@ SIGNATURES = {
     "pet_profile": (C.c_int, [C.c_void_p, C.c_int]),
     "pet_profile_read": (C.c_int, [C.c_void_p, _P(PetProfileEntry), C.c_int, _P(C.c_int)]),
     "pet_debug_fetch": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_float), C.c_size_t, _P(C.c_size_t)]),
+    "pet_gemm_host_static": (C.c_int, [C.c_int, C.c_int, C.c_int, _P(C.c_float), _P(C.c_float), _P(C.c_float), C.c_char_p,
+                                       C.c_size_t]),
     "pet_gemm_host": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P(C.c_float), _P(C.c_float),
                                 _P(C.c_float)]),
 }
