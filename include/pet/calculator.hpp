@@ -1,0 +1,198 @@
+// A header-only C++ facade over the C ABI (pet_b200.h) with the names of the reference's
+// include/pet/calculator.hpp:32-319, so that a caller of pet::Calculator recompiles against it.
+// Status codes are rethrown as the exception types the reference throws.
+#pragma once
+
+#include <array>
+#include <new>
+#include <optional>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../pet_b200.h"
+
+namespace pet {
+
+enum class GemmMode { Native = PET_GEMM_NATIVE, TF32 = PET_GEMM_TF32, BF16 = PET_GEMM_BF16, TF32x3 = PET_GEMM_TF32X3 };
+
+// pet::System (the reference's include/pet/neighbors.hpp:15-25).
+struct System {
+  int n_atoms = 0;
+  std::vector<int> atomic_numbers;
+  std::vector<double> positions;
+  std::array<double, 9> cell{};
+  std::array<bool, 3> pbc{false, false, false};
+  int charge = 0;
+  int spin_multiplicity = 1;
+};
+
+// pet::Options (calculator.hpp:32-117): the fields this path uses.
+struct Options {
+  std::optional<GemmMode> gemm;
+  bool graphs = true;
+  bool md_fixed_shapes = false;
+  std::size_t memory_budget_bytes = 0;
+  int max_batch_atoms = 0;
+  int device = -1;
+};
+
+// pet::Results (calculator.hpp:120-142).
+struct Results {
+  std::vector<double> energy, per_atom_energy, forces, virial;
+  std::vector<int> struct_id, n_atoms;
+  std::vector<double> edge_gradient;
+};
+
+// pet::EdgeListView (the reference's include/pet/device_geometry.hpp:93-110).
+struct EdgeListView {
+  int n_atoms = 0, n_local = -1;
+  const double* positions = nullptr;
+  const int* atomic_numbers = nullptr;
+  const int* offsets = nullptr;
+  const int* neighbors = nullptr;
+  const int* shifts = nullptr;
+  const double* cell = nullptr;
+  bool half = false;
+};
+
+class Calculator {
+ public:
+  struct DeviceArrays {
+    const double* positions = nullptr;
+    double* forces = nullptr;
+    double* per_atom_energy = nullptr;
+    double* per_atom_virial = nullptr;
+    double virial_scale = 1.0;
+  };
+  struct Totals {
+    double energy = 0.0;
+    double virial[6] = {0, 0, 0, 0, 0, 0};
+  };
+
+  Calculator(const std::string& model_json, const std::string& model_weights, Options opts = {}) : opts_(opts) {
+    pet_options o{};
+    o.device = opts.device;
+    o.gemm_mode = opts.gemm ? int(*opts.gemm) : -1;
+    o.graphs = opts.graphs ? 1 : 0;
+    o.md_fixed_shapes = opts.md_fixed_shapes ? 1 : 0;
+    o.memory_budget_bytes = opts.memory_budget_bytes;
+    o.max_batch_atoms = opts.max_batch_atoms;
+    const int rc = pet_calc_create(model_json.c_str(), model_weights.c_str(), &o, &h_);
+    if (rc) raise(rc, pet_last_error(nullptr));
+  }
+  ~Calculator() { pet_calc_destroy(h_); }
+  Calculator(Calculator&& o) noexcept : h_(o.h_), opts_(o.opts_), pairs_(o.pairs_), atoms_(o.atoms_) { o.h_ = nullptr; }
+  Calculator& operator=(Calculator&& o) noexcept {
+    if (this != &o) {
+      pet_calc_destroy(h_);
+      h_ = o.h_, opts_ = o.opts_, pairs_ = o.pairs_, atoms_ = o.atoms_;
+      o.h_ = nullptr;
+    }
+    return *this;
+  }
+  Calculator(const Calculator&) = delete;
+  Calculator& operator=(const Calculator&) = delete;
+
+  Results compute(const System& system, bool compute_forces = true) const {
+    return compute(std::vector<System>{system}, compute_forces);
+  }
+  Results compute(const std::vector<System>& systems, bool compute_forces = true) const {
+    Results r;
+    if (systems.empty()) return r;
+    std::vector<pet_system> ps(systems.size());
+    std::size_t N = 0;
+    for (std::size_t b = 0; b < systems.size(); ++b) {
+      const System& s = systems[b];
+      ps[b].n_atoms = s.n_atoms;
+      ps[b].atomic_numbers = s.atomic_numbers.data();
+      ps[b].positions = s.positions.data();
+      for (int k = 0; k < 9; ++k) ps[b].cell[k] = s.cell[k];
+      for (int k = 0; k < 3; ++k) ps[b].pbc[k] = s.pbc[k];
+      ps[b].charge = s.charge, ps[b].spin_multiplicity = s.spin_multiplicity;
+      r.n_atoms.push_back(s.n_atoms);
+      N += std::size_t(s.n_atoms);
+    }
+    pet_results out = sized(r, systems.size(), N, compute_forces, 0);
+    check(pet_compute(h_, ps.data(), int(ps.size()), compute_forces, &out));
+    return r;
+  }
+  Results compute_edges(const EdgeListView& v, bool compute_forces = true, bool edge_gradients = true) const {
+    const pet_edge_list l = list(v);
+    atoms_ = v.n_atoms, pairs_ = v.n_atoms > 0 ? v.offsets[v.n_atoms] : 0;
+    Results r;
+    r.n_atoms = {v.n_atoms};
+    pet_results out = sized(r, 1, std::size_t(v.n_atoms), compute_forces, edge_gradients ? pairs_ : 0);
+    check(pet_compute_edges(h_, &l, compute_forces, edge_gradients, &out));
+    return r;
+  }
+  void set_neighbors(const EdgeListView& v) {
+    const pet_edge_list l = list(v);
+    check(pet_set_neighbors(h_, &l));
+    atoms_ = v.n_atoms, pairs_ = v.n_atoms > 0 ? v.offsets[v.n_atoms] : 0;
+  }
+  Results compute_step(const double* positions, const double* cell = nullptr, bool compute_forces = true,
+                       bool edge_gradients = false) const {
+    Results r;
+    r.n_atoms = {atoms_};
+    pet_results out = sized(r, 1, std::size_t(atoms_), compute_forces, edge_gradients ? pairs_ : 0);
+    check(pet_compute_step(h_, positions, cell, compute_forces, edge_gradients, &out));
+    return r;
+  }
+  Totals compute_step(const DeviceArrays& a, const double* cell = nullptr) const {
+    const pet_device_arrays d{a.positions, a.forces, a.per_atom_energy, a.per_atom_virial, a.virial_scale};
+    pet_totals t{};
+    check(pet_compute_step_device(h_, &d, cell, &t));
+    Totals out;
+    out.energy = t.energy;
+    for (int k = 0; k < 6; ++k) out.virial[k] = t.virial[k];
+    return out;
+  }
+
+  double cutoff() const { return pet_cutoff(h_); }
+  double ghost_cutoff() const { return pet_ghost_cutoff(h_); }
+  double exchange_ghost_cutoff() const { return pet_exchange_ghost_cutoff(h_); }
+  double energy_scale() const { return pet_energy_scale(h_); }
+  bool supports(int atomic_number) const { return pet_supports(h_, atomic_number) != 0; }
+  std::size_t workspace_bytes() const { return pet_workspace_bytes(h_); }
+  Options& options() { return opts_; }
+  const Options& options() const { return opts_; }
+
+ private:
+  static pet_edge_list list(const EdgeListView& v) {
+    return pet_edge_list{v.n_atoms, v.n_local, v.positions, v.atomic_numbers, v.offsets, v.neighbors, v.shifts, v.cell, v.half ? 1 : 0};
+  }
+  static pet_results sized(Results& r, std::size_t B, std::size_t N, bool forces, int pairs) {
+    pet_results out{};
+    r.energy.assign(B, 0.0), r.per_atom_energy.assign(N, 0.0);
+    out.energy = r.energy.data(), out.per_atom_energy = r.per_atom_energy.data();
+    if (forces) {
+      r.forces.assign(3 * N, 0.0), r.virial.assign(6 * B, 0.0), r.struct_id.assign(N, 0);
+      out.forces = r.forces.data(), out.virial = r.virial.data(), out.struct_id = r.struct_id.data();
+      if (pairs > 0) {
+        r.edge_gradient.assign(3 * std::size_t(pairs), 0.0);
+        out.edge_gradient = r.edge_gradient.data();
+      }
+    }
+    return out;
+  }
+  [[noreturn]] static void raise(int rc, const char* msg) {
+    const std::string m = msg ? msg : "pet: unknown error";
+    switch (rc) {
+      case PET_ERR_INVALID: throw std::invalid_argument(m);
+      case PET_ERR_LOGIC: throw std::logic_error(m);
+      case PET_ERR_ALLOC: throw std::bad_alloc();
+      default: throw std::runtime_error(m);
+    }
+  }
+  void check(int rc) const {
+    if (rc) raise(rc, pet_last_error(h_));
+  }
+
+  pet_calc* h_ = nullptr;
+  Options opts_;
+  mutable int pairs_ = 0, atoms_ = 0;
+};
+
+}  // namespace pet

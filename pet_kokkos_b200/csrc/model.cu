@@ -497,8 +497,191 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
 
 // ---- the residual featurizer ------------------------------------------------------
 
-PassOut Model::run_residual(Stream&, Arena&, Arena&, const PackedEdges&, bool, int, Taps*) {
-  throw Error(1, "model: the residual featurizer is not built yet");
+// Per GNN layer L: tokens = [node_embedders.L[species] ; compress(input_edge, geometry, species)];
+// A PostLN blocks  tokens = LN(t + mlp(t)), t = LN(tokens + attention(tokens));  every layer is read
+// out and the readouts summed; between layers input_edge = 0.5 (input_edge + out_edge of the reverse
+// edge)  (src/residual.cpp:13-133 forward, :135-249 backward).
+PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode, Taps* taps) {
+  const int N = pk.N, E = pk.E, T = N + E, S = pk.M + 1;
+  const int D = h_.d_pet, Dh = h_.d_head, H = h_.num_heads, hd = h_.head_dim;
+  const int G = h_.num_gnn_layers, A = h_.num_attention_layers;
+  const Gemms gm{st, tmp, mode};
+  const float sc = float(1.0 / (std::sqrt(double(hd)) * h_.attention_temperature));
+  const size_t Ea = E > 0 ? E : 1, Ta = T > 0 ? T : 1, Na = N > 0 ? N : 1;
+
+  struct Block {
+    float *qkv, *merged, *ml, *s1, *s2, *pre;
+  };
+  struct Layer {
+    float *cpre, *tokens;
+    float *nh0_pre, *nh1_pre, *eh0_pre, *eh1_pre, *edge_pred;
+    std::vector<Block> blk;
+  };
+  std::vector<Layer> sav(G);
+
+  float* input_edge = save.alloc<float>(Ea * D);
+  gather_rows(st, input_edge, mat("edge_embedder.weight").w, pk.species, E, D);
+  float* net = save.alloc<float>(Na);
+  float* node_pred = save.alloc<float>(Na);
+  double* per_atom = save.alloc<double>(pk.n_atoms > 0 ? pk.n_atoms : 1);
+  PETB_CUDA(cudaMemsetAsync(per_atom, 0, sizeof(double) * size_t(pk.n_atoms > 0 ? pk.n_atoms : 1), st.s));
+
+  for (int L = 0; L < G; ++L) {
+    const std::string g = "gnn_layers." + std::to_string(L), ls = std::to_string(L), c0 = g + ".compress.0";
+    Layer& sl = sav[L];
+    sl.blk.resize(A);
+    sl.tokens = save.alloc<float>(Ta * D);
+    sl.cpre = save.alloc<float>(Ea * D);
+    float* tokens = sl.tokens;
+    gather_rows(st, tokens, mat("node_embedders." + ls + ".weight").w, pk.atom_species, N, D);
+    {
+      Scope s0(tmp);
+      float* cact = tmp.alloc<float>(Ea * D);
+      if (L == 0) {
+        compress0(st, cact, sl.cpre, vec(c0 + "@b"), mat(c0 + "@tab").w, mat(c0 + "@x4").w, pk, D);
+      } else {
+        const Mat& wi = mat(c0 + "@in");
+        GemmArgs a;
+        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
+        a.bias = vec(c0 + "@b"), a.pre = sl.cpre, a.ldp = D, a.tab = mat(c0 + "@tab").w, a.sp = pk.species;
+        a.wx = mat(c0 + "@x4").w, a.vec = pk.vec, a.dist = pk.dist, a.epi = EPI_COMPRESS;
+        gemm(st, tmp, a, mode);
+      }
+      gm.linear(tokens + size_t(N) * D, cact, mat(g + ".compress.2.weight"), vec(g + ".compress.2.bias"), E);
+    }
+    for (int a = 0; a < A; ++a) {
+      const std::string tl = g + ".trans.layers." + std::to_string(a);
+      Block& b = sl.blk[a];
+      const Mat& w_in = mat(tl + ".mlp.w_in.weight");
+      b.qkv = save.alloc<float>(Ta * 3 * D);
+      b.merged = save.alloc<float>(Ta * D);
+      b.ml = save.alloc<float>(Ta * H * 2);
+      b.s1 = save.alloc<float>(Ta * D);
+      b.s2 = save.alloc<float>(Ta * D);
+      b.pre = save.alloc<float>(Ta * w_in.rows);
+      gm.linear(b.qkv, tokens, mat(tl + ".attention.input_linear.weight"), vec(tl + ".attention.input_linear.bias"), T);
+      AttnArgs at;
+      at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+      at.pairs = pk.pairs, at.T = T;
+      at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml;
+      attention_forward(st, at);
+      // s1 = attention(tokens) + tokens
+      gm.linear(b.s1, b.merged, mat(tl + ".attention.output_linear.weight"), vec(tl + ".attention.output_linear.bias"), T,
+                tokens, 0);
+      Scope s1(tmp);
+      float* tok_a = tmp.alloc<float>(Ta * D);
+      float* hmid = tmp.alloc<float>(Ta * w_in.rows);
+      norm_fwd(st, tok_a, b.s1, nullptr, vec(tl + ".norm_attention.weight"), vec(tl + ".norm_attention.bias"), T, D);
+      gm.linear_silu(hmid, b.pre, tok_a, w_in, vec(tl + ".mlp.w_in.bias"), T);
+      // s2 = mlp(tok_a) + tok_a; tokens = LN(s2)
+      gm.linear(b.s2, hmid, mat(tl + ".mlp.w_out.weight"), vec(tl + ".mlp.w_out.bias"), T, tok_a, 0);
+      norm_fwd(st, tokens, b.s2, nullptr, vec(tl + ".norm_mlp.weight"), vec(tl + ".norm_mlp.bias"), T, D);
+    }
+    tap(taps, "tokens" + ls, tokens, size_t(T) * D);
+    // this layer's readout, summed onto the earlier layers' (src/model.cpp:656-691)
+    sl.nh0_pre = save.alloc<float>(Na * Dh), sl.nh1_pre = save.alloc<float>(Na * Dh);
+    sl.eh0_pre = save.alloc<float>(Ea * Dh), sl.eh1_pre = save.alloc<float>(Ea * Dh);
+    sl.edge_pred = save.alloc<float>(Ea);
+    {
+      Scope s2(tmp);
+      float* nh0 = tmp.alloc<float>(Na * Dh);
+      float* nh1 = tmp.alloc<float>(Na * Dh);
+      float* eh0 = tmp.alloc<float>(Ea * Dh);
+      float* eh1 = tmp.alloc<float>(Ea * Dh);
+      const std::string nh = "node_heads.energy." + ls, eh = "edge_heads.energy." + ls;
+      const std::string nl = "node_last_layers.energy." + ls + ".energy___0", el = "edge_last_layers.energy." + ls + ".energy___0";
+      gm.linear_silu(nh0, sl.nh0_pre, tokens, mat(nh + ".0.weight"), vec(nh + ".0.bias"), N);
+      gm.linear_silu(nh1, sl.nh1_pre, nh0, mat(nh + ".2.weight"), vec(nh + ".2.bias"), N);
+      gemv_rows(st, nh1, Dh, mat(nl + ".weight").w, vec(nl + ".bias"), node_pred, N, Dh);
+      gm.linear_silu(eh0, sl.eh0_pre, tokens + size_t(N) * D, mat(eh + ".0.weight"), vec(eh + ".0.bias"), E);
+      gm.linear_silu(eh1, sl.eh1_pre, eh0, mat(eh + ".2.weight"), vec(eh + ".2.bias"), E);
+      gemv_rows(st, eh1, Dh, mat(el + ".weight").w, vec(el + ".bias"), sl.edge_pred, E, Dh);
+      readout_energy(st, net, per_atom, node_pred, sl.edge_pred, pk, comp_, scale_, L > 0, L + 1 == G);
+    }
+    if (L + 1 < G) message_average(st, input_edge, tokens + size_t(N) * D, pk.reverse, E, D);
+  }
+  if (!grad) return finish(st, save, pk, false, nullptr, nullptr, nullptr, per_atom);
+
+  // ---- backward ----
+  float* x4_adj = save.alloc<float>(Ea * 4);
+  float* cf_adj = save.alloc<float>(Ea);
+  float* cutoff_adj = save.alloc<float>(Ea);  // sum over layers of the edge predictions
+  PETB_CUDA(cudaMemsetAsync(x4_adj, 0, sizeof(float) * Ea * 4, st.s));
+  PETB_CUDA(cudaMemsetAsync(cf_adj, 0, sizeof(float) * Ea, st.s));
+  PETB_CUDA(cudaMemcpyAsync(cutoff_adj, sav[0].edge_pred, sizeof(float) * Ea, cudaMemcpyDeviceToDevice, st.s));
+  for (int L = 1; L < G; ++L) add_inplace(st, cutoff_adj, sav[L].edge_pred, size_t(E));
+  float* ie_a = save.alloc<float>(Ea * D);
+  float* ie_b = save.alloc<float>(Ea * D);
+  float* ie_adj = ie_a;  // adjoint of the next layer's input_edge
+  for (int L = G - 1; L >= 0; --L) {
+    const std::string g = "gnn_layers." + std::to_string(L), ls = std::to_string(L), c0 = g + ".compress.0";
+    const Layer& sl = sav[L];
+    Scope layer_scope(tmp);
+    float* tokens_adj = tmp.alloc<float>(Ta * D);
+    float* alt = tmp.alloc<float>(Ta * D);
+    {  // the readout's adjoint of this layer's tokens
+      Scope s3(tmp);
+      float* nh1_adj = tmp.alloc<float>(Na * Dh);
+      float* nh0_adj = tmp.alloc<float>(Na * Dh);
+      float* eh1_adj = tmp.alloc<float>(Ea * Dh);
+      float* eh0_adj = tmp.alloc<float>(Ea * Dh);
+      const std::string nh = "node_heads.energy." + ls, eh = "edge_heads.energy." + ls;
+      const std::string nl = "node_last_layers.energy." + ls + ".energy___0", el = "edge_last_layers.energy." + ls + ".energy___0";
+      readout_seed_bwd(st, nh1_adj, mat(nl + ".weight").w, sl.nh1_pre, nullptr, nullptr, pk.n_local, N, Dh);
+      gm.linear_silu_bwd(nh0_adj, nh1_adj, mat(nh + ".2.weight"), sl.nh0_pre, N);
+      gm.linear_bwd(tokens_adj, nh0_adj, mat(nh + ".0.weight"), N, false);
+      readout_seed_bwd(st, eh1_adj, mat(el + ".weight").w, sl.eh1_pre, pk.cut, pk.center, pk.n_local, E, Dh);
+      gm.linear_silu_bwd(eh0_adj, eh1_adj, mat(eh + ".2.weight"), sl.eh0_pre, E);
+      gm.linear_bwd(tokens_adj + size_t(N) * D, eh0_adj, mat(eh + ".0.weight"), E, false);
+    }
+    float* ie_next = ie_adj == ie_a ? ie_b : ie_a;
+    if (L + 1 < G) message_average_bwd(st, ie_next, tokens_adj + size_t(N) * D, ie_adj, pk.reverse, E, D);
+    else PETB_CUDA(cudaMemsetAsync(ie_next, 0, sizeof(float) * Ea * D, st.s));
+    for (int a = A - 1; a >= 0; --a) {
+      const std::string tl = g + ".trans.layers." + std::to_string(a);
+      const Block& b = sl.blk[a];
+      const Mat& w_in = mat(tl + ".mlp.w_in.weight");
+      Scope s4(tmp);
+      float* s2_adj = tmp.alloc<float>(Ta * D);
+      float* tok_a_adj = tmp.alloc<float>(Ta * D);
+      // tokens_out = LN(s2), s2 = tok_a + mlp(tok_a)
+      norm_bwd(st, s2_adj, tokens_adj, b.s2, vec(tl + ".norm_mlp.weight"), true, T, D, T, tok_a_adj);
+      {
+        Scope s5(tmp);
+        float* h_adj = tmp.alloc<float>(Ta * w_in.rows);
+        gm.linear_silu_bwd(h_adj, s2_adj, mat(tl + ".mlp.w_out.weight"), b.pre, T);
+        gm.linear_bwd(tok_a_adj, h_adj, w_in, T, true);
+      }
+      // tok_a = LN(s1), s1 = tokens_in + attention(tokens_in)
+      float* s1_adj = alt;
+      norm_bwd(st, s1_adj, tok_a_adj, b.s1, vec(tl + ".norm_attention.weight"), true, T, D, T);
+      {
+        Scope s6(tmp);
+        float* dmerged = tmp.alloc<float>(Ta * D);
+        float* qkv_adj = tmp.alloc<float>(Ta * 3 * D);
+        float* cfh = tmp.alloc<float>(Ta * H);
+        gm.linear_bwd(dmerged, s1_adj, mat(tl + ".attention.output_linear.weight"), T, false);
+        AttnArgs at;
+        at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+        at.pairs = pk.pairs, at.T = T;
+        at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml, at.dmerged = dmerged, at.qkv_adj = qkv_adj, at.cfh = cfh;
+        attention_backward(st, at);
+        cutoff_share(st, cf_adj, cfh, pk.cut, N, E, H);
+        gm.linear_bwd(s1_adj, qkv_adj, mat(tl + ".attention.input_linear.weight"), T, true);
+      }
+      alt = tokens_adj;
+      tokens_adj = s1_adj;
+    }
+    {  // tokens = [node_L ; et]: only et depends on the geometry
+      Scope s7(tmp);
+      float* gz = tmp.alloc<float>(Ea * D);
+      gm.linear_silu_bwd(gz, tokens_adj + size_t(N) * D, mat(g + ".compress.2.weight"), sl.cpre, E);
+      compress_geometry_bwd(st, x4_adj, gz, mat(c0 + "@x4").w, E, D);
+      if (L > 0) gm.linear_bwd(ie_next, gz, mat(c0 + "@in"), E, true);
+    }
+    ie_adj = ie_next;
+  }
+  return finish(st, save, pk, true, x4_adj, cutoff_adj, cf_adj, per_atom);
 }
 
 }  // namespace petb

@@ -234,13 +234,9 @@ __global__ void k_cutoff_share(float* __restrict__ cf_adj, const float* __restri
   cf_adj[k] += total / cf;
 }
 
-__global__ void k_add_inplace(float* __restrict__ a, const float* __restrict__ b, size_t n4) {
+__global__ void k_add_inplace(float* __restrict__ a, const float* __restrict__ b, size_t n) {
   const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= n4) return;
-  float4 x = reinterpret_cast<float4*>(a)[t];
-  const float4 y = reinterpret_cast<const float4*>(b)[t];
-  x.x += y.x, x.y += y.y, x.z += y.z, x.w += y.w;
-  reinterpret_cast<float4*>(a)[t] = x;
+  if (t < n) a[t] += b[t];
 }
 
 __global__ void k_message_average(float* __restrict__ ie, const float* __restrict__ oe, const int* __restrict__ rev, int E,
@@ -426,7 +422,7 @@ void cutoff_share(Stream& st, float* cf_adj, const float* cfh, const float* cut,
 void add_inplace(Stream& st, float* a, const float* b, size_t n) {
   if (n == 0) return;
   const ProfScope ps(st, PC_ELEMENTWISE, double(n), 12.0 * double(n));
-  k_add_inplace<<<blocks_for(n / 4, 256), 256, 0, st.s>>>(a, b, n / 4);
+  k_add_inplace<<<blocks_for(n, 256), 256, 0, st.s>>>(a, b, n);
   PETB_LAUNCH_CHECK(st);
 }
 

@@ -1,0 +1,121 @@
+"""Engine-supplied neighbour lists: set_neighbors / compute_step / compute_edges (the reference's tests/test_edges.cpp)."""
+import numpy as np
+import pytest
+
+from oracle import neighbors_oracle as nbo
+from pet_kokkos_b200 import EdgeListView, structures as st
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def calc(lib_path, models):
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("tiny", "feedforward", "scaled", 1))
+    yield c
+    c.close()
+
+
+def full_list(s, cutoff, skin=0.0):
+    """A full periodic list with shifts, as an engine would hand it over (pairs out to cutoff + skin)."""
+    idx, _, _ = nbo.brute_force_edges(s, cutoff + skin)
+    order = np.lexsort((idx[:, 4], idx[:, 3], idx[:, 2], idx[:, 1], idx[:, 0]))
+    idx = idx[order]
+    off = np.concatenate([[0], np.cumsum(np.bincount(idx[:, 0], minlength=s["n_atoms"]))])
+    return EdgeListView(s["positions"], s["atomic_numbers"], off, idx[:, 1], idx[:, 2:5], s["cell"])
+
+
+def test_shifts_list_matches_own_search(calc):
+    """tests/test_edges.cpp:180-208: an engine's periodic list with shifts gives the periodic answer."""
+    s = st.diamond(2, jitter=0.05, seed=0)
+    ref = calc.compute(s)
+    r = calc.compute_edges(full_list(s, calc.cutoff, skin=1.0))
+    assert abs(r.energy[0] - ref.energy[0]) <= 1e-5 * abs(ref.energy[0])
+    assert np.abs(r.forces - ref.forces).max() <= 1e-4 * max(1.0, np.abs(ref.forces).max())
+    assert np.abs(r.virial - ref.virial).max() <= 1e-4 * max(1.0, np.abs(ref.virial).max())
+
+
+def test_edge_gradients_fold_to_forces_and_virial(calc):
+    """tests/test_edges.cpp:166-175: F_i = sum_out g - sum_in g and W = sum v (x) g, to 1e-9 of their scale."""
+    s = st.diamond(2, jitter=0.05, seed=1)
+    v = full_list(s, calc.cutoff, skin=0.5)
+    r = calc.compute_edges(v, True, True)
+    g = r.edge_gradient
+    i = np.repeat(np.arange(s["n_atoms"]), np.diff(v.offsets))
+    j = v.neighbors
+    F = np.zeros_like(r.forces)
+    np.add.at(F, i, g)
+    np.add.at(F, j, -g)
+    vec = s["positions"][j] + v.shifts @ s["cell"] - s["positions"][i]
+    W9 = np.einsum("ea,eb->ab", vec, g)
+    W = np.array([W9[0, 0], W9[1, 1], W9[2, 2], 0.5 * (W9[0, 1] + W9[1, 0]), 0.5 * (W9[0, 2] + W9[2, 0]), 0.5 * (W9[1, 2] + W9[2, 1])])
+    assert np.abs(F - r.forces).max() <= 1e-9 * max(1.0, np.abs(r.forces).max())
+    assert np.abs(W - r.virial[0]).max() <= 1e-9 * max(1.0, np.abs(W).max())
+
+
+def test_half_list_equals_full_list(calc):
+    """tests/test_edges.cpp:256-276."""
+    s = st.diamond(2, jitter=0.05, seed=2)
+    full = full_list(s, calc.cutoff)
+    i = np.repeat(np.arange(s["n_atoms"]), np.diff(full.offsets))
+    keep = (i < full.neighbors) | ((i == full.neighbors) & ([tuple(x) > (0, 0, 0) for x in full.shifts.tolist()]))
+    off = np.concatenate([[0], np.cumsum(np.bincount(i[keep], minlength=s["n_atoms"]))])
+    half = EdgeListView(s["positions"], s["atomic_numbers"], off, full.neighbors[keep], full.shifts[keep], s["cell"], half=True)
+    a, b = calc.compute_edges(full, True, False), calc.compute_edges(half, True, False)
+    assert abs(a.energy[0] - b.energy[0]) <= 1e-6 * abs(a.energy[0])
+    assert np.abs(a.forces - b.forces).max() <= 1e-5 * max(1.0, np.abs(a.forces).max())
+
+
+def test_ghost_domain_reproduces_the_periodic_answer(calc):
+    """tests/test_edges.cpp:117-178: owned atoms plus explicit ghost images ghost_cutoff deep, no shifts;
+    the energy is the periodic one and ghost forces summed onto their owners give the periodic forces."""
+    s = st.diamond(2, jitter=0.05, seed=3)
+    ref = calc.compute(s)
+    N, L, reach = s["n_atoms"], s["cell"][0, 0], calc.ghost_cutoff
+    pos, owner = [s["positions"]], [np.arange(N)]
+    rng = int(np.ceil(reach / L))
+    for a in range(-rng, rng + 1):
+        for b in range(-rng, rng + 1):
+            for c in range(-rng, rng + 1):
+                if (a, b, c) == (0, 0, 0):
+                    continue
+                p = s["positions"] + np.array([a, b, c]) @ s["cell"]
+                lo, hi = s["positions"].min(0) - reach, s["positions"].max(0) + reach
+                m = ((p >= lo) & (p <= hi)).all(1)
+                pos.append(p[m]), owner.append(np.arange(N)[m])
+    pos, owner = np.concatenate(pos), np.concatenate(owner)
+    # every atom within ghost_cutoff - cutoff of an owned atom needs its full list: list every atom's pairs
+    d = pos[:, None, :] - pos[None, :, :]
+    d2 = (d * d).sum(-1)
+    ii, jj = np.nonzero((d2 <= calc.cutoff ** 2) & (d2 > 1e-20))
+    off = np.concatenate([[0], np.cumsum(np.bincount(ii, minlength=len(pos)))])
+    view = EdgeListView(pos, s["atomic_numbers"][owner], off, jj, n_local=N)
+    r = calc.compute_edges(view, True, False)
+    F = np.zeros((N, 3))
+    np.add.at(F, owner, r.forces)
+    assert abs(r.energy[0] - ref.energy[0]) <= 1e-5 * abs(ref.energy[0])
+    assert np.abs(F - ref.forces).max() <= 1e-4 * max(1.0, np.abs(ref.forces).max())
+
+
+def test_stepping_one_list(calc):
+    """tests/test_edges.cpp:278-319: set once, step with moved positions; pairs that drift past the cutoff weigh nothing."""
+    s = st.diamond(2, jitter=0.05, seed=4)
+    calc.set_neighbors(full_list(s, calc.cutoff, skin=1.0))
+    rng = np.random.default_rng(0)
+    for _ in range(3):
+        moved = dict(s)
+        moved["positions"] = s["positions"] + rng.normal(0, 0.03, size=s["positions"].shape)
+        r = calc.compute_step(moved["positions"], s["cell"])
+        ref = calc.compute(moved)
+        assert abs(r.energy[0] - ref.energy[0]) <= 1e-5 * abs(ref.energy[0])
+        assert np.abs(r.forces - ref.forces).max() <= 1e-4 * max(1.0, np.abs(ref.forces).max())
+    calc.set_neighbors(full_list(s, calc.cutoff, skin=1.0))
+
+
+def test_no_list_set_is_an_error(lib_path, models):
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("tiny"))
+    c._session_atoms = 1
+    with pytest.raises(RuntimeError, match="no neighbour list set"):
+        c.compute_step(np.zeros((1, 3)))
+    c.close()
