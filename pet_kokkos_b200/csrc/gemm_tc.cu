@@ -1,20 +1,28 @@
-// The tensor-core GEMM: tcgen05.mma with TMA-fed shared-memory tiles and the accumulator in
+// The tensor-core GEMM: tcgen05.mma with TMA-fed shared-memory tiles and the accumulators in
 // tensor memory (sm_100a). See gemm.h for the interface and the epilogues.
 //
-// One CTA computes a 128 x BN tile of C = A . B^T (A [M,K], B [N,K], both K-major fp32):
-//   warp 0   producer: one thread issues cp.async.bulk.tensor (TMA) loads of a 128 x 32 slab of
-//            A and a BN x 32 slab of B per stage, 128-byte swizzled, completing on an mbarrier;
-//   warp 1   issuer: one thread issues tcgen05.mma kind::tf32 (M = 128, N = BN, K = 8) four times
-//            per stage, accumulating in tensor memory, and releases the stage with tcgen05.commit;
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (a thread owns a row), stage it through shared
-//            memory so that a warp then walks one row at a time with its lanes across columns,
-//            and run the fused epilogue with coalesced 16-byte accesses.
-// In the 3xTF32 mode the issuer's products are split: each fp32 operand x is used as
-// hi = its leading tf32 bits and lo = x - hi (made in shared memory by the epilogue warps while
-// they wait), and hi.hi + hi.lo + lo.hi accumulate in fp32 -- fp32-class accuracy on the tensor
-// cores without reading the operands from L2 a second time.
+// A persistent kernel, one CTA per SM, each walking 128 x BN tiles of C = A . B^T (A [M,K],
+// B [N,K], both K-major fp32) in an N-fastest order so that CTAs running side by side share
+// their A rows in L2. Roles, by warp:
+//   warp 0      producer: one thread issues cp.async.bulk.tensor (TMA) loads of a 128 x 32 slab
+//               of A and a BN x 32 slab of B per stage, 128-byte swizzled, landing on an mbarrier;
+//   warp 1      issuer: one thread issues tcgen05.mma kind::tf32 (M = 128, N = BN, K = 8) four
+//               times per stage into one of TWO accumulators in tensor memory, releases the stage
+//               with tcgen05.commit and hands the finished accumulator to the epilogue;
+//   warps 4-11  epilogue: tcgen05.ld the accumulator (a thread owns a row, a warp pair splits the
+//               columns), turn each 32 x 32 chunk through a per-warp shared-memory pad so that
+//               lanes run along columns, issue the epilogue's global loads for four row groups
+//               before consuming them, and write 16 bytes per lane. The accumulator is handed
+//               back as soon as it has been read, so the next tile's products overlap this
+//               tile's stores;
+//   warps 12-15 (3xTF32 mode) splitter: for every landed stage write lo = x - hi(x) beside the
+//               tiles, hi(x) being x with its 13 low mantissa bits cleared, which is what the
+//               tensor core reads of an fp32 operand. The issuer then accumulates
+//               hi.hi + hi.lo + lo.hi in fp32: fp32-class accuracy without reading the operands
+//               from L2 a second time.
 // No TMA load here uses cluster multicast. Every wait is bounded: a wait that runs out sets an
-// error word the host checks, and the CTA still reaches its tensor-memory release.
+// error word the host checks, every role then leaves its loop, and the CTA still reaches its
+// tensor-memory release.
 #include <cuda.h>
 
 #include <mutex>
@@ -26,6 +34,8 @@ namespace petb {
 namespace {
 
 constexpr int TBM = 128, TBK = 32;  // rows per tile; fp32 elements per 128-byte swizzled row
+constexpr int kEpiWarp0 = 4, kEpiWarps = 8, kSplitWarp0 = 12;
+constexpr int kPad = 32;            // floats per row of an epilogue warp's 32 x 32 pad (16-byte slots XOR-swizzled by row)
 constexpr unsigned long long kSpinLimit = 1ull << 31;  // clock64 ticks (~1 s) before a wait gives up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
@@ -110,31 +120,33 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 
 template <int BN, int STAGES, bool X3>
 struct Smem {
-  static constexpr int kA = TBM * TBK * 4, kB = BN * TBK * 4;       // bytes per stage
-  static constexpr int kStage = (kA + kB) * (X3 ? 2 : 1);            // with the lo tiles in the 3x mode
+  static constexpr int kA = TBM * TBK * 4, kB = BN * TBK * 4;  // bytes per stage
+  static constexpr int kHi = kA + kB;
+  static constexpr int kStage = kHi * (X3 ? 2 : 1);            // with the lo tiles in the 3x mode
   static constexpr int kTiles = STAGES * kStage;
-  static constexpr int kStagePad = BN + 4;                            // floats per staged accumulator row
-  static constexpr int kEpi = TBM * kStagePad * 4;
-  static constexpr int kData = kTiles > kEpi ? kTiles : kEpi;
-  static constexpr int kTotal = kData + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kPads = kEpiWarps * 32 * kPad * 4;
+  static constexpr int kTotal = kTiles + kPads + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kThreads = X3 ? 512 : 384;
 };
 
 template <int EPI, int BN, int STAGES, bool X3>
-__global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ CUtensorMap map_a,
-                                                     const __grid_constant__ CUtensorMap map_b, GemmArgs p, int* err) {
+__global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
+    k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs p, int* err) {
   using L = Smem<BN, STAGES, X3>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::kData);  // [STAGES] TMA landed
-  uint64_t* empty = full + STAGES;                                 // [STAGES] MMAs of the stage done
-  uint64_t* split = empty + STAGES;                                // [STAGES] lo tiles written (3x mode)
-  uint64_t* accum = split + STAGES;                                // accumulator complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  float* pads = reinterpret_cast<float*>(tiles + L::kTiles);
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::kTiles + L::kPads);  // [STAGES] TMA landed
+  uint64_t* empty = full + STAGES;   // [STAGES] the stage's MMAs are done
+  uint64_t* split = empty + STAGES;  // [STAGES] lo tiles written (3x mode)
+  uint64_t* tfull = split + STAGES;  // [2] accumulator complete
+  uint64_t* tempty = tfull + 2;      // [2] accumulator read back
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int m0 = (blockIdx.x / tiles_n) * TBM, n0 = (blockIdx.x % tiles_n) * BN;
+  const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + TBM - 1) / TBM;
+  const int n_tiles = tiles_m * tiles_n;
   const int nkb = (p.K + TBK - 1) / TBK;
 
   if (threadIdx.x == 0) {
@@ -143,12 +155,15 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ CUte
       mbar_init(empty + s, 1);
       mbar_init(split + s, 128);
     }
-    mbar_init(accum, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull + b, 1);
+      mbar_init(tempty + b, kEpiWarps);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // tensor memory for the accumulator: BN fp32 columns x 128 lanes
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+  if (warp == 1) {  // tensor memory: two accumulators of BN fp32 columns x 128 lanes
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -158,98 +173,133 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ CUte
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(empty + s, ((kb / STAGES) - 1) & 1, abort_flag)) break;
-        uint8_t* sa = tiles + size_t(s) * L::kStage;
-        mbar_expect_tx(full + s, L::kA + L::kB);
-        tma_load_2d(sa, &map_a, full + s, kb * TBK, m0);
-        tma_load_2d(sa + L::kA, &map_b, full + s, kb * TBK, n0);
+      int g = 0;  // k-blocks issued so far, across tiles
+      for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * TBM, n0 = (t % tiles_n) * BN;
+        bool ok = true;
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const int s = g % STAGES;
+          if (!(ok = mbar_wait(empty + s, ((g / STAGES) & 1) ^ 1, abort_flag))) break;
+          uint8_t* sa = tiles + size_t(s) * L::kStage;
+          mbar_expect_tx(full + s, L::kHi);
+          tma_load_2d(sa, &map_a, full + s, kb * TBK, m0);
+          tma_load_2d(sa + L::kA, &map_b, full + s, kb * TBK, n0);
+        }
+        if (!ok) break;
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_tf32(BN);
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(X3 ? split + s : full + s, ph, abort_flag)) break;
+      int g = 0, i = 0;
+      for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++i) {
+        const int b = i & 1;
+        bool ok = mbar_wait(tempty + b, ((i >> 1) & 1) ^ 1, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a0 = smem_u32(tiles + size_t(s) * L::kStage), b0 = a0 + L::kA;
+        const uint32_t acc = tmem + uint32_t(b * BN);
+        for (int kb = 0; ok && kb < nkb; ++kb, ++g) {
+          const int s = g % STAGES;
+          if (!(ok = mbar_wait(X3 ? split + s : full + s, (g / STAGES) & 1, abort_flag))) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a0 = smem_u32(tiles + size_t(s) * L::kStage), b0 = a0 + L::kA;
 #pragma unroll
-        for (int k = 0; k < TBK / 8; ++k) {  // 8 tf32 = 32 bytes along K per instruction
-          const uint64_t da = smem_desc(a0 + 32 * k), db = smem_desc(b0 + 32 * k);
-          mma_tf32(tmem, da, db, idesc, (kb | k) != 0);
-          if (X3) {
-            const uint64_t dal = smem_desc(a0 + L::kA + L::kB + 32 * k), dbl = smem_desc(b0 + L::kA + L::kB + 32 * k);
-            mma_tf32(tmem, da, dbl, idesc, 1);
-            mma_tf32(tmem, dal, db, idesc, 1);
+          for (int k = 0; k < TBK / 8; ++k) {  // 8 tf32 = 32 bytes along K per instruction
+            const uint64_t da = smem_desc(a0 + 32 * k), db = smem_desc(b0 + 32 * k);
+            mma_tf32(acc, da, db, idesc, (kb | k) != 0);
+            if (X3) {
+              const uint64_t dal = smem_desc(a0 + L::kHi + 32 * k), dbl = smem_desc(b0 + L::kHi + 32 * k);
+              mma_tf32(acc, da, dbl, idesc, 1);
+              mma_tf32(acc, dal, db, idesc, 1);
+            }
+          }
+          mma_commit(empty + s);
+        }
+        if (!ok) break;
+        mma_commit(tfull + b);
+      }
+    }
+  } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps) {
+    const int ew = warp - kEpiWarp0;
+    const int q = warp & 3;          // the quarter of the 128 lanes this warp may read
+    const int half = ew >> 2;        // which half of the BN columns
+    float* pad = pads + size_t(ew) * 32 * kPad;
+    const int sub = lane >> 3, c4 = (lane & 7) * 4;  // row-within-group and column of this lane's 16 bytes
+    int i = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++i) {
+      const int b = i & 1;
+      const int m0 = (t / tiles_n) * TBM, n0 = (t % tiles_n) * BN;
+      if (!mbar_wait(tfull + b, (i >> 1) & 1, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t acc = tmem + uint32_t(b * BN) + (uint32_t(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+        float v[32];
+        tmem_ld32(acc + c0, v);
+        if (c0 + 32 == (half + 1) * (BN / 2)) {  // the accumulator has been read: the issuer may reuse it
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty + b);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(pad + lane * kPad + (((j >> 2) ^ (lane & 7)) << 2)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        __syncwarp();
+        const int col = n0 + c0 + c4;
+        if (col < p.N) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {  // four row groups at a time: their loads first, then their arithmetic and stores
+            EpiLoad ld[4];
+            int rows[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              rows[u] = m0 + q * 32 + (h * 4 + u) * 4 + sub;
+              if (rows[u] < p.M) ld[u] = epilogue_load4<EPI>(p, rows[u], col);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (rows[u] < p.M) {
+                const int rr = (h * 4 + u) * 4 + sub;
+                const float4 a = *reinterpret_cast<const float4*>(pad + rr * kPad + (((lane & 7) ^ (rr & 7)) << 2));
+                const float accv[4] = {a.x, a.y, a.z, a.w};
+                epilogue_apply4<EPI>(p, rows[u], col, accv, ld[u]);
+              }
+            }
           }
         }
-        mma_commit(empty + s);
       }
-      mma_commit(accum);
     }
-  } else {
-    const int ew = warp - 2;  // 0..3
-    if (X3) {
-      // lo = x - (x with the 13 low mantissa bits cleared), written beside the stage's tiles in the same
-      // swizzled positions, so the same descriptors (offset by the stage's hi size) address them.
-      const int t = threadIdx.x - 64;
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(full + s, (kb / STAGES) & 1, abort_flag)) break;
-        float4* hi = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage);
-        float4* lo = hi + (L::kA + L::kB) / 16;
-        for (int i = t; i < (L::kA + L::kB) / 16; i += 128) {
-          const float4 x = hi[i];
+  } else if (X3 && warp >= kSplitWarp0) {
+    // lo = x - hi(x), written beside the stage's tiles at the same swizzled positions, so the same
+    // descriptors, offset by the size of the hi tiles, address them.
+    const int tid = threadIdx.x - kSplitWarp0 * 32;
+    int g = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+      for (int kb = 0; kb < nkb; ++kb, ++g) {
+        const int s = g % STAGES;
+        if (!(ok = mbar_wait(full + s, (g / STAGES) & 1, abort_flag))) break;
+        const float4* hi = reinterpret_cast<const float4*>(tiles + size_t(s) * L::kStage);
+        float4* lo = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage + L::kHi);
+#pragma unroll 4
+        for (int e = tid; e < L::kHi / 16; e += 128) {
+          const float4 x = hi[e];
           float4 y;
           y.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
           y.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
           y.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
           y.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
-          lo[i] = y;
+          lo[e] = y;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes visible to the tensor core
         mbar_arrive(split + s);
-      }
-    }
-    const bool ok = mbar_wait(accum, 0, abort_flag);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float* stage = reinterpret_cast<float*>(tiles);
-    if (ok) {
-      // A warp may read the 32 lanes of its own quarter: warps 2,3,4,5 -> lanes 64-95, 96-127, 0-31, 32-63.
-      const int q = warp & 3, row = q * 32 + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem + (uint32_t(q * 32) << 16) + c0, v);
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(stage + row * L::kStagePad + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-      }
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (ok) {
-      for (int r = ew; r < TBM; r += 4) {
-        const int row = m0 + r;
-        if (row >= p.M) break;
-#pragma unroll
-        for (int c = lane * 4; c < BN; c += 128) {
-          const int col = n0 + c;
-          if (col < p.N) {
-            const float4 a = *reinterpret_cast<const float4*>(stage + r * L::kStagePad + c);
-            const float acc[4] = {a.x, a.y, a.z, a.w};
-            epilogue_run4<EPI>(p, row, col, acc);
-          }
-        }
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(err, 1);
 }
@@ -264,6 +314,7 @@ struct TensorState {
   EncodeFn encode = nullptr;
   int* err = nullptr;       // device error word
   int* err_host = nullptr;  // pinned mirror
+  int sms = 0;
   bool ok = false;
 };
 
@@ -277,7 +328,8 @@ TensorState& state() {
     int dev = 0, major = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-    if (major != 10) return;
+    cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev);
+    if (major != 10 || s.sms <= 0) return;
     if (cudaMalloc(&s.err, sizeof(int)) != cudaSuccess) return;
     cudaMemset(s.err, 0, sizeof(int));
     if (cudaMallocHost(&s.err_host, sizeof(int)) != cudaSuccess) return;
@@ -306,16 +358,17 @@ CUtensorMap make_map(const float* base, int rows, int K, int ld, int box_rows) {
 template <int EPI, int BN, int STAGES, bool X3>
 void launch_tc(Stream& st, const GemmArgs& a) {
   using L = Smem<BN, STAGES, X3>;
+  static_assert(L::kTotal <= 227 * 1024, "the tile pipeline does not fit shared memory");
   static bool opted = false;
   auto kernel = k_gemm_tc<EPI, BN, STAGES, X3>;
   if (!opted) {
     PETB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     opted = true;
   }
-  // TMA box rows are limited to 256; a box taller than the matrix is fine (rows past it read as zero).
   const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM), mb = make_map(a.B, a.N, a.K, a.ldb, BN);
   const long long tiles = (long long) cdiv(a.M, TBM) * cdiv(a.N, BN);
-  kernel<<<(unsigned) tiles, 192, L::kTotal, st.s>>>(ma, mb, a, state().err);
+  const int grid = int(tiles < state().sms ? tiles : state().sms);
+  kernel<<<grid, L::kThreads, L::kTotal, st.s>>>(ma, mb, a, state().err);
   PETB_LAUNCH_CHECK(st);
 }
 
@@ -337,7 +390,7 @@ bool tensor_gemm_available() { return state().ok; }
 bool gemm_tensor_usable(const GemmArgs& a, int mode) {
   if (mode != GEMM_TF32 && mode != GEMM_TF32X3 && mode != GEMM_BF16) return false;
   if (!state().ok) return false;
-  // TMA: 16-byte aligned bases and row strides; the staged epilogue wants N % 4 == 0 (checked by gemm()).
+  // TMA: 16-byte aligned bases and row strides; the epilogue walks runs of four columns (N % 4 == 0, checked by gemm()).
   if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B)) & 15) return false;
   if (a.lda % 4 || a.ldb % 4 || a.K % 8) return false;
   if (a.M < 64 || a.N < 32) return false;  // too small to be worth a 128-row tensor tile
