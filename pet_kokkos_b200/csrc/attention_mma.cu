@@ -1,0 +1,403 @@
+// Attention on the tensor cores with fp32-class accuracy: warp-level mma.sync m16n8k8 on operands
+// split into a leading tf32 part and its remainder (three products per tile, small terms first),
+// fp32 accumulation. Same mathematics as attention.cu; used when an atom's tokens fit shared memory.
+//
+// One CTA per (atom, head), one warp per block of 16 query rows (and, in the backward, one more per
+// block of 16 keys). The head's Q, K, V (and dO) slices are staged once with a pitch
+// of head_dim + 4 floats, which makes every fragment load below conflict-free:
+//   X^T as B operand (scores Q K^T, dO V^T): b(k = t, n = g) = X[key 8kb + g][k0 + t]   -> banks 4g + t
+//   X as B operand (P V, dS K, dS^T Q, P^T dO): the eight contraction indices of a step are taken in
+//   the order 0,2,4,6,1,3,5,7, so b(k = t) = X[8kb + 2t][d0 + g], b(k = t + 4) = X[8kb + 2t + 1][d0 + g]
+//   -> banks 8t + g; with that order the accumulator fragment of the scores (c0, c1 hold columns
+//   2t, 2t + 1) IS the A fragment of the next product, so probabilities never leave registers.
+// Forward: all scores of a query block stay in registers for the row max and sum. Backward, with the
+// saved max and 1/sum: half of the warps take 16 queries each and form dQ = sc dS K key block by key
+// block; the other half take 16 keys each and work transposed (S^T = K Q^T, dP^T = V dO^T), so that
+// dS^T and P^T come out as A fragments for dK = sc dS^T Q and dV = P^T dO and each key's column sum of
+// dS is a row sum. Nothing S x S is stored and the two halves never wait on each other.
+// Every sum has one owner and a fixed order.
+#include <cstdlib>
+
+#include "attention.h"
+
+namespace petb {
+
+namespace {
+
+constexpr float kOff = -1e30f;
+__device__ __forceinline__ bool is_off(float lc) { return lc < -1e29f; }
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+struct Frag {
+  uint32_t hi, lo;
+};
+__device__ __forceinline__ Frag split(float x) {
+  Frag f;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(f.hi) : "f"(x));
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(f.lo) : "f"(x - __uint_as_float(f.hi)));
+  return f;
+}
+__device__ __forceinline__ void mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// c += a . b with both operands split: lo.hi + hi.lo + hi.hi
+__device__ __forceinline__ void mma3(float* c, const Frag* a, const Frag& b0, const Frag& b1) {
+  mma(c, a[0].lo, a[1].lo, a[2].lo, a[3].lo, b0.hi, b1.hi);
+  mma(c, a[0].hi, a[1].hi, a[2].hi, a[3].hi, b0.lo, b1.lo);
+  mma(c, a[0].hi, a[1].hi, a[2].hi, a[3].hi, b0.hi, b1.hi);
+}
+
+__host__ __device__ inline int round16(int s) { return (s + 15) / 16 * 16; }
+// Pitch of the S x S tables: the smallest value >= S16 that is 4 modulo 32 (see the header).
+__host__ __device__ inline int table_pitch(int S16) { return (S16 + 27) / 32 * 32 + 4; }
+
+template <int HD>
+__device__ __forceinline__ void stage(float* dst, const float* src, size_t ld, int col, int n, int N, int e0, int cnt, int rows) {
+  constexpr int Q = HD / 4, P = HD + 4;
+  for (int t = threadIdx.x; t < rows * Q; t += blockDim.x) {
+    const int r = t / Q, c = (t % Q) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < cnt) {
+      const size_t row = r == 0 ? size_t(n) : size_t(N) + e0 + r - 1;
+      v = ld4(src + row * ld + col + c);
+    }
+    *reinterpret_cast<float4*>(dst + r * P + c) = v;
+  }
+}
+
+// The A fragments (hi, lo) of rows r0.. r0+15 of X [.][P] for every 8-wide step of the head dimension.
+template <int HD>
+__device__ __forceinline__ void load_a(Frag (*f)[4], const float* x, int r0, int g, int t) {
+  constexpr int P = HD + 4;
+#pragma unroll
+  for (int ks = 0; ks < HD / 8; ++ks) {
+    f[ks][0] = split(x[(r0 + g) * P + 8 * ks + t]);
+    f[ks][1] = split(x[(r0 + g + 8) * P + 8 * ks + t]);
+    f[ks][2] = split(x[(r0 + g) * P + 8 * ks + t + 4]);
+    f[ks][3] = split(x[(r0 + g + 8) * P + 8 * ks + t + 4]);
+  }
+}
+
+template <int HD, int MAXKB>
+__global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k_attn_fwd_mma(AttnArgs p) {
+  constexpr int P = HD + 4, KS = HD / 8;
+  extern __shared__ __align__(16) float smem[];
+  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H, D = p.H * HD;
+  const int e0 = p.off[n], cnt = p.off[n + 1] - e0 + 1;
+  const int S16 = round16(cnt), nkb = S16 / 8, SM = round16(p.S);
+  float* sq = smem;
+  float* sk = sq + SM * P;
+  float* sv = sk + SM * P;
+  float* slc = sv + SM * P;
+  stage<HD>(sq, p.qkv, 3 * size_t(D), h * HD, n, p.N, e0, cnt, S16);
+  stage<HD>(sk, p.qkv, 3 * size_t(D), D + h * HD, n, p.N, e0, cnt, S16);
+  stage<HD>(sv, p.qkv, 3 * size_t(D), 2 * D + h * HD, n, p.N, e0, cnt, S16);
+  for (int r = threadIdx.x; r < S16; r += blockDim.x) {
+    const float cf = r == 0 ? 1.0f : (r < cnt ? p.cut[e0 + r - 1] : 0.f);
+    slc[r] = cf > 0.f ? __logf(cf) : kOff;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int r0 = 16 * warp;
+  if (r0 >= cnt) return;
+
+  Frag qf[KS][4];
+  load_a<HD>(qf, sq, r0, g, t);
+  float s[MAXKB][4];
+#pragma unroll
+  for (int kb = 0; kb < MAXKB; ++kb) {
+    s[kb][0] = s[kb][1] = s[kb][2] = s[kb][3] = 0.f;
+    if (kb < nkb) {
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const Frag b0 = split(sk[(8 * kb + g) * P + 8 * ks + t]), b1 = split(sk[(8 * kb + g) * P + 8 * ks + t + 4]);
+        mma3(s[kb], qf[ks], b0, b1);
+      }
+    }
+  }
+  // bias, row max, exponentials, row sum; this lane holds rows g and g + 8, keys 8kb + 2t and + 1
+  float m0 = kOff, m1 = kOff;
+#pragma unroll
+  for (int kb = 0; kb < MAXKB; ++kb)
+    if (kb < nkb) {
+      const float lc0 = slc[8 * kb + 2 * t], lc1 = slc[8 * kb + 2 * t + 1];
+      s[kb][0] = is_off(lc0) ? kOff : s[kb][0] * p.sc + lc0;
+      s[kb][1] = is_off(lc1) ? kOff : s[kb][1] * p.sc + lc1;
+      s[kb][2] = is_off(lc0) ? kOff : s[kb][2] * p.sc + lc0;
+      s[kb][3] = is_off(lc1) ? kOff : s[kb][3] * p.sc + lc1;
+      m0 = fmaxf(m0, fmaxf(s[kb][0], s[kb][1]));
+      m1 = fmaxf(m1, fmaxf(s[kb][2], s[kb][3]));
+    }
+  m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1)), m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+  m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1)), m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+  float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+  for (int kb = 0; kb < MAXKB; ++kb)
+    if (kb < nkb) {
+      s[kb][0] = is_off(s[kb][0]) ? 0.f : __expf(s[kb][0] - m0);
+      s[kb][1] = is_off(s[kb][1]) ? 0.f : __expf(s[kb][1] - m0);
+      s[kb][2] = is_off(s[kb][2]) ? 0.f : __expf(s[kb][2] - m1);
+      s[kb][3] = is_off(s[kb][3]) ? 0.f : __expf(s[kb][3] - m1);
+      l0 += s[kb][0] + s[kb][1];
+      l1 += s[kb][2] + s[kb][3];
+    }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1), l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1), l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const int q0 = r0 + g, q1 = r0 + g + 8;
+  const bool dead0 = q0 > 0 && is_off(slc[q0]), dead1 = q1 > 0 && is_off(slc[q1]);  // a query on an edge at its cutoff
+  const float il0 = (!dead0 && l0 > 0.f) ? 1.0f / l0 : 0.f, il1 = (!dead1 && l1 > 0.f) ? 1.0f / l1 : 0.f;
+
+  // O = P V, the probabilities going straight from the accumulator layout into the A operand
+  float o[KS][4];
+#pragma unroll
+  for (int db = 0; db < KS; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
+#pragma unroll
+  for (int kb = 0; kb < MAXKB; ++kb)
+    if (kb < nkb) {
+      const Frag a[4] = {split(s[kb][0] * il0), split(s[kb][2] * il1), split(s[kb][1] * il0), split(s[kb][3] * il1)};
+#pragma unroll
+      for (int db = 0; db < KS; ++db) {
+        const Frag b0 = split(sv[(8 * kb + 2 * t) * P + 8 * db + g]), b1 = split(sv[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
+        mma3(o[db], a, b0, b1);
+      }
+    }
+  const size_t g0 = q0 == 0 ? size_t(n) : size_t(p.N) + e0 + q0 - 1, g1 = size_t(p.N) + e0 + q1 - 1;
+#pragma unroll
+  for (int db = 0; db < KS; ++db) {
+    if (q0 < cnt) *reinterpret_cast<float2*>(p.merged + g0 * D + h * HD + 8 * db + 2 * t) = make_float2(o[db][0], o[db][1]);
+    if (q1 < cnt) *reinterpret_cast<float2*>(p.merged + g1 * D + h * HD + 8 * db + 2 * t) = make_float2(o[db][2], o[db][3]);
+  }
+  if (t == 0 && p.ml) {
+    if (q0 < cnt) p.ml[(g0 * p.H + h) * 2] = dead0 ? kOff : m0, p.ml[(g0 * p.H + h) * 2 + 1] = il0;
+    if (q1 < cnt) p.ml[(g1 * p.H + h) * 2] = dead1 ? kOff : m1, p.ml[(g1 * p.H + h) * 2 + 1] = il1;
+  }
+}
+
+template <int HD, int MAXT>
+__global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(AttnArgs p) {
+  constexpr int P = HD + 4, KS = HD / 8;
+  extern __shared__ __align__(16) float smem[];
+  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H, D = p.H * HD;
+  const int e0 = p.off[n], cnt = p.off[n + 1] - e0 + 1;
+  const int S16 = round16(cnt), nkb = S16 / 8, SM = round16(p.S);
+  float* sq = smem;
+  float* sk = sq + SM * P;
+  float* sv = sk + SM * P;
+  float* sg = sv + SM * P;
+  float* slc = sg + SM * P;
+  float* sm = slc + SM;
+  float* sl = sm + SM;
+  float* sd = sl + SM;
+  stage<HD>(sq, p.qkv, 3 * size_t(D), h * HD, n, p.N, e0, cnt, S16);
+  stage<HD>(sk, p.qkv, 3 * size_t(D), D + h * HD, n, p.N, e0, cnt, S16);
+  stage<HD>(sv, p.qkv, 3 * size_t(D), 2 * D + h * HD, n, p.N, e0, cnt, S16);
+  stage<HD>(sg, p.dmerged, size_t(D), h * HD, n, p.N, e0, cnt, S16);
+  for (int r = threadIdx.x; r < S16; r += blockDim.x) {
+    float lc = kOff, m = 0.f, il = 0.f;
+    if (r < cnt) {
+      const size_t row = r == 0 ? size_t(n) : size_t(p.N) + e0 + r - 1;
+      const float cf = r == 0 ? 1.0f : p.cut[e0 + r - 1];
+      lc = cf > 0.f ? __logf(cf) : kOff;
+      m = p.ml[(row * p.H + h) * 2], il = p.ml[(row * p.H + h) * 2 + 1];
+    }
+    slc[r] = lc, sm[r] = m, sl[r] = il;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
+  for (int q = warp; q < S16; q += nw) {  // Dq = dO . O, a warp per query row (O from global memory)
+    float s = 0.f;
+    if (q < cnt) {
+      const size_t grow = q == 0 ? size_t(n) : size_t(p.N) + e0 + q - 1;
+      for (int d = lane; d < HD; d += 32) s += p.merged[grow * D + h * HD + d] * sg[q * P + d];
+    }
+    s = warp_sum(s);
+    if (lane == 0) sd[q] = s;
+  }
+  __syncthreads();
+  // The first half of the warps take 16 queries each (dQ), the second half 16 keys each (dK, dV and
+  // the keys' cutoff shares), both recomputing the weights they need: no S x S table, no further barrier.
+  const int half = nw >> 1;
+  const bool keys = warp >= half;
+  const int r0 = 16 * (keys ? warp - half : warp);
+  if (r0 >= S16) return;
+  const int i0 = r0 + g, i1 = r0 + g + 8;  // this lane's two rows (queries or keys)
+  const size_t g0 = i0 == 0 ? size_t(n) : size_t(p.N) + e0 + i0 - 1, g1 = size_t(p.N) + e0 + i1 - 1;
+  if (!keys) {
+    Frag qf[KS][4], gf[KS][4];
+    load_a<HD>(qf, sq, r0, g, t);
+    load_a<HD>(gf, sg, r0, g, t);
+    const float m0 = sm[i0], m1 = sm[i1], il0 = sl[i0], il1 = sl[i1], dq0 = sd[i0], dq1 = sd[i1];
+    float dq[KS][4];
+#pragma unroll
+    for (int db = 0; db < KS; ++db) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
+    for (int kb = 0; kb < nkb; ++kb) {
+      float cs[4] = {0.f, 0.f, 0.f, 0.f}, cp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const Frag k0 = split(sk[(8 * kb + g) * P + 8 * ks + t]), k1 = split(sk[(8 * kb + g) * P + 8 * ks + t + 4]);
+        mma3(cs, qf[ks], k0, k1);
+        const Frag v0 = split(sv[(8 * kb + g) * P + 8 * ks + t]), v1 = split(sv[(8 * kb + g) * P + 8 * ks + t + 4]);
+        mma3(cp, gf[ks], v0, v1);
+      }
+      const int key = 8 * kb + 2 * t;
+      const float lc0 = slc[key], lc1 = slc[key + 1];
+      const float P0 = (il0 > 0.f && !is_off(lc0)) ? __expf(cs[0] * p.sc + lc0 - m0) * il0 : 0.f;
+      const float P1 = (il0 > 0.f && !is_off(lc1)) ? __expf(cs[1] * p.sc + lc1 - m0) * il0 : 0.f;
+      const float P2 = (il1 > 0.f && !is_off(lc0)) ? __expf(cs[2] * p.sc + lc0 - m1) * il1 : 0.f;
+      const float P3 = (il1 > 0.f && !is_off(lc1)) ? __expf(cs[3] * p.sc + lc1 - m1) * il1 : 0.f;
+      const Frag a[4] = {split(P0 * (cp[0] - dq0)), split(P2 * (cp[2] - dq1)), split(P1 * (cp[1] - dq0)), split(P3 * (cp[3] - dq1))};
+#pragma unroll
+      for (int db = 0; db < KS; ++db) {
+        const Frag b0 = split(sk[(8 * kb + 2 * t) * P + 8 * db + g]), b1 = split(sk[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
+        mma3(dq[db], a, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int db = 0; db < KS; ++db) {
+      if (i0 < cnt)
+        *reinterpret_cast<float2*>(p.qkv_adj + g0 * 3 * D + h * HD + 8 * db + 2 * t) = make_float2(dq[db][0] * p.sc, dq[db][1] * p.sc);
+      if (i1 < cnt)
+        *reinterpret_cast<float2*>(p.qkv_adj + g1 * 3 * D + h * HD + 8 * db + 2 * t) = make_float2(dq[db][2] * p.sc, dq[db][3] * p.sc);
+    }
+  } else {
+    // transposed: rows are keys. S^T = K Q^T and dP^T = V dO^T per block of 8 queries; the accumulator
+    // fragment of dS^T (and P^T) is the A operand of dK = dS^T Q (and dV = P^T dO).
+    Frag kf[KS][4], vf[KS][4];
+    load_a<HD>(kf, sk, r0, g, t);
+    load_a<HD>(vf, sv, r0, g, t);
+    const float lc0 = slc[i0], lc1 = slc[i1];
+    const bool on0 = !is_off(lc0), on1 = !is_off(lc1);
+    float dk[KS][4], dv[KS][4], cf0 = 0.f, cf1 = 0.f;
+#pragma unroll
+    for (int db = 0; db < KS; ++db)
+      dk[db][0] = dk[db][1] = dk[db][2] = dk[db][3] = dv[db][0] = dv[db][1] = dv[db][2] = dv[db][3] = 0.f;
+    for (int qb = 0; qb < nkb; ++qb) {
+      float cs[4] = {0.f, 0.f, 0.f, 0.f}, cp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const Frag q0 = split(sq[(8 * qb + g) * P + 8 * ks + t]), q1 = split(sq[(8 * qb + g) * P + 8 * ks + t + 4]);
+        mma3(cs, kf[ks], q0, q1);
+        const Frag d0 = split(sg[(8 * qb + g) * P + 8 * ks + t]), d1 = split(sg[(8 * qb + g) * P + 8 * ks + t + 4]);
+        mma3(cp, vf[ks], d0, d1);
+      }
+      const int qa = 8 * qb + 2 * t, qc = qa + 1;  // this lane's two queries of the block
+      const float ma = sm[qa], mc = sm[qc], ila = sl[qa], ilc = sl[qc], da = sd[qa], dc = sd[qc];
+      const float P0 = (on0 && ila > 0.f) ? __expf(cs[0] * p.sc + lc0 - ma) * ila : 0.f;  // key i0, query qa
+      const float P1 = (on0 && ilc > 0.f) ? __expf(cs[1] * p.sc + lc0 - mc) * ilc : 0.f;  // key i0, query qc
+      const float P2 = (on1 && ila > 0.f) ? __expf(cs[2] * p.sc + lc1 - ma) * ila : 0.f;  // key i1, query qa
+      const float P3 = (on1 && ilc > 0.f) ? __expf(cs[3] * p.sc + lc1 - mc) * ilc : 0.f;
+      const float S0 = P0 * (cp[0] - da), S1 = P1 * (cp[1] - dc), S2 = P2 * (cp[2] - da), S3 = P3 * (cp[3] - dc);
+      cf0 += S0 + S1, cf1 += S2 + S3;
+      const Frag as[4] = {split(S0), split(S2), split(S1), split(S3)};
+      const Frag ap[4] = {split(P0), split(P2), split(P1), split(P3)};
+#pragma unroll
+      for (int db = 0; db < KS; ++db) {
+        const Frag b0 = split(sq[qa * P + 8 * db + g]), b1 = split(sq[qc * P + 8 * db + g]);
+        mma3(dk[db], as, b0, b1);
+        const Frag d0 = split(sg[qa * P + 8 * db + g]), d1 = split(sg[qc * P + 8 * db + g]);
+        mma3(dv[db], ap, d0, d1);
+      }
+    }
+    cf0 += __shfl_xor_sync(0xffffffffu, cf0, 1), cf0 += __shfl_xor_sync(0xffffffffu, cf0, 2);
+    cf1 += __shfl_xor_sync(0xffffffffu, cf1, 1), cf1 += __shfl_xor_sync(0xffffffffu, cf1, 2);
+#pragma unroll
+    for (int db = 0; db < KS; ++db) {
+      const int c = h * HD + 8 * db + 2 * t;
+      if (i0 < cnt) {
+        *reinterpret_cast<float2*>(p.qkv_adj + g0 * 3 * D + D + c) = make_float2(dk[db][0] * p.sc, dk[db][1] * p.sc);
+        *reinterpret_cast<float2*>(p.qkv_adj + g0 * 3 * D + 2 * D + c) = make_float2(dv[db][0], dv[db][1]);
+      }
+      if (i1 < cnt) {
+        *reinterpret_cast<float2*>(p.qkv_adj + g1 * 3 * D + D + c) = make_float2(dk[db][2] * p.sc, dk[db][3] * p.sc);
+        *reinterpret_cast<float2*>(p.qkv_adj + g1 * 3 * D + 2 * D + c) = make_float2(dv[db][2], dv[db][3]);
+      }
+    }
+    if (t == 0) {  // each key's dS summed over its queries: the cutoff factor's share from this head
+      if (i0 < cnt) p.cfh[g0 * p.H + h] = cf0;
+      if (i1 < cnt) p.cfh[g1 * p.H + h] = cf1;
+    }
+  }
+}
+
+bool enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("PET_ATTN_MMA");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+size_t fwd_bytes(int S, int HD) {
+  const int SM = round16(S);
+  return sizeof(float) * (3 * size_t(SM) * (HD + 4) + SM);
+}
+size_t bwd_bytes(int S, int HD) {
+  const int SM = round16(S);
+  return sizeof(float) * (4 * size_t(SM) * (HD + 4) + 4 * size_t(SM));
+}
+
+template <class K>
+void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, int threads, int* opted) {
+  if (int(bytes) > *opted) {
+    PETB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
+    *opted = int(bytes);
+  }
+  kernel<<<p.N * p.H, threads, bytes, st.s>>>(p);
+  PETB_LAUNCH_CHECK(st);
+}
+
+template <int HD>
+bool fwd_hd(Stream& st, const AttnArgs& p) {
+  const int S16 = round16(p.S), threads = 32 * (S16 / 16);
+  const size_t bytes = fwd_bytes(p.S, HD);
+  if (bytes > 200 * 1024) return false;
+  static int o10 = 48 * 1024, o16 = 48 * 1024, o22 = 48 * 1024;
+  if (S16 <= 80) launch(st, k_attn_fwd_mma<HD, 10>, p, bytes, threads, &o10);
+  else if (S16 <= 128) launch(st, k_attn_fwd_mma<HD, 16>, p, bytes, threads, &o16);
+  else if (S16 <= 176) launch(st, k_attn_fwd_mma<HD, 22>, p, bytes, threads, &o22);
+  else return false;
+  return true;
+}
+template <int HD>
+bool bwd_hd(Stream& st, const AttnArgs& p) {
+  const int S16 = round16(p.S), threads = 2 * 32 * (S16 / 16);  // a warp per 16 queries and a warp per 16 keys
+  const size_t bytes = bwd_bytes(p.S, HD);
+  if (bytes > 200 * 1024 || threads > 512) return false;
+  static int o320 = 48 * 1024, o512 = 48 * 1024;
+  if (threads <= 320) launch(st, k_attn_bwd_mma<HD, 320>, p, bytes, threads, &o320);
+  else launch(st, k_attn_bwd_mma<HD, 512>, p, bytes, threads, &o512);
+  return true;
+}
+
+}  // namespace
+
+// True if the tensor-core kernel took the pass; false leaves it to the other kernels.
+bool attention_forward_mma(Stream& st, const AttnArgs& p) {
+  if (!enabled()) return false;
+  switch (p.hd) {
+    case 16: return fwd_hd<16>(st, p);
+    case 32: return fwd_hd<32>(st, p);
+    case 64: return fwd_hd<64>(st, p);
+    default: return false;
+  }
+}
+
+bool attention_backward_mma(Stream& st, const AttnArgs& p) {
+  if (!enabled()) return false;
+  switch (p.hd) {
+    case 16: return bwd_hd<16>(st, p);
+    case 32: return bwd_hd<32>(st, p);
+    case 64: return bwd_hd<64>(st, p);
+    default: return false;
+  }
+}
+
+}  // namespace petb
