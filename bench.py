@@ -288,7 +288,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gemm", default=os.environ.get("PET_GEMM", "native"), choices=["native", "tf32", "bf16", "3xtf32"])
+    ap.add_argument("--gemm", default=os.environ.get("PET_GEMM", "3xtf32"), choices=["native", "tf32", "bf16", "3xtf32"])
     ap.add_argument("--workload", default="diamond1728", choices=sorted(MODEL_OF))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU arm beside the GPU number")
     args = ap.parse_args()

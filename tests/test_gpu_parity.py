@@ -48,14 +48,16 @@ def test_goldens(name, tmp_path, lib_path):
     c.close()
 
 
+@pytest.mark.parametrize("gemm", ["native", "3xtf32"])
 @pytest.mark.parametrize("shape,workload", [("xs", "diamond64"), ("s", "water648"), ("s", "diamond1728")])
-def test_benchmark_configs_match_oracle(models, lib_path, shape, workload):
+def test_benchmark_configs_match_oracle(models, lib_path, shape, workload, gemm):
+    """Both fp32-accurate GEMM modes (CUDA cores; 3xTF32 split on the tensor cores) meet the parity band."""
     from pet_kokkos_b200 import Calculator
     jp, sp = models(shape)
     meta, tens = ck.load_checkpoint(jp, sp)
     systems = st.workload(workload)
     ref = po.evaluate(meta, tens, systems, dtype=torch.float64)
-    c = Calculator(jp, sp)
+    c = Calculator(jp, sp, gemm=gemm)
     r = c.compute(systems)
     check(r, ref)
     assert np.abs(r.forces).max() > 100 * F_ABS, "the force tolerance must bite"
@@ -121,6 +123,21 @@ def test_full_size_properties(models, lib_path):
     assert abs(r3.energy[0] - r.energy[0]) <= E_REL * abs(r.energy[0])
     assert np.abs(r3.forces - r.forces[perm]).max() <= F_ABS
     c.close()
+
+
+def test_tf32_mode_is_a_speed_mode_within_its_band(models, lib_path):
+    """tests/test_determinism.cpp:462-568 and README accuracy table: tf32 GEMMs stay within ~1e-3 eV/atom and 0.03 eV/A."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("s")
+    systems = st.workload("water648")
+    a = Calculator(jp, sp, gemm="native")
+    b = Calculator(jp, sp, gemm="tf32")
+    ra, rb = a.compute(systems), b.compute(systems)
+    n = systems[0]["n_atoms"]
+    assert abs(ra.energy[0] - rb.energy[0]) / n <= 1e-3
+    assert np.abs(ra.forces - rb.forces).max() <= 0.03
+    assert np.abs(ra.forces - rb.forces).max() > 1e-7  # it really is a different arithmetic
+    a.close(), b.close()
 
 
 def test_errors_are_reported(models, lib_path):
