@@ -255,3 +255,38 @@ def build_edges(systems, species_to_index, cutoff, width, cutoff_function="Bump"
         "max_neighbors": int(max(counts.max() if N else 0, 1)),
         "raw": raw, "raw_vec": vec, "raw_dist": dist,
     }
+
+
+def build_edges_from_list(positions, species, offsets, neighbors, cutoff, width, cutoff_function="Bump", shifts=None,
+                          cell=None, n_local=None):
+    """Packed model edges from an engine's own full neighbour list (the reference's EdgeSession::set/step,
+    src/device_geometry.cpp:410-454,712-778): v = r_j + shift.cell - r_i, kept when d <= cutoff, slots in list
+    order, partner = the (j, i, -shift) entry."""
+    positions = np.asarray(positions, dtype=np.float64)
+    N = len(positions)
+    ii = np.repeat(np.arange(N), np.diff(offsets))
+    jj = np.asarray(neighbors, dtype=np.int64)
+    sh = np.zeros((len(jj), 3), np.int64) if shifts is None else np.asarray(shifts, dtype=np.int64)
+    vec = positions[jj] - positions[ii]
+    if shifts is not None:
+        vec = positions[jj] + sh @ np.asarray(cell, dtype=np.float64).reshape(3, 3) - positions[ii]
+    dist = np.sqrt((vec * vec).sum(1))
+    raw = np.concatenate([ii[:, None], jj[:, None], sh], 1)
+    raw_rev = reverse_edges(raw, None)
+    keep = dist <= cutoff
+    fn = bump_cutoff_f32 if cutoff_function == "Bump" else cosine_cutoff_f32
+    cut = fn(dist, np.full_like(dist, cutoff), width).astype(np.float32)
+    kept = np.nonzero(keep)[0]
+    packed_of_raw = np.full(len(dist), -1, np.int64)
+    packed_of_raw[kept] = np.arange(len(kept))
+    center = ii[kept]
+    counts = np.bincount(center, minlength=N)
+    rr = raw_rev[kept]
+    species = np.asarray(species, dtype=np.int64)
+    return {
+        "n_atoms": N, "n_struct": 1, "species": species, "struct_id": np.zeros(N, np.int64),
+        "off": np.concatenate([[0], np.cumsum(counts)]).astype(np.int64), "center": center, "neighbor": jj[kept],
+        "shift": sh[kept], "nb_species": species[jj[kept]], "reverse": np.where(rr >= 0, packed_of_raw[np.maximum(rr, 0)], -1),
+        "vec": vec[kept], "dist": dist[kept], "cut": cut[kept], "max_neighbors": int(max(counts.max() if N else 0, 1)),
+        "raw": raw, "raw_vec": vec, "raw_dist": dist, "n_local": N if n_local is None or n_local < 0 else int(n_local),
+    }

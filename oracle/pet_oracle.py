@@ -311,14 +311,19 @@ def evaluate(meta, tensors, systems, dtype=torch.float32, forces=True, want=None
     if threads:
         torch.set_num_threads(threads)
     h = meta["hypers"]
-    ed = nbo.build_edges(systems, meta["species_to_index"], h["cutoff"], h["cutoff_width"], h["cutoff_function"],
-                         search=search)
+    if isinstance(systems, dict) and "off" in systems:  # packed edges made elsewhere (an engine's own list)
+        ed = systems
+    else:
+        ed = nbo.build_edges(systems, meta["species_to_index"], h["cutoff"], h["cutoff_width"], h["cutoff_function"],
+                             search=search)
     W = Weights(meta, tensors, dtype)
     vec = torch.from_numpy(ed["vec"]).clone().requires_grad_(forces)
     fwd = forward_feedforward if h["featurizer_type"] == "feedforward" else forward_residual
     with torch.set_grad_enabled(forces):
         per_atom = fwd(W, ed, vec, want)
         N, B = ed["n_atoms"], ed["n_struct"]
+        if ed.get("n_local", N) < N:  # ghosts shape the energy but are not in it (src/ops.cpp:420-425)
+            per_atom = per_atom * (torch.arange(N) < ed["n_local"])
         sid = torch.from_numpy(ed["struct_id"])
         energy = torch.zeros(B, dtype=torch.float64).index_add(0, sid, per_atom)
         out = {"energy": energy.detach().numpy(), "per_atom_energy": per_atom.detach().numpy(), "edges": ed}

@@ -119,3 +119,21 @@ def test_no_list_set_is_an_error(lib_path, models):
     with pytest.raises(RuntimeError, match="no neighbour list set"):
         c.compute_step(np.zeros((1, 3)))
     c.close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_domain_decomposition_on_one_gpu(calc, world):
+    """The multi-GPU single-cell path with its ranks played one after another on one GPU: owned atoms plus
+    ghost shells per rank, ghost forces folded onto owners, energies and virials summed (pet_kokkos_b200/domain.py).
+    Tolerances are the reference's for a ghost domain (tests/test_edges.cpp:117-178)."""
+    from pet_kokkos_b200 import domain
+    s = st.diamond(3, jitter=0.05, seed=5)
+    ref = calc.compute(s)
+    e, F, W = 0.0, np.zeros((s["n_atoms"], 3)), np.zeros(6)
+    for rank in range(world):
+        view, owner, n_local = domain.local_domain(s, rank, world, calc.cutoff, calc.ghost_cutoff)
+        pe, pF, pW = domain.fold(calc.compute_edges(view, True, False), owner, s["n_atoms"])
+        e, F, W = e + pe, F + pF, W + pW
+    assert abs(e - ref.energy[0]) <= 1e-5 * abs(ref.energy[0])
+    assert np.abs(F - ref.forces).max() <= 1e-4 * max(1.0, np.abs(ref.forces).max())
+    assert np.abs(W - ref.virial[0]).max() <= 1e-4 * max(1.0, np.abs(ref.virial).max())
