@@ -375,12 +375,24 @@ void launch_tc(Stream& st, const GemmArgs& a) {
 template <int EPI>
 void dispatch_tc(Stream& st, const GemmArgs& a, int mode) {
   const bool x3 = mode == GEMM_TF32X3;
-  if (a.N % 256 == 0) {
+  // The widest tile that still gives every SM a tile: a GEMM over the atoms' rows (a few thousand) would
+  // otherwise run on a handful of CTAs with a long, latency-bound K loop each.
+  const long long mt = cdiv(a.M, TBM);
+  const int sms = state().sms;
+  int bn = 64;
+  if (a.N % 256 == 0 && mt * (a.N / 256) >= sms) bn = 256;
+  else if (a.N % 128 == 0 && mt * (a.N / 128) >= sms) bn = 128;
+  else if (a.N % 64 != 0) bn = a.N % 256 == 0 ? 256 : 128;  // ragged widths: a wide tile with a zero-filled edge
+  if (bn == 256) {
     if (x3) return launch_tc<EPI, 256, 2, true>(st, a);
     return launch_tc<EPI, 256, 4, false>(st, a);
   }
-  if (x3) return launch_tc<EPI, 128, 3, true>(st, a);
-  return launch_tc<EPI, 128, 4, false>(st, a);
+  if (bn == 128) {
+    if (x3) return launch_tc<EPI, 128, 3, true>(st, a);
+    return launch_tc<EPI, 128, 4, false>(st, a);
+  }
+  if (x3) return launch_tc<EPI, 64, 4, true>(st, a);
+  return launch_tc<EPI, 64, 6, false>(st, a);
 }
 
 }  // namespace
