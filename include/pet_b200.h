@@ -172,6 +172,9 @@ int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neig
  * device time in milliseconds of the latest evaluation (CUDA events on the
  * calculator's stream). */
 long long pet_kernel_launches(const pet_calc* c);
+/* Evaluations served by replaying a recorded CUDA graph (Options::graphs; the reference's GraphCache,
+ * include/pet/graph.hpp:68-146: eager first, capture second, replay after). */
+long long pet_graph_replays(const pet_calc* c);
 double pet_last_device_ms(const pet_calc* c);
 
 /* Per-class device timing of evaluations (no counterpart in the reference's API; its

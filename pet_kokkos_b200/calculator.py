@@ -90,6 +90,7 @@ SIGNATURES = {
     "pet_last_shapes": (C.c_int, [C.c_void_p, _P(C.c_int), _P(C.c_int), _P(C.c_int)]),
     "pet_kernel_launches": (C.c_longlong, [C.c_void_p]),
     "pet_last_device_ms": (C.c_double, [C.c_void_p]),
+    "pet_graph_replays": (C.c_longlong, [C.c_void_p]),
     "pet_profile": (C.c_int, [C.c_void_p, C.c_int]),
     "pet_profile_read": (C.c_int, [C.c_void_p, _P(PetProfileEntry), C.c_int, _P(C.c_int)]),
     "pet_debug_fetch": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_float), C.c_size_t, _P(C.c_size_t)]),
@@ -245,6 +246,10 @@ class Calculator:
     @property
     def kernel_launches(self):
         return self._lib.pet_kernel_launches(self._h)
+
+    @property
+    def graph_replays(self):
+        return self._lib.pet_graph_replays(self._h)
 
     @property
     def last_device_ms(self):

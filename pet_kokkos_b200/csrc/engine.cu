@@ -101,6 +101,7 @@ Engine::Engine(const std::string& json, const std::string& weights, const pet_op
 Engine::~Engine() {
   cudaSetDevice(device);
   cudaDeviceSynchronize();
+  drop_graphs();
   model.reset();
   if (pinned) cudaFreeHost(pinned);
   if (host_stage) cudaFreeHost(host_stage);
@@ -222,11 +223,85 @@ void Engine::update_staged(const double* positions, const double* cells) {
 
 // ---- one evaluation -----------------------------------------------------------------
 
+void Engine::drop_graphs() {
+  for (auto& g : graph_cache)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
+  graph_cache.clear();
+  graph_seen.clear();
+}
+
+// One pass of the network over packed edges: eagerly, or as a recorded CUDA graph once the same shapes and
+// buffers have been seen before (eager first, capture second, replay after). The key holds everything the
+// recorded launches depend on besides the weights: shapes, the input pointers, and the pools' generations.
 void Engine::run_model(const PackedEdges& pk, bool forces) {
   taps.clear();
-  last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, want_taps ? &taps : nullptr);
-  last_pk = pk;
-  have_out = true;
+  const bool eager_only = !graphs || want_taps || prof.on;
+  if (eager_only) {
+    last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, want_taps ? &taps : nullptr);
+    last_pk = pk, have_out = true;
+    return;
+  }
+  auto ptr = [](const void* q) { return uint64_t(reinterpret_cast<uintptr_t>(q)); };
+  const std::vector<uint64_t> key = {uint64_t(pk.N),      uint64_t(pk.E),     uint64_t(pk.M),       uint64_t(pk.B),
+                                     uint64_t(pk.n_atoms), uint64_t(pk.n_local), uint64_t(forces),   uint64_t(gemm_mode),
+                                     ptr(pk.off),          ptr(pk.center),     ptr(pk.species),      ptr(pk.reverse),
+                                     ptr(pk.vec),          ptr(pk.dist),       ptr(pk.cut),          ptr(pk.atom_species),
+                                     ptr(pk.soff),         save_arena.generation(), tmp_arena.generation(),
+                                     ptr(save_arena.alloc_bytes(0))};
+  for (auto& g : graph_cache)
+    if (g.key == key) {
+      PETB_CUDA(cudaGraphLaunch(g.exec, st.s));
+      st.launches += g.launches;
+      ++graph_replays;
+      g.stamp = ++graph_clock;
+      save_arena.rewind(g.save_after), tmp_arena.rewind(g.tmp_after);
+      last_out = g.out, last_pk = pk, have_out = true;
+      return;
+    }
+  bool seen = false;
+  for (auto& k : graph_seen) seen = seen || k == key;
+  if (!seen) {  // first time: eagerly (the pools may still grow, which a capture cannot contain)
+    if (graph_seen.size() >= 32) graph_seen.erase(graph_seen.begin());
+    graph_seen.push_back(key);
+    last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, nullptr);
+    last_pk = pk, have_out = true;
+    return;
+  }
+  GraphEntry g;
+  g.key = key;
+  const long long before = st.launches;
+  const uint64_t gen_s = save_arena.generation(), gen_t = tmp_arena.generation();
+  cudaGraph_t graph = nullptr;
+  PETB_CUDA(cudaStreamBeginCapture(st.s, cudaStreamCaptureModeRelaxed));
+  try {
+    g.out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, nullptr);
+  } catch (...) {
+    cudaStreamEndCapture(st.s, &graph);
+    if (graph) cudaGraphDestroy(graph);
+    throw;
+  }
+  PETB_CUDA(cudaStreamEndCapture(st.s, &graph));
+  g.launches = st.launches - before;
+  g.save_after = save_arena.mark(), g.tmp_after = tmp_arena.mark();
+  if (gen_s != save_arena.generation() || gen_t != tmp_arena.generation()) {
+    // A pool grew during the capture (it should not, after the eager pass): do not keep the recording.
+    cudaGraphDestroy(graph);
+    throw Error(3, "pet: the scratch pool grew while a pass was being recorded");
+  }
+  const cudaError_t ie = cudaGraphInstantiate(&g.exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (ie != cudaSuccess) throw Error(5, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(ie));
+  PETB_CUDA(cudaGraphLaunch(g.exec, st.s));
+  g.stamp = ++graph_clock;
+  if (graph_cache.size() >= 8) {  // least recently used out
+    size_t lru = 0;
+    for (size_t i = 1; i < graph_cache.size(); ++i)
+      if (graph_cache[i].stamp < graph_cache[lru].stamp) lru = i;
+    cudaGraphExecDestroy(graph_cache[lru].exec);
+    graph_cache.erase(graph_cache.begin() + lru);
+  }
+  last_out = g.out, last_pk = pk, have_out = true;
+  graph_cache.push_back(g);
 }
 
 void Engine::compute_staged(bool forces) {
@@ -429,10 +504,7 @@ static StepOut session_step(Engine& I, const double* positions, bool on_device, 
   I.last_B = 1, I.last_N = N;
   StepOut so;
   if (N == 0) return so;
-  I.taps.clear();
-  I.last_out = I.model->run(st, I.save_arena, I.tmp_arena, pk, forces, I.gemm_mode, I.want_taps ? &I.taps : nullptr);
-  I.last_pk = pk;
-  I.have_out = true;
+  I.run_model(pk, forces);
   if (forces && s.E > 0) {
     so.eg_raw = I.save_arena.alloc<double>(3 * size_t(s.E));
     k_raw_edge_grad<<<cdiv(s.E, 256), 256, 0, st.s>>>(so.eg_raw, I.last_out.f.edge_grad, pk.packed_of_raw, s.E,

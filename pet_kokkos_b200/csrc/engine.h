@@ -80,8 +80,24 @@ struct Engine {
   Session md;
   std::string error;
 
- private:
+  // Recorded passes (the reference's GraphCache, include/pet/graph.hpp:68-146): a pass of given shapes and
+  // buffers runs eagerly the first time, is captured the second time and replayed afterwards.
+  struct GraphEntry {
+    std::vector<uint64_t> key;
+    cudaGraphExec_t exec = nullptr;
+    PassOut out;
+    Arena::Mark save_after{}, tmp_after{};
+    long long launches = 0;
+    uint64_t stamp = 0;
+  };
+  std::vector<GraphEntry> graph_cache;
+  std::vector<std::vector<uint64_t>> graph_seen;
+  uint64_t graph_clock = 0;
+  long long graph_replays = 0;
   void run_model(const PackedEdges& pk, bool forces);
+  void drop_graphs();
+
+ private:
   void* staging(size_t bytes);
 };
 

@@ -79,6 +79,27 @@ def test_bit_identical_repeats_and_batch_independence(models, lib_path):
     c.close()
 
 
+@pytest.mark.parametrize("gemm", ["native", "3xtf32"])
+def test_graph_replay_gives_eager_bits(models, lib_path, gemm):
+    """tests/test_determinism.cpp:238-254: a replayed recording returns the bits of the eager pass."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("xs")
+    systems = [st.diamond(2, jitter=0.05, seed=0), st.random_mixture(40, 9.0, seed=1)]
+    eager = Calculator(jp, sp, gemm=gemm, graphs=False)
+    rec = Calculator(jp, sp, gemm=gemm, graphs=True)
+    want = eager.compute(systems)
+    got = [rec.compute(systems) for _ in range(5)]
+    assert eager.graph_replays == 0 and rec.graph_replays >= 2
+    for r in got:
+        for k in ("energy", "per_atom_energy", "forces", "virial"):
+            assert (getattr(r, k) == getattr(want, k)).all(), k
+    # other shapes in between do not disturb a recording
+    rec.compute(st.diamond(1))
+    again = rec.compute(systems)
+    assert (again.forces == want.forces).all()
+    eager.close(), rec.close()
+
+
 def test_forces_match_finite_differences_on_device(models, lib_path):
     """tests/test_fd.cpp:61-112 on the CUDA path: analytic forces against central differences of its own energies."""
     from pet_kokkos_b200 import Calculator
