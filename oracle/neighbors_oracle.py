@@ -7,7 +7,10 @@ numpy float64 throughout: Python/numpy never contract a*b+c into an FMA, so the
 distance tests below reproduce the reference's un-contracted arithmetic bit for
 bit when written in the reference's association order.
 
-Parity pins (reference's own model-free tests, restated in tests/):
+Parity pins: the packed list of the reference's own device search, compiled for
+the host (oracle/_ref/libpet_ref.so), equals this module's to the bit -- order,
+vectors, distances, partners (tests/test_reference_pin.py) -- and the reference's
+own model-free tests, restated in tests/:
   tests/test_cell_list.cpp:119-157,192-212  cell list == brute force edge set,
       reproducible order, brute-force order for small structures
   tests/test_neighbors.cpp:52-128           coordination, padding, reverse map

@@ -12,11 +12,16 @@ derivation of the same quantity, folded exactly as the reference folds it
 reference's mixed precision (fp32 network, fp64 geometry and sums);
 dtype=float64 is the rounding-free truth both fp32 paths are compared against.
 
-PARITY UNPINNED for the network numerics: the reference's golden files
-(tests/golden/pet-*.json) need published weights that are not available
-offline and the reference needs Kokkos (absent) to compile, so this restatement
-is pinned only by the model-free vectors (neighbour lists, cutoff values, GEMM
-error bands) and by self-consistency (finite differences, fp64 vs fp32).
+PARITY PINNED against the reference's own code: its unmodified sources are
+compiled for the host (oracle/build_ref.sh -> oracle/_ref/libpet_ref.so, g++
+against the Kokkos stand-in in oracle/kokkos_host/) and this restatement is held
+to that library's Calculator::compute, compute_edges and set_neighbors +
+compute_step outputs -- live in tests/test_reference_pin.py, and through the ref_*
+arrays of the committed fixtures (tests/golden/*.npz, written by
+tests/golden/make_golden.py from that library) where the library is not present.
+The reference's golden files (tests/golden/pet-*.json) need published weights
+that are not available offline; random-initialised checkpoints in the
+reference's file format, read by both sides, take their place.
 """
 from __future__ import annotations
 

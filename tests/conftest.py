@@ -40,6 +40,16 @@ def models(tmp_path_factory):
 
 
 @pytest.fixture(scope="session")
+def reference():
+    """The reference's own evaluator compiled for the host (oracle/reference_lib.py): built here when a checkout
+    of the reference is at hand, used prebuilt otherwise, and the test skipped where there is neither."""
+    from oracle import reference_lib
+    if not reference_lib.build():
+        pytest.skip("the reference library is not built and no reference checkout is present")
+    return reference_lib
+
+
+@pytest.fixture(scope="session")
 def has_gpu():
     import torch
     return torch.cuda.is_available()

@@ -44,6 +44,8 @@ def test_goldens(name, tmp_path, lib_path):
     # forces here are O(10) eV/A for the "scaled" models: the absolute band is scaled accordingly
     scale = max(1.0, np.abs(g["forces"]).max())
     check(r, {k: g[k] for k in ("energy", "per_atom_energy", "forces", "virial")}, f_abs=F_ABS * scale)
+    # and against the reference's own outputs on the same files (ref_*: Calculator::compute of the reference)
+    check(r, {k: g["ref_" + k] for k in ("energy", "per_atom_energy", "forces", "virial")}, f_abs=F_ABS * scale)
     assert c.last_shapes()[1] == int(g["n_edges"]) and c.last_shapes()[2] == int(g["max_neighbors"])
     c.close()
 

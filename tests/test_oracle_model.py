@@ -72,6 +72,22 @@ def test_oracle_reproduces_goldens(name, tmp_path):
     assert len(r["edges"]["center"]) == int(g["n_edges"])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("name", sorted(make_golden.CASES))
+def test_oracle_matches_the_reference_outputs(name, dtype, tmp_path):
+    """The pin: the restatement against what the reference's own Calculator::compute returned on the same
+    files and structures (ref_* in the fixtures, recorded by tests/golden/make_golden.py from the reference
+    compiled for the host). Bands: energy 1e-6 relative, forces 1e-5 eV/A per eV/A of force scale, virial
+    1e-5 of its scale."""
+    g = np.load(GOLDEN / f"{name}.npz")
+    jp, sp, meta, tens, systems = make_golden.build_case(name, tmp_path)
+    r = po.evaluate(meta, tens, systems, dtype=dtype)
+    assert np.abs(r["energy"] - g["ref_energy"]).max() <= 1e-6 * np.abs(g["ref_energy"]).max()
+    assert np.abs(r["per_atom_energy"] - g["ref_per_atom_energy"]).max() <= 1e-6 * np.abs(g["ref_energy"]).max()
+    assert np.abs(r["forces"] - g["ref_forces"]).max() <= 1e-5 * max(1.0, np.abs(g["ref_forces"]).max())
+    assert np.abs(r["virial"] - g["ref_virial"]).max() <= 1e-5 * max(1.0, np.abs(g["ref_virial"]).max())
+
+
 def test_checkpoint_roundtrip(tmp_path):
     """The writer's files read back with the reference's layout: u64 header length, JSON index, F32 data."""
     jp, sp = ck.write_random_checkpoint(tmp_path / "m", "tiny", seed=5)
