@@ -279,6 +279,7 @@ def forward_residual(W: Weights, ed, vec, want=None):
 
     input_edge = W("edge_embedder.weight")[nb_species]
     net = torch.zeros(N, dtype=dt)
+    keep = lambda k, v: want.__setitem__(k, v.detach().clone()) if want is not None else None
     for L in range(G):
         g = f"gnn_layers.{L}"
         z = W(g + ".compress.0@b") + W(g + ".compress.0@tab")[nb_species] + x4 @ W(g + ".compress.0@x4").T
@@ -296,9 +297,13 @@ def forward_residual(W: Weights, ed, vec, want=None):
                         W(t + ".mlp.w_out.weight"), W(t + ".mlp.w_out.bias")) + tok_a
             tokens = ln(s2, t + ".norm_mlp")
         node_feat, edge_feat = tokens[:N], tokens[N:]
+        keep(f"tokens{L}", tokens)
         node_pred, edge_pred = head(node_feat, L, "node"), head(edge_feat, L, "edge")
+        keep(f"node_pred{L}", node_pred)
+        keep(f"edge_pred{L}", edge_pred)
         s = node_pred.double().index_add(0, center, cut.double() * edge_pred.double())
         net = (net.double() + s).to(dt) if L > 0 else s.to(dt)        # readout_accumulate(acc = i > 0)
+        keep(f"net{L}", net)
         if L + 1 < G:                                                  # src/residual.cpp:123-132
             partner = torch.where((rev >= 0)[:, None], edge_feat[rev.clamp(min=0)], torch.zeros_like(edge_feat))
             input_edge = 0.5 * (input_edge + partner)

@@ -8,6 +8,10 @@ namespace petb {
 struct AttnArgs {
   int N = 0, H = 0, hd = 0, S = 0;  // atoms, heads, head_dim, most tokens of any atom (max neighbours + 1)
   float sc = 1.f;                   // 1 / (sqrt(head_dim) * temperature)
+  // How the products run (the reference's AttentionMode, include/pet/gemm.hpp): false = Native, fp32 on the CUDA
+  // cores; true = TF32x3, the split products on the tensor cores (mma.sync), as accurate but for the tensor core's
+  // truncating accumulate.
+  bool tensor = false;
   double pairs = 0.0;               // sum over atoms of tokens^2 (work accounting only)
   double T = 0.0;                   // token rows (work accounting only)
   const int* off = nullptr;         // [N+1] each atom's range of edge rows

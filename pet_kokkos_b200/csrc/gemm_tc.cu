@@ -129,6 +129,15 @@ struct Smem {
   static constexpr int kThreads = X3 ? 512 : 384;
 };
 
+// The low part of the 3xTF32 split. The tensor core reads the top 19 bits of an fp32 operand (sign, exponent, 10
+// mantissa bits) and ignores the rest, so hi(x) is x truncated; x - hi(x) is exact and has up to 13 significant
+// bits, of which the tensor core would again keep the top 11 by truncation -- a bias toward zero that adds up along
+// K. Rounding it to 11 bits here, to nearest even, leaves an unbiased error of 2^-25 of x instead.
+__device__ __forceinline__ float tf32_lo(float x) {
+  const uint32_t r = __float_as_uint(x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u));
+  return __uint_as_float((r + 0x0FFFu + ((r >> 13) & 1u)) & 0xFFFFE000u);
+}
+
 template <int EPI, int BN, int STAGES, bool X3>
 __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
     k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs p, int* err) {
@@ -205,11 +214,13 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
 #pragma unroll
           for (int k = 0; k < TBK / 8; ++k) {  // 8 tf32 = 32 bytes along K per instruction
             const uint64_t da = smem_desc(a0 + 32 * k), db = smem_desc(b0 + 32 * k);
-            mma_tf32(acc, da, db, idesc, (kb | k) != 0);
-            if (X3) {
+            if (X3) {  // the two small cross terms first, then hi.hi on top of them
               const uint64_t dal = smem_desc(a0 + L::kHi + 32 * k), dbl = smem_desc(b0 + L::kHi + 32 * k);
-              mma_tf32(acc, da, dbl, idesc, 1);
+              mma_tf32(acc, da, dbl, idesc, (kb | k) != 0);
               mma_tf32(acc, dal, db, idesc, 1);
+              mma_tf32(acc, da, db, idesc, 1);
+            } else {
+              mma_tf32(acc, da, db, idesc, (kb | k) != 0);
             }
           }
           mma_commit(empty + s);
@@ -285,10 +296,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
         for (int e = tid; e < L::kHi / 16; e += 128) {
           const float4 x = hi[e];
           float4 y;
-          y.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
-          y.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
-          y.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
-          y.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+          y.x = tf32_lo(x.x), y.y = tf32_lo(x.y), y.z = tf32_lo(x.z), y.w = tf32_lo(x.w);
           lo[e] = y;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes visible to the tensor core

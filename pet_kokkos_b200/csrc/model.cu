@@ -167,6 +167,18 @@ Model::~Model() {
 
 namespace {
 
+// The attention mode that goes with a GEMM mode unless PET_ATTN names one (native | tf32x3), as the reference's
+// Options::attention / PET_ATTN (include/pet/calculator.hpp:46-49): Native with native GEMMs, TF32x3 otherwise.
+bool attention_on_tensor_cores(int gemm_mode) {
+  static const int forced = [] {
+    const char* e = std::getenv("PET_ATTN");
+    if (!e) return -1;
+    const std::string v(e);
+    return v == "native" ? 0 : (v == "tf32x3" || v == "3xtf32") ? 1 : -1;
+  }();
+  return forced >= 0 ? forced == 1 : gemm_mode != GEMM_NATIVE;
+}
+
 struct Gemms {
   Stream& st;
   Arena& tmp;
@@ -331,6 +343,7 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
       }
       AttnArgs at;
       at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+      at.tensor = attention_on_tensor_cores(mode);
       at.pairs = pk.pairs, at.T = T;
       at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml;
       attention_forward(st, at);
@@ -471,6 +484,7 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
         gm.linear_bwd(dmerged, tok_adj, mat(tl + ".attention.output_linear.weight"), T, false);
         AttnArgs at;
         at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+      at.tensor = attention_on_tensor_cores(mode);
         at.pairs = pk.pairs, at.T = T;
         at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml, at.dmerged = dmerged, at.qkv_adj = qkv_adj, at.cfh = cfh;
         attention_backward(st, at);
@@ -562,6 +576,7 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
       gm.linear(b.qkv, tokens, mat(tl + ".attention.input_linear.weight"), vec(tl + ".attention.input_linear.bias"), T);
       AttnArgs at;
       at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+      at.tensor = attention_on_tensor_cores(mode);
       at.pairs = pk.pairs, at.T = T;
       at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml;
       attention_forward(st, at);
@@ -597,6 +612,9 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
       gm.linear_silu(eh1, sl.eh1_pre, eh0, mat(eh + ".2.weight"), vec(eh + ".2.bias"), E);
       gemv_rows(st, eh1, Dh, mat(el + ".weight").w, vec(el + ".bias"), sl.edge_pred, E, Dh);
       readout_energy(st, net, per_atom, node_pred, sl.edge_pred, pk, comp_, scale_, L > 0, L + 1 == G);
+      tap(taps, "node_pred" + ls, node_pred, N);
+      tap(taps, "edge_pred" + ls, sl.edge_pred, E);
+      tap(taps, "net" + ls, net, N);
     }
     if (L + 1 < G) message_average(st, input_edge, tokens + size_t(N) * D, pk.reverse, E, D);
   }
@@ -663,6 +681,7 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
         gm.linear_bwd(dmerged, s1_adj, mat(tl + ".attention.output_linear.weight"), T, false);
         AttnArgs at;
         at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+      at.tensor = attention_on_tensor_cores(mode);
         at.pairs = pk.pairs, at.T = T;
         at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml, at.dmerged = dmerged, at.qkv_adj = qkv_adj, at.cfh = cfh;
         attention_backward(st, at);
