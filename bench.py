@@ -40,6 +40,10 @@ os.environ.setdefault("OMP_WAIT_POLICY", "passive")
 
 METRIC = "atom_evals_per_s"
 UNIT = "atom-evals/s"
+# DRAM traffic of one weight-GEMM launch per token row (atoms + kept edges), from one ncu capture:
+# dram__bytes_read.sum + dram__bytes_write.sum averaged over six consecutive k_gemm_tc launches of the water648
+# workload (35.5 MB at 25 320 rows). A GEMM reads A once and writes C once, so it grows with the rows.
+GEMM_DRAM_BYTES_PER_TOKEN_ROW = 35.5e6 / 25320
 MODEL_OF = {"diamond64": "xs", "water648": "s", "diamond1728": "s", "batch512x64": "s", "diamond13824": "l"}
 
 
@@ -260,7 +264,10 @@ def run_ours(args):
                 ach = p["flops"] / (p["ms"] * 1e-3) / 1e12
                 roof = {"kernel": "weight GEMMs with fused epilogues", "bound": "tensor", "achieved": ach,
                         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"],
-                        "peak_source": f"{peaks['source']} cuBLAS bf16, sustained", "traffic": None,
+                        "peak_source": f"{peaks['source']} cuBLAS bf16, sustained",
+                        "traffic": GEMM_DRAM_BYTES_PER_TOKEN_ROW * (n_act + n_edges),
+                        "traffic_source": "ncu dram bytes per launch on water648 (profiles/k_gemm_tc_water648_s_3xtf32.md), "
+                                          "scaled by token rows",
                         "launches": p["launches"], "avg_launch_ms": per_launch_ms}
             else:
                 ach = p["bytes"] / (p["ms"] * 1e-3) / 1e9

@@ -132,10 +132,11 @@ struct Smem {
 // The low part of the 3xTF32 split. The tensor core reads the top 19 bits of an fp32 operand (sign, exponent, 10
 // mantissa bits) and ignores the rest, so hi(x) is x truncated; x - hi(x) is exact and has up to 13 significant
 // bits, of which the tensor core would again keep the top 11 by truncation -- a bias toward zero that adds up along
-// K. Rounding it to 11 bits here, to nearest even, leaves an unbiased error of 2^-25 of x instead.
+// K. Adding half of the last kept bit here makes that truncation a rounding to nearest (ties away from zero, one
+// case in 8192), which leaves an unbiased error of 2^-25 of x instead; the add carries into the exponent when the
+// mantissa overflows, as rounding should, and a zero remainder stays below the kept bits.
 __device__ __forceinline__ float tf32_lo(float x) {
-  const uint32_t r = __float_as_uint(x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u));
-  return __uint_as_float((r + 0x0FFFu + ((r >> 13) & 1u)) & 0xFFFFE000u);
+  return __uint_as_float(__float_as_uint(x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u)) + 0x1000u);
 }
 
 template <int EPI, int BN, int STAGES, bool X3>
@@ -292,7 +293,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
         if (!(ok = mbar_wait(full + s, (g / STAGES) & 1, abort_flag))) break;
         const float4* hi = reinterpret_cast<const float4*>(tiles + size_t(s) * L::kStage);
         float4* lo = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage + L::kHi);
-#pragma unroll 4
+#pragma unroll 8
         for (int e = tid; e < L::kHi / 16; e += 128) {
           const float4 x = hi[e];
           float4 y;
