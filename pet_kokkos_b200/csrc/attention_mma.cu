@@ -36,10 +36,13 @@ __device__ __forceinline__ float warp_sum(float v) {
 struct Frag {
   uint32_t hi, lo;
 };
+// x = hi + lo with hi the leading 11 significant bits of x (truncated) and lo the remainder rounded to 11 bits
+// (half of the last kept bit added, then masked). Integer and fp32-add instructions only: cvt.rna.tf32 runs on the
+// quarter-rate conversion pipe, which two conversions per operand element had saturated.
 __device__ __forceinline__ Frag split(float x) {
   Frag f;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(f.hi) : "f"(x));
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(f.lo) : "f"(x - __uint_as_float(f.hi)));
+  f.hi = __float_as_uint(x) & 0xFFFFE000u;
+  f.lo = (__float_as_uint(x - __uint_as_float(f.hi)) + 0x1000u) & 0xFFFFE000u;
   return f;
 }
 __device__ __forceinline__ void mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -53,6 +56,27 @@ __device__ __forceinline__ void mma3(float* c, const Frag* a, const Frag& b0, co
   mma(c, a[0].lo, a[1].lo, a[2].lo, a[3].lo, b0.hi, b1.hi);
   mma(c, a[0].hi, a[1].hi, a[2].hi, a[3].hi, b0.lo, b1.lo);
   mma(c, a[0].hi, a[1].hi, a[2].hi, a[3].hi, b0.hi, b1.hi);
+}
+// The same for G independent accumulators that share the A operand, one term at a time: consecutive
+// instructions never depend on each other, so the tensor pipe's latency is covered inside one warp.
+template <int G>
+__device__ __forceinline__ void mma3_shared_a(float (*c)[4], const Frag* a, const Frag (*b)[2]) {
+#pragma unroll
+  for (int j = 0; j < G; ++j) mma(c[j], a[0].lo, a[1].lo, a[2].lo, a[3].lo, b[j][0].hi, b[j][1].hi);
+#pragma unroll
+  for (int j = 0; j < G; ++j) mma(c[j], a[0].hi, a[1].hi, a[2].hi, a[3].hi, b[j][0].lo, b[j][1].lo);
+#pragma unroll
+  for (int j = 0; j < G; ++j) mma(c[j], a[0].hi, a[1].hi, a[2].hi, a[3].hi, b[j][0].hi, b[j][1].hi);
+}
+// The same for two accumulators with their own A operands (two products that run side by side).
+__device__ __forceinline__ void mma3_pair(float* c0, const Frag* a0, const Frag& p0, const Frag& p1, float* c1, const Frag* a1,
+                                          const Frag& r0, const Frag& r1) {
+  mma(c0, a0[0].lo, a0[1].lo, a0[2].lo, a0[3].lo, p0.hi, p1.hi);
+  mma(c1, a1[0].lo, a1[1].lo, a1[2].lo, a1[3].lo, r0.hi, r1.hi);
+  mma(c0, a0[0].hi, a0[1].hi, a0[2].hi, a0[3].hi, p0.lo, p1.lo);
+  mma(c1, a1[0].hi, a1[1].hi, a1[2].hi, a1[3].hi, r0.lo, r1.lo);
+  mma(c0, a0[0].hi, a0[1].hi, a0[2].hi, a0[3].hi, p0.hi, p1.hi);
+  mma(c1, a1[0].hi, a1[1].hi, a1[2].hi, a1[3].hi, r0.hi, r1.hi);
 }
 
 __host__ __device__ inline int round16(int s) { return (s + 15) / 16 * 16; }
@@ -88,19 +112,20 @@ __device__ __forceinline__ void load_a(Frag (*f)[4], const float* x, int r0, int
 
 template <int HD, int MAXKB>
 __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k_attn_fwd_mma(AttnArgs p) {
-  constexpr int P = HD + 4, KS = HD / 8;
+  constexpr int P = HD + 4, KS = HD / 8, R = 8 * MAXKB;  // R: staged token rows, the kernel's most (zero past the atom's)
+  constexpr int G = MAXKB % 5 == 0 ? 5 : (MAXKB % 4 == 0 ? 4 : 2);  // key blocks whose score tiles advance together
   extern __shared__ __align__(16) float smem[];
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H, D = p.H * HD;
   const int e0 = p.off[n], cnt = p.off[n + 1] - e0 + 1;
-  const int S16 = round16(cnt), nkb = S16 / 8, SM = round16(p.S);
+  const int S16 = round16(cnt), nkb = S16 / 8;
   float* sq = smem;
-  float* sk = sq + SM * P;
-  float* sv = sk + SM * P;
-  float* slc = sv + SM * P;
+  float* sk = sq + R * P;
+  float* sv = sk + R * P;
+  float* slc = sv + R * P;
   stage<HD>(sq, p.qkv, 3 * size_t(D), h * HD, n, p.N, e0, cnt, S16);
-  stage<HD>(sk, p.qkv, 3 * size_t(D), D + h * HD, n, p.N, e0, cnt, S16);
-  stage<HD>(sv, p.qkv, 3 * size_t(D), 2 * D + h * HD, n, p.N, e0, cnt, S16);
-  for (int r = threadIdx.x; r < S16; r += blockDim.x) {
+  stage<HD>(sk, p.qkv, 3 * size_t(D), D + h * HD, n, p.N, e0, cnt, R);
+  stage<HD>(sv, p.qkv, 3 * size_t(D), 2 * D + h * HD, n, p.N, e0, cnt, R);
+  for (int r = threadIdx.x; r < R; r += blockDim.x) {
     const float cf = r == 0 ? 1.0f : (r < cnt ? p.cut[e0 + r - 1] : 0.f);
     slc[r] = cf > 0.f ? __logf(cf) : kOff;
   }
@@ -113,13 +138,19 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
   load_a<HD>(qf, sq, r0, g, t);
   float s[MAXKB][4];
 #pragma unroll
-  for (int kb = 0; kb < MAXKB; ++kb) {
-    s[kb][0] = s[kb][1] = s[kb][2] = s[kb][3] = 0.f;
-    if (kb < nkb) {
+  for (int kb = 0; kb < MAXKB; ++kb) s[kb][0] = s[kb][1] = s[kb][2] = s[kb][3] = 0.f;
+#pragma unroll
+  for (int kg = 0; kg < MAXKB; kg += G) {
+    if (kg < nkb) {  // the same for the whole CTA; a group's blocks past the atom's keys read zero rows
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
-        const Frag b0 = split(sk[(8 * kb + g) * P + 8 * ks + t]), b1 = split(sk[(8 * kb + g) * P + 8 * ks + t + 4]);
-        mma3(s[kb], qf[ks], b0, b1);
+        Frag b[G][2];
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          b[j][0] = split(sk[(8 * (kg + j) + g) * P + 8 * ks + t]);
+          b[j][1] = split(sk[(8 * (kg + j) + g) * P + 8 * ks + t + 4]);
+        }
+        mma3_shared_a<G>(&s[kg], qf[ks], b);
       }
     }
   }
@@ -163,11 +194,13 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
   for (int kb = 0; kb < MAXKB; ++kb)
     if (kb < nkb) {
       const Frag a[4] = {split(s[kb][0] * il0), split(s[kb][2] * il1), split(s[kb][1] * il0), split(s[kb][3] * il1)};
+      Frag b[KS][2];
 #pragma unroll
       for (int db = 0; db < KS; ++db) {
-        const Frag b0 = split(sv[(8 * kb + 2 * t) * P + 8 * db + g]), b1 = split(sv[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
-        mma3(o[db], a, b0, b1);
+        b[db][0] = split(sv[(8 * kb + 2 * t) * P + 8 * db + g]);
+        b[db][1] = split(sv[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
       }
+      mma3_shared_a<KS>(o, a, b);
     }
   const size_t g0 = q0 == 0 ? size_t(n) : size_t(p.N) + e0 + q0 - 1, g1 = size_t(p.N) + e0 + q1 - 1;
 #pragma unroll
@@ -243,9 +276,8 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
         const Frag k0 = split(sk[(8 * kb + g) * P + 8 * ks + t]), k1 = split(sk[(8 * kb + g) * P + 8 * ks + t + 4]);
-        mma3(cs, qf[ks], k0, k1);
         const Frag v0 = split(sv[(8 * kb + g) * P + 8 * ks + t]), v1 = split(sv[(8 * kb + g) * P + 8 * ks + t + 4]);
-        mma3(cp, gf[ks], v0, v1);
+        mma3_pair(cs, qf[ks], k0, k1, cp, gf[ks], v0, v1);
       }
       const int key = 8 * kb + 2 * t;
       const float lc0 = slc[key], lc1 = slc[key + 1];
@@ -254,11 +286,13 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
       const float P2 = (il1 > 0.f && !is_off(lc0)) ? __expf(cs[2] * p.sc + lc0 - m1) * il1 : 0.f;
       const float P3 = (il1 > 0.f && !is_off(lc1)) ? __expf(cs[3] * p.sc + lc1 - m1) * il1 : 0.f;
       const Frag a[4] = {split(P0 * (cp[0] - dq0)), split(P2 * (cp[2] - dq1)), split(P1 * (cp[1] - dq0)), split(P3 * (cp[3] - dq1))};
+      Frag b[KS][2];
 #pragma unroll
       for (int db = 0; db < KS; ++db) {
-        const Frag b0 = split(sk[(8 * kb + 2 * t) * P + 8 * db + g]), b1 = split(sk[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
-        mma3(dq[db], a, b0, b1);
+        b[db][0] = split(sk[(8 * kb + 2 * t) * P + 8 * db + g]);
+        b[db][1] = split(sk[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
       }
+      mma3_shared_a<KS>(dq, a, b);
     }
 #pragma unroll
     for (int db = 0; db < KS; ++db) {
@@ -284,9 +318,8 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
         const Frag q0 = split(sq[(8 * qb + g) * P + 8 * ks + t]), q1 = split(sq[(8 * qb + g) * P + 8 * ks + t + 4]);
-        mma3(cs, kf[ks], q0, q1);
         const Frag d0 = split(sg[(8 * qb + g) * P + 8 * ks + t]), d1 = split(sg[(8 * qb + g) * P + 8 * ks + t + 4]);
-        mma3(cp, vf[ks], d0, d1);
+        mma3_pair(cs, kf[ks], q0, q1, cp, vf[ks], d0, d1);
       }
       const int qa = 8 * qb + 2 * t, qc = qa + 1;  // this lane's two queries of the block
       const float ma = sm[qa], mc = sm[qc], ila = sl[qa], ilc = sl[qc], da = sd[qa], dc = sd[qc];
@@ -298,12 +331,17 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
       cf0 += S0 + S1, cf1 += S2 + S3;
       const Frag as[4] = {split(S0), split(S2), split(S1), split(S3)};
       const Frag ap[4] = {split(P0), split(P2), split(P1), split(P3)};
+      {
+        Frag b[KS][2];
 #pragma unroll
-      for (int db = 0; db < KS; ++db) {
-        const Frag b0 = split(sq[qa * P + 8 * db + g]), b1 = split(sq[qc * P + 8 * db + g]);
-        mma3(dk[db], as, b0, b1);
-        const Frag d0 = split(sg[qa * P + 8 * db + g]), d1 = split(sg[qc * P + 8 * db + g]);
-        mma3(dv[db], ap, d0, d1);
+        for (int db = 0; db < KS; ++db) b[db][0] = split(sq[qa * P + 8 * db + g]), b[db][1] = split(sq[qc * P + 8 * db + g]);
+        mma3_shared_a<KS>(dk, as, b);
+      }
+      {
+        Frag b[KS][2];
+#pragma unroll
+        for (int db = 0; db < KS; ++db) b[db][0] = split(sg[qa * P + 8 * db + g]), b[db][1] = split(sg[qc * P + 8 * db + g]);
+        mma3_shared_a<KS>(dv, ap, b);
       }
     }
     cf0 += __shfl_xor_sync(0xffffffffu, cf0, 1), cf0 += __shfl_xor_sync(0xffffffffu, cf0, 2);
@@ -335,9 +373,9 @@ bool enabled() {
   return on;
 }
 
-size_t fwd_bytes(int S, int HD) {
-  const int SM = round16(S);
-  return sizeof(float) * (3 * size_t(SM) * (HD + 4) + SM);
+size_t fwd_bytes(int maxkb, int HD) {
+  const int R = 8 * maxkb;
+  return sizeof(float) * (3 * size_t(R) * (HD + 4) + R);
 }
 size_t bwd_bytes(int S, int HD) {
   const int SM = round16(S);
@@ -357,13 +395,11 @@ void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, int threads, 
 template <int HD>
 bool fwd_hd(Stream& st, const AttnArgs& p) {
   const int S16 = round16(p.S), threads = 32 * (S16 / 16);
-  const size_t bytes = fwd_bytes(p.S, HD);
-  if (bytes > 200 * 1024) return false;
+  if (S16 > 176 || fwd_bytes(22, HD) > 200 * 1024) return false;
   static int o10 = 48 * 1024, o16 = 48 * 1024, o22 = 48 * 1024;
-  if (S16 <= 80) launch(st, k_attn_fwd_mma<HD, 10>, p, bytes, threads, &o10);
-  else if (S16 <= 128) launch(st, k_attn_fwd_mma<HD, 16>, p, bytes, threads, &o16);
-  else if (S16 <= 176) launch(st, k_attn_fwd_mma<HD, 22>, p, bytes, threads, &o22);
-  else return false;
+  if (S16 <= 80) launch(st, k_attn_fwd_mma<HD, 10>, p, fwd_bytes(10, HD), threads, &o10);
+  else if (S16 <= 128) launch(st, k_attn_fwd_mma<HD, 16>, p, fwd_bytes(16, HD), threads, &o16);
+  else launch(st, k_attn_fwd_mma<HD, 22>, p, fwd_bytes(22, HD), threads, &o22);
   return true;
 }
 template <int HD>
