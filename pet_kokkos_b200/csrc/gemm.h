@@ -35,6 +35,9 @@ struct GemmArgs {
   int lda = 0;
   const float* B = nullptr;  // [N,K]
   int ldb = 0;
+  // Non-zero: B + b_lo_offset holds the low parts of B's 3xTF32 split, computed once when the weights were loaded
+  // (same shape and pitch); the tensor-core kernel then loads them instead of splitting every B tile it stages.
+  size_t b_lo_offset = 0;
   float* C = nullptr;        // [M, N] (EPI_SWIGLU: [M,N/2]; EPI_SWIGLU_BWD: [M,2N])
   int ldc = 0;
   int M = 0, N = 0, K = 0;

@@ -141,7 +141,8 @@ __device__ __forceinline__ float tf32_lo(float x) {
 
 template <int EPI, int BN, int STAGES, bool X3>
 __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
-    k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs p, int* err) {
+    k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              const __grid_constant__ CUtensorMap map_blo, GemmArgs p, int* err) {
   using L = Smem<BN, STAGES, X3>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -191,9 +192,11 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
           const int s = g % STAGES;
           if (!(ok = mbar_wait(empty + s, ((g / STAGES) & 1) ^ 1, abort_flag))) break;
           uint8_t* sa = tiles + size_t(s) * L::kStage;
-          mbar_expect_tx(full + s, L::kHi);
+          const bool b_lo = X3 && p.b_lo_offset != 0;  // B's low parts come from memory, not from the splitter
+          mbar_expect_tx(full + s, L::kHi + (b_lo ? L::kB : 0));
           tma_load_2d(sa, &map_a, full + s, kb * TBK, m0);
           tma_load_2d(sa + L::kA, &map_b, full + s, kb * TBK, n0);
+          if (b_lo) tma_load_2d(sa + L::kHi + L::kA, &map_blo, full + s, kb * TBK, n0);
         }
         if (!ok) break;
       }
@@ -285,6 +288,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
     // lo = x - hi(x), written beside the stage's tiles at the same swizzled positions, so the same
     // descriptors, offset by the size of the hi tiles, address them.
     const int tid = threadIdx.x - kSplitWarp0 * 32;
+    const int n16 = (p.b_lo_offset != 0 ? L::kA : L::kHi) / 16;  // 16-byte pieces to split: A's, and B's unless they came split
     int g = 0;
     bool ok = true;
     for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
@@ -294,7 +298,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
         const float4* hi = reinterpret_cast<const float4*>(tiles + size_t(s) * L::kStage);
         float4* lo = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage + L::kHi);
 #pragma unroll 8
-        for (int e = tid; e < L::kHi / 16; e += 128) {
+        for (int e = tid; e < n16; e += 128) {
           const float4 x = hi[e];
           float4 y;
           y.x = tf32_lo(x.x), y.y = tf32_lo(x.y), y.z = tf32_lo(x.z), y.w = tf32_lo(x.w);
@@ -375,9 +379,10 @@ void launch_tc(Stream& st, const GemmArgs& a) {
     opted = true;
   }
   const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM), mb = make_map(a.B, a.N, a.K, a.ldb, BN);
+  const CUtensorMap mblo = a.b_lo_offset ? make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, BN) : mb;
   const long long tiles = (long long) cdiv(a.M, TBM) * cdiv(a.N, BN);
   const int grid = int(tiles < state().sms ? tiles : state().sms);
-  kernel<<<grid, L::kThreads, L::kTotal, st.s>>>(ma, mb, a, state().err);
+  kernel<<<grid, L::kThreads, L::kTotal, st.s>>>(ma, mb, mblo, a, state().err);
   PETB_LAUNCH_CHECK(st);
 }
 

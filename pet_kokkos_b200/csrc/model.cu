@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstring>
 
 #include "attention.h"
 #include "gemm.h"
@@ -14,19 +15,32 @@ using Taps = std::map<std::string, std::pair<const float*, size_t>>;
 // ---- weights -----------------------------------------------------------------
 
 void Model::put_mat(const std::string& name, int rows, int cols, const double* d) {
-  std::vector<float> w(size_t(rows) * cols), wt(size_t(rows) * cols);
+  // Both orientations, then the low parts of their 3xTF32 split (x minus its leading 11 significant bits, with half
+  // of the last bit the tensor core keeps added so that its truncation rounds): [w | wt | w_lo | wt_lo].
+  const size_t n = size_t(rows) * cols;
+  std::vector<float> w(4 * n);
   for (int a = 0; a < rows; ++a)
     for (int b = 0; b < cols; ++b) {
       const float v = float(d[size_t(a) * cols + b]);
       w[size_t(a) * cols + b] = v;
-      wt[size_t(b) * rows + a] = v;
+      w[n + size_t(b) * rows + a] = v;
     }
+  for (size_t i = 0; i < 2 * n; ++i) {
+    uint32_t bits, lo;
+    std::memcpy(&bits, &w[i], 4);
+    bits &= 0xFFFFE000u;
+    float hi;
+    std::memcpy(&hi, &bits, 4);
+    const float r = w[i] - hi;
+    std::memcpy(&lo, &r, 4);
+    lo += 0x1000u;
+    std::memcpy(&w[2 * n + i], &lo, 4);
+  }
   float* dev = nullptr;
-  PETB_CUDA(cudaMalloc(&dev, 2 * w.size() * sizeof(float)));
+  PETB_CUDA(cudaMalloc(&dev, w.size() * sizeof(float)));
   owned_.push_back(dev);
   PETB_CUDA(cudaMemcpy(dev, w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice));
-  PETB_CUDA(cudaMemcpy(dev + w.size(), wt.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice));
-  mat_[name] = Mat{dev, dev + w.size(), rows, cols};
+  mat_[name] = Mat{dev, dev + n, rows, cols, 2 * n};
 }
 
 void Model::put_vec(const std::string& name, int len, const double* d) {
@@ -188,42 +202,42 @@ struct Gemms {
   void linear(float* out, const float* in, const Mat& W, const float* bias, int M, const float* res = nullptr,
               int res_row0 = 0) const {
     GemmArgs a;
-    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.C = out, a.ldc = W.rows;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.C = out, a.ldc = W.rows;
     a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.res = res, a.ldr = W.rows, a.res_row0 = res_row0;
     gemm(st, tmp, a, mode);
   }
   // out = silu(pre), pre = in . W^T + bias, kept when `pre` is given
   void linear_silu(float* out, float* pre, const float* in, const Mat& W, const float* bias, int M) const {
     GemmArgs a;
-    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.C = out, a.ldc = W.rows;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.C = out, a.ldc = W.rows;
     a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.pre = pre, a.ldp = W.rows, a.epi = EPI_SILU;
     gemm(st, tmp, a, mode);
   }
   // pre[M, 2F] = in . W^T + bias (interleaved v, g); h[M, F] = v * sigmoid(g)
   void swiglu_in(float* h, float* pre, const float* in, const Mat& W, const float* bias, int M) const {
     GemmArgs a;
-    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.C = h, a.ldc = W.rows / 2;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.C = h, a.ldc = W.rows / 2;
     a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.pre = pre, a.ldp = W.rows, a.epi = EPI_SWIGLU;
     gemm(st, tmp, a, mode);
   }
   // in_adj[M, W.cols] (+)= out_adj[M, W.rows] . W
   void linear_bwd(float* in_adj, const float* out_adj, const Mat& W, int M, bool acc) const {
     GemmArgs a;
-    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.C = in_adj, a.ldc = W.cols;
+    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.b_lo_offset = W.lo_off, a.C = in_adj, a.ldc = W.cols;
     a.M = M, a.N = W.cols, a.K = W.rows, a.res = acc ? in_adj : nullptr, a.ldr = W.cols;
     gemm(st, tmp, a, mode);
   }
   // grad[M, W.cols] = (out_adj . W) * silu'(pre)
   void linear_silu_bwd(float* grad, const float* out_adj, const Mat& W, const float* pre, int M) const {
     GemmArgs a;
-    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.C = grad, a.ldc = W.cols;
+    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.b_lo_offset = W.lo_off, a.C = grad, a.ldc = W.cols;
     a.M = M, a.N = W.cols, a.K = W.rows, a.pre = const_cast<float*>(pre), a.ldp = W.cols, a.epi = EPI_SILU_BWD;
     gemm(st, tmp, a, mode);
   }
   // pre_adj[M, 2F] from h_adj = out_adj . W_out and the saved pre
   void swiglu_out_bwd(float* pre_adj, const float* out_adj, const Mat& w_out, const float* pre, int M) const {
     GemmArgs a;
-    a.A = out_adj, a.lda = w_out.rows, a.B = w_out.wt, a.ldb = w_out.rows, a.C = pre_adj, a.ldc = 2 * w_out.cols;
+    a.A = out_adj, a.lda = w_out.rows, a.B = w_out.wt, a.ldb = w_out.rows, a.b_lo_offset = w_out.lo_off, a.C = pre_adj, a.ldc = 2 * w_out.cols;
     a.M = M, a.N = w_out.cols, a.K = w_out.rows, a.pre = const_cast<float*>(pre), a.ldp = 2 * w_out.cols;
     a.epi = EPI_SWIGLU_BWD;
     gemm(st, tmp, a, mode);
@@ -308,7 +322,7 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
       } else {
         const Mat& wi = mat(c0 + "@in");
         GemmArgs a;
-        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
+        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.b_lo_offset = wi.lo_off, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
         a.bias = vec(c0 + "@b"), a.pre = sl.cpre, a.ldp = D, a.tab = mat(c0 + "@tab").w, a.sp = pk.species;
         a.wx = mat(c0 + "@x4").w, a.vec = pk.vec, a.dist = pk.dist, a.epi = EPI_COMPRESS;
         gemm(st, tmp, a, mode);
@@ -556,7 +570,7 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
       } else {
         const Mat& wi = mat(c0 + "@in");
         GemmArgs a;
-        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
+        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.b_lo_offset = wi.lo_off, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
         a.bias = vec(c0 + "@b"), a.pre = sl.cpre, a.ldp = D, a.tab = mat(c0 + "@tab").w, a.sp = pk.species;
         a.wx = mat(c0 + "@x4").w, a.vec = pk.vec, a.dist = pk.dist, a.epi = EPI_COMPRESS;
         gemm(st, tmp, a, mode);

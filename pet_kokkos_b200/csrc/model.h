@@ -22,6 +22,7 @@ struct Mat {
   const float* w = nullptr;
   const float* wt = nullptr;
   int rows = 0, cols = 0;
+  size_t lo_off = 0;  // w + lo_off and wt + lo_off: the low parts of the 3xTF32 split of w and wt
 };
 
 struct PassOut {
