@@ -25,6 +25,7 @@
 // tensor-memory release.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "epilogue.cuh"
@@ -33,7 +34,7 @@ namespace petb {
 
 namespace {
 
-constexpr int TBM = 128, TBK = 32;  // rows per tile; fp32 elements per 128-byte swizzled row
+constexpr int TBM = 128;  // rows per tile
 constexpr int kEpiWarp0 = 4, kEpiWarps = 8, kSplitWarp0 = 12;
 constexpr int kPad = 32;            // floats per row of an epilogue warp's 32 x 32 pad (16-byte slots XOR-swizzled by row)
 constexpr unsigned long long kSpinLimit = 1ull << 31;  // clock64 ticks (~1 s) before a wait gives up
@@ -82,9 +83,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address >> 4 in bits 0-13,
 // leading byte offset (unused for swizzled K-major: 1) in 16-29, stride byte offset (1024 B between
 // 8-row groups) >> 4 in 32-45, descriptor version 1 in 46-47, layout type 2 (SWIZZLE_128B) in 61-63.
+// With 16 fp32 per row (64-byte rows, 64-byte swizzle) the 8-row groups are 512 B apart and the layout type is 4.
+template <int BK>
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  return uint64_t((addr & 0x3FFFF) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
-         (uint64_t(2) << 61);
+  constexpr uint64_t sbo = BK == 32 ? 1024 : 512, layout = BK == 32 ? 2 : 4;
+  return uint64_t((addr & 0x3FFFF) >> 4) | (uint64_t(1) << 16) | (uint64_t(sbo >> 4) << 32) | (uint64_t(1) << 46) | (layout << 61);
 }
 // Instruction descriptor, kind::tf32: D fp32 (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2), both
 // K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
@@ -120,7 +123,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 
 template <int BN, int STAGES, bool X3>
 struct Smem {
-  static constexpr int kA = TBM * TBK * 4, kB = BN * TBK * 4;  // bytes per stage
+  // fp32 elements of K per stage: a 128-byte swizzled row, or half of one where four stages of the widest 3x tile
+  // have to fit (finer stages hide the load latency that two coarse ones cannot)
+  static constexpr int BK = (X3 && BN == 256 && STAGES == 4) ? 16 : 32;
+  static constexpr int kA = TBM * BK * 4, kB = BN * BK * 4;  // bytes per stage
   static constexpr int kHi = kA + kB;
   static constexpr int kStage = kHi * (X3 ? 2 : 1);            // with the lo tiles in the 3x mode
   static constexpr int kTiles = STAGES * kStage;
@@ -158,6 +164,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + TBM - 1) / TBM;
   const int n_tiles = tiles_m * tiles_n;
+  constexpr int TBK = L::BK;
   const int nkb = (p.K + TBK - 1) / TBK;
 
   if (threadIdx.x == 0) {
@@ -217,9 +224,9 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
           const uint32_t a0 = smem_u32(tiles + size_t(s) * L::kStage), b0 = a0 + L::kA;
 #pragma unroll
           for (int k = 0; k < TBK / 8; ++k) {  // 8 tf32 = 32 bytes along K per instruction
-            const uint64_t da = smem_desc(a0 + 32 * k), db = smem_desc(b0 + 32 * k);
+            const uint64_t da = smem_desc<TBK>(a0 + 32 * k), db = smem_desc<TBK>(b0 + 32 * k);
             if (X3) {  // the two small cross terms first, then hi.hi on top of them
-              const uint64_t dal = smem_desc(a0 + L::kHi + 32 * k), dbl = smem_desc(b0 + L::kHi + 32 * k);
+              const uint64_t dal = smem_desc<TBK>(a0 + L::kHi + 32 * k), dbl = smem_desc<TBK>(b0 + L::kHi + 32 * k);
               mma_tf32(acc, da, dbl, idesc, (kb | k) != 0);
               mma_tf32(acc, dal, db, idesc, 1);
               mma_tf32(acc, da, db, idesc, 1);
@@ -355,14 +362,15 @@ TensorState& state() {
 
 // A [rows, K] fp32 row-major matrix as a 2-D tensor map with a 32 x box_rows box, 128-byte swizzle,
 // zero fill outside the matrix.
-CUtensorMap make_map(const float* base, int rows, int K, int ld, int box_rows) {
+CUtensorMap make_map(const float* base, int rows, int K, int ld, int box_rows, int bk) {
   CUtensorMap m;
   const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
   const cuuint64_t strides[1] = {cuuint64_t(ld) * 4};
-  const cuuint32_t box[2] = {TBK, cuuint32_t(box_rows)};
+  const cuuint32_t box[2] = {cuuint32_t(bk), cuuint32_t(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = state().encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) throw Error(5, "gemm: cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
   return m;
@@ -378,12 +386,22 @@ void launch_tc(Stream& st, const GemmArgs& a) {
     PETB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     opted = true;
   }
-  const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM), mb = make_map(a.B, a.N, a.K, a.ldb, BN);
-  const CUtensorMap mblo = a.b_lo_offset ? make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, BN) : mb;
+  const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM, L::BK), mb = make_map(a.B, a.N, a.K, a.ldb, BN, L::BK);
+  const CUtensorMap mblo = a.b_lo_offset ? make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, BN, L::BK) : mb;
   const long long tiles = (long long) cdiv(a.M, TBM) * cdiv(a.N, BN);
   const int grid = int(tiles < state().sms ? tiles : state().sms);
   kernel<<<grid, L::kThreads, L::kTotal, st.s>>>(ma, mb, mblo, a, state().err);
   PETB_LAUNCH_CHECK(st);
+}
+
+// The widest 3x tile runs four 16-column stages (64-byte swizzle) rather than two 32-column ones: the same bytes in
+// flight, handed over in finer pieces (2 % faster on the 1728-atom benchmark). PET_GEMM_FINE=0 picks the coarse form.
+bool fine_stages() {
+  static const bool on = [] {
+    const char* e = std::getenv("PET_GEMM_FINE");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 template <int EPI>
@@ -398,7 +416,7 @@ void dispatch_tc(Stream& st, const GemmArgs& a, int mode) {
   else if (a.N % 128 == 0 && mt * (a.N / 128) >= sms) bn = 128;
   else if (a.N % 64 != 0) bn = a.N % 256 == 0 ? 256 : 128;  // ragged widths: a wide tile with a zero-filled edge
   if (bn == 256) {
-    if (x3) return launch_tc<EPI, 256, 2, true>(st, a);
+    if (x3) return fine_stages() ? launch_tc<EPI, 256, 4, true>(st, a) : launch_tc<EPI, 256, 2, true>(st, a);
     return launch_tc<EPI, 256, 4, false>(st, a);
   }
   if (bn == 128) {
