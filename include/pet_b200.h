@@ -77,6 +77,24 @@ typedef struct pet_results {
   double* edge_gradient;    /* [n_pairs * 3] */
 } pet_results;
 
+/* pet::Exchange (include/pet/exchange.hpp:19-41): what an engine supplies when it runs PET over several
+ * ranks with ghosts only one cutoff deep. Ghosts then have no pairs of their own; an edge from an owned atom to a
+ * ghost reads its partner edge's row from the rank that owns the ghost, once per message-passing layer in the
+ * forward and once in the backward. Every pointer handed to the callbacks is a DEVICE pointer; `stream` is the
+ * calculator's cudaStream_t. A callback either enqueues its transfers on that stream (NCCL send/recv, peer
+ * copies) or synchronizes it, does the transfer its own way and returns once `in` is filled. Every rank makes the
+ * same sequence of calls, also with n_live = 0. Return 0, or non-zero to fail the evaluation.
+ * (atoms_forward / atoms_reverse of the reference serve the adaptive cutoff, which this path does not have.) */
+typedef struct pet_exchange {
+  void* user;
+  /* Exchange::set_live: once per evaluation, the kept edges to ghosts: live[n_live], ascending indices into the
+   * list's owned-atom -> ghost pairs counted in list order (atom by atom, each atom's pairs in turn). */
+  int (*set_live)(void* user, const int* live, int n_live, void* stream);
+  /* Exchange::edges: out[n_live * width] holds one row per live edge, in set_live's order; send each to the rank
+   * owning that ghost and fill in[n_live * width] with the partner edges' rows in the same order. */
+  int (*edges)(void* user, const float* out, float* in, int n_live, int width, void* stream);
+} pet_exchange;
+
 /* pet::EdgeListView (include/pet/device_geometry.hpp:93-110): an MD engine's own
  * neighbour list. n_local < 0: every atom is owned. */
 typedef struct pet_edge_list {
@@ -88,6 +106,7 @@ typedef struct pet_edge_list {
   const int* shifts;            /* [offsets[n_atoms] * 3], optional */
   const double* cell;           /* [9], with shifts           */
   int half;
+  const pet_exchange* exchange; /* EdgeListView::exchange; null: one rank, or ghosts ghost_cutoff deep. A full list. */
 } pet_edge_list;
 
 /* Calculator::DeviceArrays / Totals (calculator.hpp:248-259): DEVICE pointers,

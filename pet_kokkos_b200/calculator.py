@@ -38,11 +38,20 @@ class PetResults(C.Structure):
                 ("struct_id", C.POINTER(C.c_int)), ("edge_gradient", C.POINTER(C.c_double))]
 
 
+# pet_exchange's callbacks: device pointers and the calculator's stream arrive as integers.
+SET_LIVE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p)
+EDGES_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p)
+
+
+class PetExchange(C.Structure):
+    _fields_ = [("user", C.c_void_p), ("set_live", SET_LIVE_FN), ("edges", EDGES_FN)]
+
+
 class PetEdgeList(C.Structure):
     _fields_ = [("n_atoms", C.c_int), ("n_local", C.c_int), ("positions", C.POINTER(C.c_double)),
                 ("atomic_numbers", C.POINTER(C.c_int)), ("offsets", C.POINTER(C.c_int)),
                 ("neighbors", C.POINTER(C.c_int)), ("shifts", C.POINTER(C.c_int)), ("cell", C.POINTER(C.c_double)),
-                ("half", C.c_int)]
+                ("half", C.c_int), ("exchange", C.POINTER(PetExchange))]
 
 
 class PetDeviceArrays(C.Structure):
@@ -180,6 +189,9 @@ class EdgeListView:
     cell: np.ndarray | None = None
     half: bool = False
     n_local: int = -1
+    # pet::Exchange (include/pet/exchange.hpp:19-41) for a list whose ghosts are one cutoff deep: an object with
+    # set_live(live_ptr, n_live, stream) and edges(out_ptr, in_ptr, n_live, width, stream); device pointers as ints.
+    exchange: object | None = None
 
 
 class Calculator:
@@ -323,6 +335,25 @@ class Calculator:
         if v.cell is not None:
             keep["cell"] = np.ascontiguousarray(v.cell, dtype=np.float64).reshape(9)
             el.cell = _dptr(keep["cell"])
+        if v.exchange is not None:
+            ex = v.exchange
+
+            def _guard(fn):
+                def call(*a):
+                    try:
+                        fn(*a)
+                        return 0
+                    except Exception:  # an exception must not cross the C frame: fail the evaluation instead
+                        import traceback
+                        traceback.print_exc()
+                        return 1
+                return call
+            cb = PetExchange(None,
+                             SET_LIVE_FN(_guard(lambda user, live, n, stream: ex.set_live(live or 0, n, stream or 0))),
+                             EDGES_FN(_guard(lambda user, out, inn, n, w, stream: ex.edges(out or 0, inn or 0, n, w, stream or 0))))
+            keep["exchange"] = cb
+            el.exchange = C.pointer(cb)
+            self._exchange_keep = cb  # the library keeps the function pointers for as long as the list is set
         return el, keep
 
     def set_neighbors(self, view: EdgeListView):

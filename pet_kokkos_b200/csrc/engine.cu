@@ -36,6 +36,23 @@ __global__ void k_raw_edge_grad(double* __restrict__ eg, const double* __restric
   for (int c = 0; c < 3; ++c) eg[3 * size_t(e) + c] = p >= 0 ? scale * grad[3 * size_t(p) + c] : 0.0;
 }
 
+// Which of the edges to ghosts kept a row this time, and where (the reference's remote_map, src/model.cpp:459-497).
+__global__ void k_live_flag(int* __restrict__ flag, const int* __restrict__ remote_raw, const int* __restrict__ packed_of_raw,
+                            int R) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < R) flag[r] = packed_of_raw[remote_raw[r]] >= 0;
+}
+__global__ void k_live_fill(int* __restrict__ live, int* __restrict__ live_packed, int* __restrict__ remote_of,
+                            const int* __restrict__ at, const int* __restrict__ remote_raw,
+                            const int* __restrict__ packed_of_raw, int R) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= R) return;
+  const int k = packed_of_raw[remote_raw[r]];
+  if (k < 0) return;
+  const int l = at[r];
+  live[l] = r, live_packed[l] = k, remote_of[k] = l;
+}
+
 // An edge with no partner gives its target's share of the force itself (orphan_forces, src/forces.cpp:400-410).
 __global__ void k_orphan_forces(double* __restrict__ forces, const double* __restrict__ eg, const int* __restrict__ ooff,
                                 const int* __restrict__ oedge, int N) {
@@ -235,7 +252,8 @@ void Engine::drop_graphs() {
 // recorded launches depend on besides the weights: shapes, the input pointers, and the pools' generations.
 void Engine::run_model(const PackedEdges& pk, bool forces) {
   taps.clear();
-  const bool eager_only = !graphs || want_taps || prof.on;
+  // An exchanged list calls back into the engine in the middle of the pass: it is never recorded.
+  const bool eager_only = !graphs || want_taps || prof.on || pk.exchange != nullptr;
   if (eager_only) {
     last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, want_taps ? &taps : nullptr);
     last_pk = pk, have_out = true;
@@ -391,6 +409,12 @@ void Engine::set_neighbors(const pet_edge_list* v) {
     throw Error(2, "pet: an edge list needs offsets and atomic numbers");
   const int N = v->n_atoms, L = N > 0 ? v->offsets[N] : 0;
   if (N >= (1 << 24)) throw Error(1, "pet: too many atoms for the edge key");
+  const int n_own = v->n_local < 0 ? N : v->n_local;
+  if (v->exchange) {  // ghosts one cutoff deep: they are neighbours only (src/device_geometry.cpp:679)
+    if (v->half) throw Error(2, "pet: an exchanged list must be a full list");
+    if (!v->exchange->set_live || !v->exchange->edges) throw Error(2, "pet: an exchange needs set_live and edges callbacks");
+    if (n_own < N && v->offsets[N] != v->offsets[n_own]) throw Error(2, "pet: with an exchange, ghosts have no pairs of their own");
+  }
   std::vector<int> sp(N);
   for (int i = 0; i < N; ++i) sp[i] = species_index(v->atomic_numbers[i]);
   // Directed edges grouped by centre: each atom's listed pairs, then the mirrors of the pairs that list it.
@@ -472,6 +496,20 @@ void Engine::set_neighbors(const pet_edge_list* v) {
     PETB_CUDA(cudaMemcpyAsync(s.oedge, oedge.data(), 4 * size_t(s.n_orphan), cudaMemcpyHostToDevice, st.s));
     PETB_CUDA(cudaStreamSynchronize(st.s));
   }
+  s.has_exchange = v->exchange != nullptr;
+  s.n_remote = 0, s.remote_raw = nullptr;
+  if (s.has_exchange) {
+    s.exchange = *v->exchange;
+    std::vector<int> remote;
+    for (int e = 0; e < E; ++e)
+      if (rj[e] >= s.n_local) remote.push_back(e);
+    s.n_remote = int(remote.size());
+    s.remote_raw = A.alloc<int>(s.n_remote > 0 ? s.n_remote : 1);
+    if (s.n_remote > 0) {
+      PETB_CUDA(cudaMemcpyAsync(s.remote_raw, remote.data(), 4 * size_t(s.n_remote), cudaMemcpyHostToDevice, st.s));
+      PETB_CUDA(cudaStreamSynchronize(st.s));
+    }
+  }
   s.valid = true;
 }
 
@@ -499,8 +537,34 @@ static StepOut session_step(Engine& I, const double* positions, bool on_device, 
     PETB_CUDA(cudaMemcpyAsync(s.pos, positions, 24 * size_t(N), on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st.s));
   if (cell) PETB_CUDA(cudaMemcpyAsync(s.cell, cell, 72, cudaMemcpyHostToDevice, st.s));
   edge_vectors(st, s.re, s.pos, s.cell);
-  PackedEdges pk = pack_edges(st, I.nbr_arena, s.re, N, s.species, I.model->cutoff_spec(), I.pinned);
+  // With an exchange only the owned atoms are centres (token rows); ghosts are neighbours.
+  const int NC = s.has_exchange ? s.n_local : N;
+  PackedEdges pk = pack_edges(st, I.nbr_arena, s.re, NC, s.species, I.model->cutoff_spec(), I.pinned);
   pk.n_atoms = N, pk.n_local = s.n_local, pk.B = 1, pk.sid = s.sid, pk.soff = s.soff;
+  if (s.has_exchange) {
+    Arena& A = I.nbr_arena;
+    const int R = s.n_remote, Ra = R > 0 ? R : 1;
+    int* flag = A.alloc<int>(Ra + 1);
+    int* at = A.alloc<int>(Ra + 1);
+    int* live = A.alloc<int>(Ra);
+    int* live_packed = A.alloc<int>(Ra);
+    int* remote_of = A.alloc<int>(pk.E > 0 ? pk.E : 1);
+    PETB_CUDA(cudaMemsetAsync(remote_of, 0xFF, 4 * size_t(pk.E > 0 ? pk.E : 1), st.s));
+    int n_live = 0;
+    if (R > 0) {
+      k_live_flag<<<cdiv(R, 256), 256, 0, st.s>>>(flag, s.remote_raw, pk.packed_of_raw, R);
+      PETB_LAUNCH_CHECK(st);
+      exclusive_scan(st, A, flag, at, R);
+      k_live_fill<<<cdiv(R, 256), 256, 0, st.s>>>(live, live_packed, remote_of, at, s.remote_raw, pk.packed_of_raw, R);
+      PETB_LAUNCH_CHECK(st);
+      PETB_CUDA(cudaMemcpyAsync(I.pinned, at + R, sizeof(int), cudaMemcpyDeviceToHost, st.s));
+      PETB_CUDA(cudaStreamSynchronize(st.s));
+      n_live = I.pinned[0];
+    }
+    pk.n_live = n_live, pk.live_packed = live_packed, pk.remote_of = remote_of, pk.exchange = &s.exchange;
+    if (s.exchange.set_live(s.exchange.user, live, n_live, static_cast<void*>(st.s)) != 0)
+      throw Error(1, "pet: the exchange's set_live() failed");
+  }
   I.last_B = 1, I.last_N = N;
   StepOut so;
   if (N == 0) return so;

@@ -33,6 +33,12 @@ struct Session {
   int* oedge = nullptr;    // [n_orphan]
   int n_orphan = 0;
   std::vector<int> src, dir;  // each directed edge's pair in the engine's list, and its sign
+  // Over several ranks with ghosts one cutoff deep (EdgeListView::exchange): the engine's callbacks, and the
+  // owned-atom -> ghost edges in list order as raw edge indices (the reference's remote_raw).
+  bool has_exchange = false;
+  pet_exchange exchange{};
+  int n_remote = 0;
+  int* remote_raw = nullptr;  // [n_remote]
 };
 
 struct Engine {

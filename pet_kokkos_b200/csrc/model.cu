@@ -5,6 +5,7 @@
 #include <cmath>
 #include <cstring>
 
+#include "../../include/pet_b200.h"
 #include "attention.h"
 #include "gemm.h"
 
@@ -244,6 +245,16 @@ struct Gemms {
   }
 };
 
+// One swap of rows with the other ranks (Exchange::edges, include/pet/exchange.hpp:36-40): out[n_live, width] goes to
+// the ranks that own the ghosts, in[n_live, width] comes back with the partner edges' rows. Every rank calls it the same
+// number of times, with or without live edges of its own.
+void exchange_rows(Stream& st, const PackedEdges& pk, const float* out, float* in, int width) {
+  const pet_exchange* ex = static_cast<const pet_exchange*>(pk.exchange);
+  if (!ex || !ex->edges) throw Error(3, "pet: an exchanged list without an edges() callback");
+  if (ex->edges(ex->user, out, in, pk.n_live, width, static_cast<void*>(st.s)) != 0)
+    throw Error(1, "pet: the exchange's edges() failed");
+}
+
 struct Scope {
   Arena& a;
   Arena::Mark m;
@@ -296,6 +307,7 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
   };
   struct Layer {
     float *cpre, *cph_pre, *out_edge;
+    float* remote_in = nullptr;  // [n_live, D] partner rows received from other ranks (an exchanged list)
     std::vector<Block> blk;
   };
   std::vector<Layer> sav(G);
@@ -396,8 +408,17 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
       Scope s4(tmp);
       float* comb = tmp.alloc<float>(Ea * 2 * D);
       float* cph = tmp.alloc<float>(Ea * 2 * D);
+      RemoteRows remote;
+      if (pk.exchange) {  // edges to ghosts read their partners' rows from the ghosts' ranks (src/feedforward.cpp:171-179)
+        const size_t La = size_t(pk.n_live > 0 ? pk.n_live : 1) * D;
+        float* send = tmp.alloc<float>(La);
+        sl.remote_in = save.alloc<float>(La);
+        gather_live(st, send, sl.out_edge, D, 0, pk.live_packed, pk.n_live, D);
+        exchange_rows(st, pk, send, sl.remote_in, D);
+        remote = RemoteRows{pk.remote_of, sl.remote_in};
+      }
       concat_norm_fwd(st, comb, sl.out_edge, pk.reverse, input_edge, vec("combination_norms." + ls + ".weight"),
-                      vec("combination_norms." + ls + ".bias"), E, D);
+                      vec("combination_norms." + ls + ".bias"), E, D, remote);
       gm.linear_silu(cph, sl.cph_pre, comb, mat("combination_mlps." + ls + ".0.weight"), vec("combination_mlps." + ls + ".0.bias"), E);
       gm.linear(input_edge, cph, mat("combination_mlps." + ls + ".2.weight"), vec("combination_mlps." + ls + ".2.bias"), E,
                 input_edge, 0);
@@ -466,7 +487,19 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
       float* cnorm_adj = tmp.alloc<float>(Ea * 2 * D);
       gm.linear_silu_bwd(cph_adj, ie_adj, mat("combination_mlps." + ls + ".2.weight"), sl.cph_pre, E);
       gm.linear_bwd(cnorm_adj, cph_adj, mat("combination_mlps." + ls + ".0.weight"), E, false);
-      concat_norm_bwd(st, edge_adj, cnorm_adj, sl.out_edge, pk.reverse, ie_adj, vec("combination_norms." + ls + ".weight"), E, D);
+      RemoteRows remote;
+      float* remote_adj = nullptr;
+      if (pk.exchange) {  // the partner's rank wants the adjoint of the row this edge read (src/feedforward.cpp:241-255)
+        const size_t La = size_t(pk.n_live > 0 ? pk.n_live : 1) * D;
+        float* send = tmp.alloc<float>(La);
+        remote_adj = tmp.alloc<float>(La);
+        remote = RemoteRows{pk.remote_of, sl.remote_in};
+        concat_norm_remote_bwd(st, send, cnorm_adj, sl.out_edge, vec("combination_norms." + ls + ".weight"), pk.live_packed,
+                               pk.n_live, D, remote);
+        exchange_rows(st, pk, send, remote_adj, D);
+      }
+      concat_norm_bwd(st, edge_adj, cnorm_adj, sl.out_edge, pk.reverse, ie_adj, vec("combination_norms." + ls + ".weight"), E, D,
+                      remote, remote_adj);
     }
     for (int a = A - 1; a >= 0; --a) {
       const std::string tl = g + ".trans.layers." + std::to_string(a);
@@ -630,7 +663,18 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
       tap(taps, "edge_pred" + ls, sl.edge_pred, E);
       tap(taps, "net" + ls, net, N);
     }
-    if (L + 1 < G) message_average(st, input_edge, tokens + size_t(N) * D, pk.reverse, E, D);
+    if (L + 1 < G) {
+      RemoteRows remote;
+      if (pk.exchange) {  // src/residual.cpp:123-132
+        const size_t La = size_t(pk.n_live > 0 ? pk.n_live : 1) * D;
+        float* send = tmp.alloc<float>(La);
+        float* recv = tmp.alloc<float>(La);
+        gather_live(st, send, tokens + size_t(N) * D, D, 0, pk.live_packed, pk.n_live, D);
+        exchange_rows(st, pk, send, recv, D);
+        remote = RemoteRows{pk.remote_of, recv};
+      }
+      message_average(st, input_edge, tokens + size_t(N) * D, pk.reverse, E, D, remote);
+    }
   }
   if (!grad) return finish(st, save, pk, false, nullptr, nullptr, nullptr, per_atom);
 
@@ -667,7 +711,18 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
       gm.linear_bwd(tokens_adj + size_t(N) * D, eh0_adj, mat(eh + ".0.weight"), E, false);
     }
     float* ie_next = ie_adj == ie_a ? ie_b : ie_a;
-    if (L + 1 < G) message_average_bwd(st, ie_next, tokens_adj + size_t(N) * D, ie_adj, pk.reverse, E, D);
+    if (L + 1 < G) {
+      RemoteRows remote;
+      if (pk.exchange) {  // src/residual.cpp:189
+        const size_t La = size_t(pk.n_live > 0 ? pk.n_live : 1) * D;
+        float* send = tmp.alloc<float>(La);
+        float* recv = tmp.alloc<float>(La);
+        gather_live(st, send, ie_adj, D, 0, pk.live_packed, pk.n_live, D);
+        exchange_rows(st, pk, send, recv, D);
+        remote = RemoteRows{pk.remote_of, recv};
+      }
+      message_average_bwd(st, ie_next, tokens_adj + size_t(N) * D, ie_adj, pk.reverse, E, D, remote);
+    }
     else PETB_CUDA(cudaMemsetAsync(ie_next, 0, sizeof(float) * Ea * D, st.s));
     for (int a = A - 1; a >= 0; --a) {
       const std::string tl = g + ".trans.layers." + std::to_string(a);

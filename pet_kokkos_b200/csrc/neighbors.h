@@ -64,6 +64,12 @@ struct PackedEdges {
   const int* atom_species = nullptr;  // [n_atoms]
   const int* sid = nullptr;           // [n_atoms]
   const int* soff = nullptr;          // [B+1]
+  // Over several ranks with an exchange (the reference's remote_map, src/model.cpp:459-497): the kept edges from
+  // an owned atom to a ghost ("live"), whose partner rows another rank holds.
+  int n_live = 0;
+  const int* live_packed = nullptr;  // [n_live] packed row of each live edge, in the engine's order
+  const int* remote_of = nullptr;    // [E] live index of a packed row, or -1
+  const void* exchange = nullptr;    // the engine's pet_exchange (host pointer), null without one
 };
 
 struct CutoffSpec {

@@ -66,15 +66,34 @@ __global__ void __launch_bounds__(256) k_norm_fwd(float* __restrict__ out, float
   for (int d = lane; d < D; d += 32) o[d] = (x[d] - mu) * inv * w[d] + (ln ? bias[d] : 0.f);
 }
 
+// Edge q's partner row: its reverse edge's, the row another rank sent for it, or none.
+__device__ __forceinline__ const float* partner_row(const float* oe, const int* rev, const RemoteRows& rm, int q, int D) {
+  const int r = rev[q];
+  if (r >= 0) return oe + size_t(r) * D;
+  if (rm.of) {
+    const int l = rm.of[q];
+    if (l >= 0) return rm.rows + size_t(l) * D;
+  }
+  return nullptr;
+}
+
+__global__ void k_gather_live(float* __restrict__ out, const float* __restrict__ src, int ld, int col0,
+                              const int* __restrict__ live_packed, int n_live, int D4) {
+  const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= size_t(n_live) * D4) return;
+  const int l = int(t / D4), q = int(t % D4), k = live_packed[l];
+  reinterpret_cast<float4*>(out)[t] = k >= 0 ? ld4(src + size_t(k) * ld + col0 + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
 __global__ void __launch_bounds__(256) k_concat_norm_fwd(float* __restrict__ out, const float* __restrict__ oe,
                                                          const int* __restrict__ rev, float* __restrict__ ie,
                                                          const float* __restrict__ w, const float* __restrict__ bias, int E,
-                                                         int D) {
+                                                         int D, RemoteRows rm) {
   const int k = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (k >= E) return;
-  const int r = rev[k], W = 2 * D;
+  const int W = 2 * D;
   const float* a = oe + size_t(k) * D;
-  const float* b = r >= 0 ? oe + size_t(r) * D : nullptr;
+  const float* b = partner_row(oe, rev, rm, k, D);
   float s = 0.f;
   for (int d = lane; d < D; d += 32) {
     const float v = a[d];
@@ -131,49 +150,71 @@ __global__ void __launch_bounds__(256) k_norm_bwd(float* __restrict__ in_adj, co
   }
 }
 
+// The statistics of row q of the concat [oe(q) | partner(q) or 0] and of its adjoint.
+__device__ __forceinline__ RowStats concat_stats(const float* oe, const float* b, const float* out_adj, const float* w, int q,
+                                                 int D, int lane) {
+  const int W = 2 * D;
+  const float* a = oe + size_t(q) * D;
+  const float* ga = out_adj + size_t(q) * W;
+  float s = 0.f;
+  for (int d = lane; d < D; d += 32) s += a[d] + (b ? b[d] : 0.f);
+  const float mu = warp_sum(s) / W;
+  float sq = 0.f, sg = 0.f, sgx = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float c0 = a[d] - mu, c1 = (b ? b[d] : 0.f) - mu;
+    const float g0 = ga[d] * w[d], g1 = ga[D + d] * w[D + d];
+    sq += c0 * c0 + c1 * c1, sg += g0 + g1, sgx += g0 * c0 + g1 * c1;
+  }
+  sq = warp_sum(sq), sg = warp_sum(sg), sgx = warp_sum(sgx);
+  const float inv = 1.0f / sqrtf(sq / W + kLnEps);
+  return RowStats{mu, inv, sg / W, sgx * inv / W};
+}
+
 __global__ void __launch_bounds__(256) k_concat_norm_bwd(float* __restrict__ edge_adj, const float* __restrict__ out_adj,
                                                          const float* __restrict__ oe, const int* __restrict__ rev,
                                                          const float* __restrict__ ie_adj, const float* __restrict__ w, int E,
-                                                         int D) {
+                                                         int D, RemoteRows rm, const float* __restrict__ remote_adj) {
   const int k = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (k >= E) return;
   const int W = 2 * D, r = rev[k];
-  // Row q of the concat is [oe(q) | oe(rev q) or 0].
-  auto stats = [&](int q) {
-    const int pq = rev[q];
-    const float* a = oe + size_t(q) * D;
-    const float* b = pq >= 0 ? oe + size_t(pq) * D : nullptr;
-    const float* ga = out_adj + size_t(q) * W;
-    float s = 0.f;
-    for (int d = lane; d < D; d += 32) s += a[d] + (b ? b[d] : 0.f);
-    const float mu = warp_sum(s) / W;
-    float sq = 0.f, sg = 0.f, sgx = 0.f;
-    for (int d = lane; d < D; d += 32) {
-      const float c0 = a[d] - mu, c1 = (b ? b[d] : 0.f) - mu;
-      const float g0 = ga[d] * w[d], g1 = ga[D + d] * w[D + d];
-      sq += c0 * c0 + c1 * c1, sg += g0 + g1, sgx += g0 * c0 + g1 * c1;
-    }
-    sq = warp_sum(sq), sg = warp_sum(sg), sgx = warp_sum(sgx);
-    const float inv = 1.0f / sqrtf(sq / W + kLnEps);
-    return RowStats{mu, inv, sg / W, sgx * inv / W};
-  };
-  const RowStats sk = stats(k);
+  const RowStats sk = concat_stats(oe, partner_row(oe, rev, rm, k, D), out_adj, w, k, D, lane);
   RowStats sr = sk;
-  const float* xr2 = nullptr;  // the second half of row r: oe(rev r)
+  const float* xr2 = nullptr;  // the second half of row r: its partner's row
   if (r >= 0) {
-    sr = stats(r);
-    const int pr = rev[r];
-    xr2 = pr >= 0 ? oe + size_t(pr) * D : nullptr;
+    xr2 = partner_row(oe, rev, rm, r, D);
+    sr = concat_stats(oe, xr2, out_adj, w, r, D, lane);
   }
+  // An edge to another rank's atom: that rank computed the adjoint of the row it read from here.
+  const float* far = (r < 0 && rm.of && remote_adj && rm.of[k] >= 0) ? remote_adj + size_t(rm.of[k]) * D : nullptr;
   for (int d = lane; d < D; d += 32) {
     const float gk = sk.inv * (out_adj[size_t(k) * W + d] * w[d] - sk.mg - (oe[size_t(k) * D + d] - sk.mu) * sk.inv * sk.mgx);
     float back = 0.f;
     if (r >= 0) {
       const float x = (xr2 ? xr2[d] : 0.f) - sr.mu;
       back = sr.inv * (out_adj[size_t(r) * W + D + d] * w[D + d] - sr.mg - x * sr.inv * sr.mgx);
+    } else if (far) {
+      back = far[d];
     }
     edge_adj[size_t(k) * D + d] = ie_adj[size_t(k) * D + d] + gk + back;
   }
+}
+
+// send(l, :) = the second half of the norm's input adjoint on live edge l's row: what its partner's rank adds.
+__global__ void __launch_bounds__(256) k_concat_norm_remote_bwd(float* __restrict__ send, const float* __restrict__ out_adj,
+                                                                const float* __restrict__ oe, const float* __restrict__ w,
+                                                                const int* __restrict__ live_packed, int n_live, int D,
+                                                                RemoteRows rm) {
+  const int l = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (l >= n_live) return;
+  const int k = live_packed[l], W = 2 * D;
+  if (k < 0) {
+    for (int d = lane; d < D; d += 32) send[size_t(l) * D + d] = 0.f;
+    return;
+  }
+  const float* b = rm.rows + size_t(l) * D;
+  const RowStats sk = concat_stats(oe, b, out_adj, w, k, D, lane);
+  for (int d = lane; d < D; d += 32)
+    send[size_t(l) * D + d] = sk.inv * (out_adj[size_t(k) * W + D + d] * w[D + d] - sk.mg - (b[d] - sk.mu) * sk.inv * sk.mgx);
 }
 
 __global__ void __launch_bounds__(256) k_compress_geometry_bwd(float* __restrict__ x4_adj, const float* __restrict__ g,
@@ -240,25 +281,27 @@ __global__ void k_add_inplace(float* __restrict__ a, const float* __restrict__ b
 }
 
 __global__ void k_message_average(float* __restrict__ ie, const float* __restrict__ oe, const int* __restrict__ rev, int E,
-                                  int D4) {
+                                  int D4, RemoteRows rm) {
   const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= size_t(E) * D4) return;
-  const int k = int(t / D4), q = int(t % D4), r = rev[k];
+  const int k = int(t / D4), q = int(t % D4);
   float4 x = reinterpret_cast<float4*>(ie)[t];
-  const float4 y = r >= 0 ? reinterpret_cast<const float4*>(oe)[size_t(r) * D4 + q] : make_float4(0, 0, 0, 0);
+  const float* pr = partner_row(oe, rev, rm, k, 4 * D4);
+  const float4 y = pr ? ld4(pr + 4 * q) : make_float4(0, 0, 0, 0);
   reinterpret_cast<float4*>(ie)[t] = make_float4(0.5f * (x.x + y.x), 0.5f * (x.y + y.y), 0.5f * (x.z + y.z), 0.5f * (x.w + y.w));
 }
 
 // The adjoint of message_average: ie_adj_out(k) = 0.5 ie_adj_in(k); oe_adj(k) += 0.5 ie_adj_in(rev k).
 __global__ void k_message_average_bwd(float* __restrict__ ie_out, float* __restrict__ oe_adj, const float* __restrict__ ie_in,
-                                      const int* __restrict__ rev, int E, int D4) {
+                                      const int* __restrict__ rev, int E, int D4, RemoteRows rm) {
   const size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= size_t(E) * D4) return;
-  const int k = int(t / D4), q = int(t % D4), r = rev[k];
+  const int k = int(t / D4), q = int(t % D4);
   const float4 x = reinterpret_cast<const float4*>(ie_in)[t];
   float4 o = reinterpret_cast<float4*>(oe_adj)[t];
-  if (r >= 0) {
-    const float4 y = reinterpret_cast<const float4*>(ie_in)[size_t(r) * D4 + q];
+  const float* pr = partner_row(ie_in, rev, rm, k, 4 * D4);  // the partner edge's adjoint row, here or from its rank
+  if (pr) {
+    const float4 y = ld4(pr + 4 * q);
     o.x += 0.5f * y.x, o.y += 0.5f * y.y, o.z += 0.5f * y.z, o.w += 0.5f * y.w;
   }
   reinterpret_cast<float4*>(oe_adj)[t] = o;
@@ -364,11 +407,18 @@ void norm_fwd(Stream& st, float* out, float* in, const float* add, const float* 
   PETB_LAUNCH_CHECK(st);
 }
 
+void gather_live(Stream& st, float* out, const float* src, int ld, int col0, const int* live_packed, int n_live, int D) {
+  if (n_live == 0) return;
+  const ProfScope ps(st, PC_GATHER, 0.0, 8.0 * double(n_live) * D);
+  k_gather_live<<<blocks_for(size_t(n_live) * (D / 4), 256), 256, 0, st.s>>>(out, src, ld, col0, live_packed, n_live, D / 4);
+  PETB_LAUNCH_CHECK(st);
+}
+
 void concat_norm_fwd(Stream& st, float* out, const float* oe, const int* rev, float* ie, const float* w, const float* bias,
-                     int E, int D) {
+                     int E, int D, RemoteRows remote) {
   if (E == 0) return;
   const ProfScope ps(st, PC_NORM, 12.0 * double(E) * D, 24.0 * double(E) * D);
-  k_concat_norm_fwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(out, oe, rev, ie, w, bias, E, D);
+  k_concat_norm_fwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(out, oe, rev, ie, w, bias, E, D, remote);
   PETB_LAUNCH_CHECK(st);
 }
 
@@ -381,10 +431,20 @@ void norm_bwd(Stream& st, float* in_adj, const float* out_adj, const float* in, 
 }
 
 void concat_norm_bwd(Stream& st, float* edge_adj, const float* out_adj, const float* oe, const int* rev, const float* ie_adj,
-                     const float* w, int E, int D) {
+                     const float* w, int E, int D, RemoteRows remote, const float* remote_adj) {
   if (E == 0) return;
   const ProfScope ps(st, PC_NORM, 20.0 * double(E) * D, 24.0 * double(E) * D);
-  k_concat_norm_bwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E, D);
+  k_concat_norm_bwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E, D, remote,
+                                                                      remote_adj);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void concat_norm_remote_bwd(Stream& st, float* send, const float* out_adj, const float* oe, const float* w,
+                            const int* live_packed, int n_live, int D, RemoteRows remote) {
+  if (n_live == 0) return;
+  const ProfScope ps(st, PC_NORM, 20.0 * double(n_live) * D, 16.0 * double(n_live) * D);
+  k_concat_norm_remote_bwd<<<blocks_for(size_t(n_live) * 32, 256), 256, 0, st.s>>>(send, out_adj, oe, w, live_packed, n_live, D,
+                                                                                  remote);
   PETB_LAUNCH_CHECK(st);
 }
 
@@ -426,17 +486,19 @@ void add_inplace(Stream& st, float* a, const float* b, size_t n) {
   PETB_LAUNCH_CHECK(st);
 }
 
-void message_average(Stream& st, float* ie, const float* oe, const int* rev, int E, int D) {
+void message_average(Stream& st, float* ie, const float* oe, const int* rev, int E, int D, RemoteRows remote) {
   if (E == 0) return;
   const ProfScope ps(st, PC_GATHER, 2.0 * double(E) * D, 12.0 * double(E) * D);
-  k_message_average<<<blocks_for(size_t(E) * (D / 4), 256), 256, 0, st.s>>>(ie, oe, rev, E, D / 4);
+  k_message_average<<<blocks_for(size_t(E) * (D / 4), 256), 256, 0, st.s>>>(ie, oe, rev, E, D / 4, remote);
   PETB_LAUNCH_CHECK(st);
 }
 
-void message_average_bwd(Stream& st, float* ie_adj_out, float* oe_adj, const float* ie_adj_in, const int* rev, int E, int D) {
+void message_average_bwd(Stream& st, float* ie_adj_out, float* oe_adj, const float* ie_adj_in, const int* rev, int E, int D,
+                         RemoteRows remote_adj) {
   if (E == 0) return;
   const ProfScope ps(st, PC_GATHER, 2.0 * double(E) * D, 20.0 * double(E) * D);
-  k_message_average_bwd<<<blocks_for(size_t(E) * (D / 4), 256), 256, 0, st.s>>>(ie_adj_out, oe_adj, ie_adj_in, rev, E, D / 4);
+  k_message_average_bwd<<<blocks_for(size_t(E) * (D / 4), 256), 256, 0, st.s>>>(ie_adj_out, oe_adj, ie_adj_in, rev, E, D / 4,
+                                                                              remote_adj);
   PETB_LAUNCH_CHECK(st);
 }
 

@@ -19,10 +19,20 @@ void compress0(Stream& st, float* out, float* pre, const float* b, const float* 
 // out = norm(in [+ add, stored back into in]); RMSNorm when bias is null, else LayerNorm  (norm_rows, src/ops.hpp:381-401)
 void norm_fwd(Stream& st, float* out, float* in, const float* add, const float* w, const float* bias, int R, int D);
 
-// The combination norm with its gather: row k of the input is [oe(k) | oe(rev k) or 0];
+// Partner rows that live on another rank (an exchanged list): edge k's partner row is rows[of[k]] when its local
+// partner is missing and of[k] >= 0. All null without an exchange.
+struct RemoteRows {
+  const int* of = nullptr;      // [E] live index of a packed edge, or -1
+  const float* rows = nullptr;  // [n_live, D]
+};
+
+// out(l, :) = src(live_packed[l], col0 : col0 + D), src rows ld floats apart: the rows an exchange sends.
+void gather_live(Stream& st, float* out, const float* src, int ld, int col0, const int* live_packed, int n_live, int D);
+
+// The combination norm with its gather: row k of the input is [oe(k) | oe(rev k), the remote partner's row, or 0];
 // ie(k) += oe(k) on the way  (src/feedforward.cpp:182-193)
 void concat_norm_fwd(Stream& st, float* out, const float* oe, const int* rev, float* ie, const float* w, const float* bias,
-                     int E, int D);
+                     int E, int D, RemoteRows remote = {});
 
 // in_adj = g for rows < acc_row0, in_adj += g for the rest; g the norm's input adjoint
 // (norm_rows_bwd, src/ops.hpp:404-436). `also`, unless null, receives a copy of the result.
@@ -30,8 +40,13 @@ void norm_bwd(Stream& st, float* in_adj, const float* out_adj, const float* in, 
               int acc_row0, float* also = nullptr);
 
 // edge_adj(k) = ie_adj(k) + g(k)[:D] + g(rev k)[D:], g from out_adj [E,2D]  (concat_norm_bwd, src/ops.cpp:191-244)
+// With an exchange: `remote` holds the partner rows the forward read, `remote_adj` the partners' adjoints of this
+// rank's rows (what concat_norm_remote_bwd computed on the other side).
 void concat_norm_bwd(Stream& st, float* edge_adj, const float* out_adj, const float* oe, const int* rev, const float* ie_adj,
-                     const float* w, int E, int D);
+                     const float* w, int E, int D, RemoteRows remote = {}, const float* remote_adj = nullptr);
+// send(l, :) = the adjoint of the partner row that live edge l read: g(live_packed[l])[D:]  (src/feedforward.cpp:246-255)
+void concat_norm_remote_bwd(Stream& st, float* send, const float* out_adj, const float* oe, const float* w,
+                            const int* live_packed, int n_live, int D, RemoteRows remote);
 
 // x4_adj(k,c) += sum_d g(k,d) wx(d,c)  (the reduction of compress_bwd, src/ops.cpp:373-401)
 void compress_geometry_bwd(Stream& st, float* x4_adj, const float* g, const float* wx, int E, int D);
@@ -52,8 +67,10 @@ void cutoff_share(Stream& st, float* cf_adj, const float* cfh, const float* cut,
 // a += b, elementwise
 void add_inplace(Stream& st, float* a, const float* b, size_t n);
 // input_edge(k) = 0.5 (input_edge(k) + oe(rev k) or 0)  (re_msg, src/residual.cpp:123-132)
-void message_average(Stream& st, float* ie, const float* oe, const int* rev, int E, int D);
-void message_average_bwd(Stream& st, float* ie_adj_out, float* oe_adj, const float* ie_adj_in, const int* rev, int E, int D);
+void message_average(Stream& st, float* ie, const float* oe, const int* rev, int E, int D, RemoteRows remote = {});
+// With an exchange, `remote_adj` holds the partners' ie_adj_in rows (src/residual.cpp:189).
+void message_average_bwd(Stream& st, float* ie_adj_out, float* oe_adj, const float* ie_adj_in, const int* rev, int E, int D,
+                         RemoteRows remote_adj = {});
 
 struct ForceOut {
   double* edge_grad = nullptr;  // [E,3]

@@ -1,0 +1,54 @@
+"""Exchange-mode decomposition on the GPU: ranks played as threads of one process on one device (the reference's
+ImageExchange test, tests/test_edges.cpp:385-478). Ghosts are one cutoff deep, edge rows cross at every layer, and the
+sum over ranks must be the periodic single-domain answer; with the exchange muted it must not be."""
+import numpy as np
+import pytest
+
+from pet_kokkos_b200 import exchange, structures as st
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("featurizer", ["feedforward", "residual"])
+@pytest.mark.parametrize("n,world", [(2, 2), (3, 2), (3, 4)])
+def test_exchanged_domains_reproduce_the_periodic_cell(lib_path, models, featurizer, n, world):
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("tiny", featurizer, "scaled", 31)
+    s = st.diamond(n, jitter=0.05, seed=6)
+    whole = Calculator(jp, sp)
+    ref = whole.compute(s)
+    assert whole.exchange_ghost_cutoff == whole.cutoff
+    calcs = [Calculator(jp, sp) for _ in range(world)]
+    E, F, W, hub = exchange.compute_threads(calcs, s, whole.cutoff)
+    assert abs(E - ref.energy[0]) <= 1e-6 * max(abs(ref.energy[0]), np.abs(ref.per_atom_energy).sum())
+    assert np.abs(F - ref.forces).max() <= 1e-5 * max(1.0, np.abs(ref.forces).max())
+    assert np.abs(W - ref.virial[0]).max() <= 1e-5 * max(1.0, np.abs(ref.virial).max())
+    for c in calcs + [whole]:
+        c.close()
+
+
+def test_muting_the_exchange_changes_the_answer(lib_path, models):
+    """tests/test_edges.cpp:470-478: the rows that cross are not decoration."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("tiny", "feedforward", "scaled", 31)
+    s = st.diamond(2, jitter=0.05, seed=6)
+    whole = Calculator(jp, sp)
+    ref = whole.compute(s)
+    calcs = [Calculator(jp, sp) for _ in range(2)]
+    domains = [exchange.exchange_domain(s, r, 2, whole.cutoff) for r in range(2)]
+    hub = exchange.ThreadHub(exchange.route(domains))
+    hub.mute = True
+    import threading
+    out = [None, None]
+
+    def run(r):
+        fields, owner, _, _ = domains[r]
+        res = calcs[r].compute_edges(exchange.view_of(fields, exchange.ThreadExchange(hub, r)), True, False)
+        out[r] = exchange.fold_to_owners(res, owner, s["n_atoms"])
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    E = out[0][0] + out[1][0]
+    assert abs(E - ref.energy[0]) > 1e-4 * np.abs(ref.per_atom_energy).sum()
+    for c in calcs + [whole]:
+        c.close()
