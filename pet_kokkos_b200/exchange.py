@@ -282,3 +282,27 @@ def compute_threads(calcs, system, cutoff):
     F = sum(o[1] for o in out)
     W = sum(o[2] for o in out)
     return E, F, W, hub
+
+
+def compute_distributed(calc, system, cutoff, group=None, steps=1, positions=None):
+    """One process per GPU (torch.distributed initialised, NCCL): this rank evaluates its domain of `system` with
+    ghosts one cutoff deep and an NcclExchange; returns the whole cell's (energy, forces, virial) on every rank.
+    With steps > 1 the list is set once and compute_step runs `steps` times (an MD engine between list rebuilds)."""
+    import torch
+    import torch.distributed as dist
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    domains = [exchange_domain(system, r, world, cutoff) for r in range(world)]
+    fields, owner, _, _ = domains[rank]
+    ex = NcclExchange(route(domains)[rank], group)
+    view = view_of(fields, ex)
+    if steps == 1:
+        res = calc.compute_edges(view, True, False)
+    else:
+        calc.set_neighbors(view)
+        for _ in range(steps):
+            res = calc.compute_step(fields["positions"], None, True, False)
+    e, F, W = fold_to_owners(res, owner, system["n_atoms"])
+    buf = torch.from_numpy(np.concatenate([[e], W, F.ravel()])).cuda()
+    dist.all_reduce(buf, group=group)
+    out = buf.cpu().numpy()
+    return out[0], out[7:].reshape(-1, 3), out[1:7]

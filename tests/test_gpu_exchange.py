@@ -52,3 +52,21 @@ def test_muting_the_exchange_changes_the_answer(lib_path, models):
     assert abs(E - ref.energy[0]) > 1e-4 * np.abs(ref.per_atom_energy).sum()
     for c in calcs + [whole]:
         c.close()
+
+
+def test_one_process_per_gpu_over_nccl():
+    """The same decomposition with real ranks: torchrun, one process per GPU, rows crossing with NCCL all-to-all.
+    Needs two GPUs; NVLS is switched off as for every test in which a rank could leave early."""
+    import os
+    import subprocess
+    import sys
+    import torch
+    n = min(torch.cuda.device_count(), 4)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "exchange_nccl_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29541", worker],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "EXCHANGE_NCCL_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
