@@ -73,24 +73,33 @@ def exchange_domain(system, rank, world, cutoff):
 def route(domains):
     """For every rank p and every edge r of its edges to ghosts: (rank q, index r' among q's edges to ghosts) of the
     partner edge. The partner of i -> g (g an image of atom j) is, on j's owner, j -> its image of i with the opposite
-    vector; the vector (rounded) tells several images of one atom apart."""
-    key_of = {}
+    vector; the vector (rounded to 1e-4 A) tells several images of one atom apart."""
+    n_atoms = 1 + max(int(d[1].max()) for d in domains if len(d[1]))
+    keys, partners, label = [], [], []
     for q, (fields, owner, image, remote) in enumerate(domains):
         x = fields["positions"]
-        for r, (i, g) in enumerate(remote):
-            v = x[g] - x[i]
-            key_of[(int(owner[i]), int(owner[g]), tuple(np.round(v, 5)))] = (q, r)
-    out = []
-    for p, (fields, owner, image, remote) in enumerate(domains):
-        x = fields["positions"]
-        dest = np.zeros((len(remote), 2), int)
-        for r, (i, g) in enumerate(remote):
-            v = x[g] - x[i]
-            k = (int(owner[g]), int(owner[i]), tuple(np.round(-v, 5)))
-            if k not in key_of:
-                raise RuntimeError(f"rank {p}: edge {r} to a ghost has no partner on the ghost's rank")
-            dest[r] = key_of[k]
-        out.append(dest)
+        i, g = remote[:, 0], remote[:, 1]
+        v = np.rint((x[g] - x[i]) * 1e4).astype(np.int64)
+        oi, og = owner[i].astype(np.int64), owner[g].astype(np.int64)
+        pack = lambda w: ((w[:, 0] + (1 << 20)) << 42) | ((w[:, 1] + (1 << 20)) << 21) | (w[:, 2] + (1 << 20))
+        keys.append(np.stack([oi * n_atoms + og, pack(v)], 1))
+        partners.append(np.stack([og * n_atoms + oi, pack(-v)], 1))
+        label.append(np.stack([np.full(len(remote), q), np.arange(len(remote))], 1))
+    keys, partners, label = np.concatenate(keys), np.concatenate(partners), np.concatenate(label)
+    n = len(keys)
+    _, inv = np.unique(np.concatenate([keys, partners]), axis=0, return_inverse=True)
+    inv = inv.reshape(-1)
+    edge_of_id = np.full(inv.max() + 1 if n else 1, -1, np.int64)
+    edge_of_id[inv[:n]] = np.arange(n)
+    match = edge_of_id[inv[n:]]
+    if (match < 0).any():
+        bad = int(np.nonzero(match < 0)[0][0])
+        raise RuntimeError(f"rank {label[bad, 0]}: edge {label[bad, 1]} to a ghost has no partner on the ghost's rank")
+    dest = label[match]
+    out, at = [], 0
+    for d in domains:
+        out.append(dest[at:at + len(d[3])])
+        at += len(d[3])
     return out
 
 
