@@ -257,10 +257,10 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
   __syncthreads();
   // The first half of the warps take 16 queries each (dQ), the second half 16 keys each (dK, dV and
   // the keys' cutoff shares), both recomputing the weights they need: no S x S table, no further barrier.
+  // With more blocks than warps of a kind (long neighbour lists) a warp takes every half-th block in turn.
   const int half = nw >> 1;
   const bool keys = warp >= half;
-  const int r0 = 16 * (keys ? warp - half : warp);
-  if (r0 >= S16) return;
+  for (int r0 = 16 * (keys ? warp - half : warp); r0 < S16; r0 += 16 * half) {
   const int i0 = r0 + g, i1 = r0 + g + 8;  // this lane's two rows (queries or keys)
   const size_t g0 = i0 == 0 ? size_t(n) : size_t(p.N) + e0 + i0 - 1, g1 = size_t(p.N) + e0 + i1 - 1;
   if (!keys) {
@@ -363,6 +363,7 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
       if (i1 < cnt) p.cfh[g1 * p.H + h] = cf1;
     }
   }
+  }
 }
 
 bool enabled() {
@@ -404,9 +405,11 @@ bool fwd_hd(Stream& st, const AttnArgs& p) {
 }
 template <int HD>
 bool bwd_hd(Stream& st, const AttnArgs& p) {
-  const int S16 = round16(p.S), threads = 2 * 32 * (S16 / 16);  // a warp per 16 queries and a warp per 16 keys
+  const int S16 = round16(p.S);
+  int threads = 2 * 32 * (S16 / 16);  // a warp per 16 queries and a warp per 16 keys, up to 512 threads: then blocks in turn
+  if (threads > 512) threads = 512;
   const size_t bytes = bwd_bytes(p.S, HD);
-  if (bytes > 200 * 1024 || threads > 512) return false;
+  if (bytes > 200 * 1024) return false;
   static int o320 = 48 * 1024, o512 = 48 * 1024;
   if (threads <= 320) launch(st, k_attn_bwd_mma<HD, 320>, p, bytes, threads, &o320);
   else launch(st, k_attn_bwd_mma<HD, 512>, p, bytes, threads, &o512);
