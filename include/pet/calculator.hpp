@@ -46,6 +46,18 @@ struct Results {
 };
 
 // pet::EdgeListView (the reference's include/pet/device_geometry.hpp:93-110).
+// What an engine supplies when it runs PET over several ranks with ghosts one cutoff deep: the reference's
+// pet::Exchange (include/pet/exchange.hpp:19-41) with device pointers and the calculator's CUDA stream in place of
+// Kokkos views. Work enqueued on `stream` is ordered with the evaluation; anything else must be complete on return.
+class Exchange {
+ public:
+  virtual ~Exchange() = default;
+  // Once per evaluation: the kept edges to ghosts, ascending indices into the list's owned-atom -> ghost pairs.
+  virtual void set_live(const int* live, int n_live, void* stream) = 0;
+  // out[n_live, width]: one row per live edge to send to the ghost's owner; in[n_live, width]: the partners' rows.
+  virtual void edges(const float* out, float* in, int n_live, int width, void* stream) = 0;
+};
+
 struct EdgeListView {
   int n_atoms = 0, n_local = -1;
   const double* positions = nullptr;
@@ -55,6 +67,7 @@ struct EdgeListView {
   const int* shifts = nullptr;
   const double* cell = nullptr;
   bool half = false;
+  Exchange* exchange = nullptr;  // must outlive the list
 };
 
 class Calculator {
@@ -119,7 +132,8 @@ class Calculator {
     return r;
   }
   Results compute_edges(const EdgeListView& v, bool compute_forces = true, bool edge_gradients = true) const {
-    const pet_edge_list l = list(v);
+    pet_exchange ex{};
+    const pet_edge_list l = list(v, ex);
     atoms_ = v.n_atoms, pairs_ = v.n_atoms > 0 ? v.offsets[v.n_atoms] : 0;
     Results r;
     r.n_atoms = {v.n_atoms};
@@ -128,7 +142,8 @@ class Calculator {
     return r;
   }
   void set_neighbors(const EdgeListView& v) {
-    const pet_edge_list l = list(v);
+    pet_exchange ex{};
+    const pet_edge_list l = list(v, ex);
     check(pet_set_neighbors(h_, &l));
     atoms_ = v.n_atoms, pairs_ = v.n_atoms > 0 ? v.offsets[v.n_atoms] : 0;
   }
@@ -160,8 +175,31 @@ class Calculator {
   const Options& options() const { return opts_; }
 
  private:
-  static pet_edge_list list(const EdgeListView& v) {
-    return pet_edge_list{v.n_atoms, v.n_local, v.positions, v.atomic_numbers, v.offsets, v.neighbors, v.shifts, v.cell, v.half ? 1 : 0};
+  // The library copies the callbacks out of `ex` during the call; the Exchange object itself is the caller's.
+  static pet_edge_list list(const EdgeListView& v, pet_exchange& ex) {
+    const pet_exchange* pex = nullptr;
+    if (v.exchange) {
+      ex.user = v.exchange;
+      ex.set_live = [](void* u, const int* live, int n, void* stream) -> int {
+        try {
+          static_cast<Exchange*>(u)->set_live(live, n, stream);
+          return 0;
+        } catch (...) {
+          return 1;
+        }
+      };
+      ex.edges = [](void* u, const float* out, float* in, int n, int width, void* stream) -> int {
+        try {
+          static_cast<Exchange*>(u)->edges(out, in, n, width, stream);
+          return 0;
+        } catch (...) {
+          return 1;
+        }
+      };
+      pex = &ex;
+    }
+    return pet_edge_list{v.n_atoms, v.n_local, v.positions, v.atomic_numbers, v.offsets, v.neighbors,
+                         v.shifts,  v.cell,    v.half ? 1 : 0, pex};
   }
   static pet_results sized(Results& r, std::size_t B, std::size_t N, bool forces, int pairs) {
     pet_results out{};
