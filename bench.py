@@ -96,6 +96,27 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Libraries under the GPU arm write to stdout (NCCL prints its version when its first communicator is made): from
+    here on everything written to stdout goes to stderr, and emit() alone writes to the real stdout."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    if _RESULT_FD is None:
+        print(line, flush=True)
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, (line + "\n").encode())
+
+
 def make_model(tmp, shape):
     from pet_kokkos_b200 import checkpoint as ck
     return ck.write_random_checkpoint(Path(tmp) / f"bench_{shape}", shape, seed=0, init="n002")
@@ -238,7 +259,7 @@ def run_one_cell(args):
     if rank == 0:
         value = n_total * args.steps / wall
         listed = len(fields["positions"])
-        print(json.dumps({
+        emit(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": step_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
@@ -371,7 +392,7 @@ def run_ours(args):
             threads = os.cpu_count() or 1
             na, t, kind = time_cpu(jp, sp, cs, 2, 1, threads)
             cpu = {"value": na / float(np.mean(t)), "unit": UNIT, "cores": threads, "kind": kind, "sample": what}
-        print(json.dumps({
+        emit(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": step_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"native": "f32", "tf32": "tf32", "bf16": "bf16", "3xtf32": "f32 (3xTF32)"}[args.gemm],
@@ -401,6 +422,7 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
+    keep_stdout_for_the_result()
     if args.workload == "diamond13824":
         return run_one_cell(args)
     return run_ours(args)
