@@ -197,7 +197,7 @@ class EdgeListView:
 class Calculator:
     """A loaded model on one GPU.  Reuse one across calls: it holds the scratch pools."""
 
-    def __init__(self, model_json, model_weights=None, gemm=None, device=-1, graphs=None):
+    def __init__(self, model_json, model_weights=None, gemm=None, device=-1, graphs=None, md_fixed_shapes=None):
         self._h = None
         self._lib = load_library()
         if model_weights is None:  # a path prefix, as the reference's resolve_model accepts
@@ -208,6 +208,8 @@ class Calculator:
             o.gemm_mode = GEMM_MODES[gemm] if isinstance(gemm, str) else int(gemm)
         if graphs is not None:
             o.graphs = int(bool(graphs))
+        if md_fixed_shapes is not None:  # Options::md_fixed_shapes (calculator.hpp:111-116)
+            o.md_fixed_shapes = int(bool(md_fixed_shapes))
         h = C.c_void_p()
         rc = self._lib.pet_calc_create(os.fsencode(model_json), os.fsencode(model_weights), C.byref(o), C.byref(h))
         if rc:

@@ -62,10 +62,11 @@ __global__ void k_orphan_forces(double* __restrict__ forces, const double* __res
     for (int c = 0; c < 3; ++c) forces[3 * size_t(a) + c] -= eg[3 * size_t(oedge[k]) + c];
 }
 
+// `skip`, unless null, is the fixed-shape overflow flag: a step that did not fit adds nothing (it is redone).
 __global__ void k_add_arrays(double* __restrict__ f, const double* __restrict__ forces, double* __restrict__ e,
-                             const double* __restrict__ per_atom, int N) {
+                             const double* __restrict__ per_atom, int N, const int* __restrict__ skip) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= N) return;
+  if (i >= N || (skip && *skip)) return;
   if (f)
     for (int c = 0; c < 3; ++c) f[3 * size_t(i) + c] += forces[3 * size_t(i) + c];
   if (e) e[i] += per_atom[i];
@@ -74,9 +75,9 @@ __global__ void k_add_arrays(double* __restrict__ f, const double* __restrict__ 
 // Each directed edge's sym(v (x) g), half to each end, gathered per atom (md_atom_virial, src/calculator.cpp:846-868).
 __global__ void k_atom_virial(double* __restrict__ w, const double* __restrict__ eg, const double* __restrict__ vec,
                               const int* __restrict__ roff, const int* __restrict__ rrev, const int* __restrict__ ooff,
-                              const int* __restrict__ oedge, int N, double scale) {
+                              const int* __restrict__ oedge, int N, double scale, const int* __restrict__ skip) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= N) return;
+  if (i >= N || (skip && *skip)) return;
   double s[6] = {0, 0, 0, 0, 0, 0};
   auto add = [&](int e) {
     const double* v = vec + 3 * size_t(e);
@@ -108,6 +109,7 @@ Engine::Engine(const std::string& json, const std::string& weights, const pet_op
   else PETB_CUDA(cudaGetDevice(&device));
   gemm_mode = opts && opts->gemm_mode >= 0 ? opts->gemm_mode : env_gemm_mode();
   graphs = (opts && opts->graphs >= 0 ? opts->graphs : env_int("PET_GRAPHS", 1)) != 0;
+  md_fixed = (opts && opts->md_fixed_shapes >= 0 ? opts->md_fixed_shapes : env_int("PET_MD_FIXED", 0)) != 0;
   PETB_CUDA(cudaStreamCreateWithFlags(&st.s, cudaStreamNonBlocking));
   PETB_CUDA(cudaEventCreate(&ev0));
   PETB_CUDA(cudaEventCreate(&ev1));
@@ -496,6 +498,9 @@ void Engine::set_neighbors(const pet_edge_list* v) {
     PETB_CUDA(cudaMemcpyAsync(s.oedge, oedge.data(), 4 * size_t(s.n_orphan), cudaMemcpyHostToDevice, st.s));
     PETB_CUDA(cudaStreamSynchronize(st.s));
   }
+  s.caps_valid = false, s.e_cap = s.m_cap = 0;
+  s.overflow = A.alloc<int>(1);
+  PETB_CUDA(cudaMemsetAsync(s.overflow, 0, sizeof(int), st.s));
   s.has_exchange = v->exchange != nullptr;
   s.n_remote = 0, s.remote_raw = nullptr;
   if (s.has_exchange) {
@@ -539,7 +544,17 @@ static StepOut session_step(Engine& I, const double* positions, bool on_device, 
   edge_vectors(st, s.re, s.pos, s.cell);
   // With an exchange only the owned atoms are centres (token rows); ghosts are neighbours.
   const int NC = s.has_exchange ? s.n_local : N;
-  PackedEdges pk = pack_edges(st, I.nbr_arena, s.re, NC, s.species, I.model->cutoff_spec(), I.pinned);
+  const bool fixed = I.md_fixed && s.caps_valid && !s.has_exchange && N > 0;
+  PackedEdges pk;
+  if (fixed) {  // nothing is read back: the shapes are the capacities, the overflow flag travels with the results
+    pk = pack_edges_fixed(st, I.nbr_arena, s.re, NC, s.species, I.model->cutoff_spec(), s.e_cap, s.m_cap, s.pairs, s.overflow);
+  } else {
+    pk = pack_edges(st, I.nbr_arena, s.re, NC, s.species, I.model->cutoff_spec(), I.pinned);
+    if (I.md_fixed && !s.has_exchange) {  // size the capacities with room to move (src/device_geometry.cpp:749-777)
+      s.e_cap = pk.E + pk.E / 20 + 64, s.m_cap = pk.M + 2, s.pairs = pk.pairs, s.caps_valid = true;
+      PETB_CUDA(cudaMemsetAsync(s.overflow, 0, sizeof(int), st.s));
+    }
+  }
   pk.n_atoms = N, pk.n_local = s.n_local, pk.B = 1, pk.sid = s.sid, pk.soff = s.soff;
   if (s.has_exchange) {
     Arena& A = I.nbr_arena;
@@ -583,10 +598,23 @@ static StepOut session_step(Engine& I, const double* positions, bool on_device, 
   return so;
 }
 
+// True when the latest fixed-shape step outgrew its capacities: they are dropped, and the caller redoes the step,
+// which then runs with the shapes read back and sizes new ones.
+static bool fixed_step_overflowed(Engine& I) {
+  Session& s = I.md;
+  if (!I.md_fixed || !s.caps_valid || s.has_exchange || !s.overflow) return false;
+  PETB_CUDA(cudaMemcpyAsync(I.pinned + 8, s.overflow, sizeof(int), cudaMemcpyDeviceToHost, I.st.s));
+  PETB_CUDA(cudaStreamSynchronize(I.st.s));
+  if (I.pinned[8] == 0) return false;
+  s.caps_valid = false;
+  return true;
+}
+
 void Engine::compute_step(const double* positions, const double* cell, bool forces, bool edge_gradients, pet_results* out) {
   PETB_CUDA(cudaSetDevice(device));
   if (!positions && md.n_atoms > 0) throw Error(2, "pet: no positions given");
-  const StepOut so = session_step(*this, positions, false, cell, forces);
+  StepOut so = session_step(*this, positions, false, cell, forces);
+  if (fixed_step_overflowed(*this)) so = session_step(*this, positions, false, cell, forces);
   std::vector<double> g;
   if (forces && edge_gradients && out && out->edge_gradient && so.eg_raw) {
     g.resize(3 * size_t(md.E));
@@ -605,24 +633,33 @@ void Engine::compute_step_device(const pet_device_arrays* a, const double* cell,
   PETB_CUDA(cudaSetDevice(device));
   if (!a || !a->positions) throw Error(2, "pet: no device positions given");
   const bool forces = a->forces != nullptr;
-  const StepOut so = session_step(*this, a->positions, true, cell, forces);
   const int N = md.n_atoms;
   pet_totals t{};
-  if (have_out && N > 0) {
-    k_add_arrays<<<cdiv(N, 256), 256, 0, st.s>>>(a->forces, last_out.f.forces, a->per_atom_energy, last_out.per_atom, N);
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    const StepOut so = session_step(*this, a->positions, true, cell, forces);
+    if (!(have_out && N > 0)) break;
+    // the adds are skipped on the device when a fixed-shape step did not fit: that step is redone below
+    const int* skip = (md_fixed && md.caps_valid && !md.has_exchange) ? md.overflow : nullptr;
+    k_add_arrays<<<cdiv(N, 256), 256, 0, st.s>>>(a->forces, last_out.f.forces, a->per_atom_energy, last_out.per_atom, N, skip);
     PETB_LAUNCH_CHECK(st);
     if (a->per_atom_virial && forces && so.eg_raw) {
       k_atom_virial<<<cdiv(N, 256), 256, 0, st.s>>>(a->per_atom_virial, so.eg_raw, md.re.vec, md.re.off, md.re.reverse,
-                                                    md.n_orphan > 0 ? md.ooff : nullptr, md.oedge, N, 0.5 * a->virial_scale);
+                                                    md.n_orphan > 0 ? md.ooff : nullptr, md.oedge, N, 0.5 * a->virial_scale, skip);
       PETB_LAUNCH_CHECK(st);
     }
     double* h = reinterpret_cast<double*>(pinned + 16);
     PETB_CUDA(cudaMemcpyAsync(h, last_out.f.energy, 8, cudaMemcpyDeviceToHost, st.s));
     if (forces) PETB_CUDA(cudaMemcpyAsync(h + 1, last_out.f.vir6, 48, cudaMemcpyDeviceToHost, st.s));
+    if (skip) PETB_CUDA(cudaMemcpyAsync(pinned + 8, md.overflow, sizeof(int), cudaMemcpyDeviceToHost, st.s));
     PETB_CUDA(cudaStreamSynchronize(st.s));
+    if (skip && pinned[8] != 0) {  // outgrown: drop the capacities and run the step again, read back and resized
+      md.caps_valid = false;
+      continue;
+    }
     t.energy = h[0];
     if (forces)
       for (int k = 0; k < 6; ++k) t.virial[k] = h[1 + k];
+    break;
   }
   if (totals) *totals = t;
 }

@@ -35,6 +35,12 @@ struct Session {
   std::vector<int> src, dir;  // each directed edge's pair in the engine's list, and its sign
   // Over several ranks with ghosts one cutoff deep (EdgeListView::exchange): the engine's callbacks, and the
   // owned-atom -> ghost edges in list order as raw edge indices (the reference's remote_raw).
+  // Fixed shapes (Options::md_fixed_shapes): row and neighbour capacities kept from step to step, sized by an
+  // eager step with room to move, and grown (the step redone) when a step outgrows them.
+  bool caps_valid = false;
+  int e_cap = 0, m_cap = 0;
+  double pairs = 0.0;
+  int* overflow = nullptr;  // device flag: the latest fixed-shape step did not fit
   bool has_exchange = false;
   pet_exchange exchange{};
   int n_remote = 0;
@@ -63,6 +69,7 @@ struct Engine {
   int device = 0;
   int gemm_mode = 0;
   bool graphs = true;
+  bool md_fixed = false;  // Options::md_fixed_shapes / PET_MD_FIXED
   Stream st;
   Profiler prof;
   Checkpoint ckpt;

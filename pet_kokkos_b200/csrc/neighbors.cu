@@ -367,14 +367,15 @@ __global__ void k_pack(int NC, RawEdges re, PackedEdges pk, CutoffSpec cs) {
   const int a = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (a >= NC) return;
   int row = pk.off[a];
+  const int row_end = pk.off[a + 1];  // with fixed shapes an atom's rows may be fewer than its kept edges (overflow)
   const int e1 = re.off[a + 1];
   for (int e0 = re.off[a]; e0 < e1; e0 += 32) {
     const int e = e0 + lane;
     const bool keep = e < e1 && re.dist[e] <= cs.cutoff;
     const unsigned m = __ballot_sync(0xffffffffu, keep);
     if (e < e1) {
-      if (keep) {
-        const int p = row + __popc(m & ((1u << lane) - 1u));
+      const int p = row + __popc(m & ((1u << lane) - 1u));
+      if (keep && p < row_end) {
         const int j = re.j[e];
         pk.packed_of_raw[e] = p;
         pk.raw_of[p] = e;
@@ -395,8 +396,28 @@ __global__ void k_pack(int NC, RawEdges re, PackedEdges pk, CutoffSpec cs) {
 __global__ void k_pack_reverse(PackedEdges pk, const int* __restrict__ raw_reverse) {
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= pk.E) return;
+  if (p >= pk.off[pk.N]) {  // a capacity's dead row: no atom's, no partner
+    pk.reverse[p] = -1;
+    return;
+  }
   const int r = raw_reverse[pk.raw_of[p]];
   pk.reverse[p] = r >= 0 ? pk.packed_of_raw[r] : -1;
+}
+
+// Fixed shapes: more kept edges than rows, or more of one atom's than the attention kernels were sized for.
+__global__ void k_check_capacity(const int* __restrict__ off, int NC, const int* __restrict__ maxm, int e_cap, int m_cap,
+                                 int* __restrict__ overflow) {
+  if (off[NC] > e_cap || *maxm > m_cap) *overflow = 1;
+}
+// A step that does not fit still has to stay inside its buffers until the host sees the flag and redoes it: no atom
+// keeps more than m_cap rows, and no row lies past e_cap.
+__global__ void k_clamp_counts(int* __restrict__ kcnt, int NC, int m_cap) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a < NC && kcnt[a] > m_cap) kcnt[a] = m_cap;
+}
+__global__ void k_clamp_offsets(int* __restrict__ off, int NC, int e_cap) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a <= NC && off[a] > e_cap) off[a] = e_cap;
 }
 
 }  // namespace
@@ -510,6 +531,56 @@ PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int NC, con
       k_pack_reverse<<<cdiv(pk.E, 256), 256, 0, st.s>>>(pk, re.reverse);
       PETB_LAUNCH_CHECK(st);
     }
+  }
+  return pk;
+}
+
+// The same with the shapes given: E_cap rows (the kept edges packed into the first of them, the rest dead: zero
+// geometry, zero weight, no partner, in no atom's range) and M_cap as the most edges of an atom, so that nothing
+// is read back and a stepping loop keeps one set of shapes (the reference's edge_capacity, src/model.cpp:549-567).
+// *overflow is set on the device when the step does not fit; the caller reads it with the results.
+PackedEdges pack_edges_fixed(Stream& st, Arena& arena, const RawEdges& re, int NC, const int* atom_species, const CutoffSpec& cs,
+                             int e_cap, int m_cap, double pairs, int* overflow) {
+  PackedEdges pk;
+  pk.N = NC, pk.E = e_cap, pk.M = m_cap, pk.pairs = pairs;
+  pk.atom_species = atom_species;
+  pk.off = arena.alloc<int>(NC + 1);
+  const ProfScope ps(st, PC_GEOMETRY, 0.0, 60.0 * double(re.E) + 8.0 * NC);
+  int* kcnt = arena.alloc<int>(NC + 4);
+  int* maxm = kcnt + NC;
+  unsigned long long* pr = reinterpret_cast<unsigned long long*>(arena.alloc_bytes(8));
+  PETB_CUDA(cudaMemsetAsync(maxm, 0, sizeof(int), st.s));
+  PETB_CUDA(cudaMemsetAsync(pr, 0, 8, st.s));
+  k_keep_count<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re.off, re.dist, cs.cutoff, kcnt, maxm, pr);
+  PETB_LAUNCH_CHECK(st);
+  k_clamp_counts<<<cdiv(NC, 256), 256, 0, st.s>>>(kcnt, NC, m_cap);  // maxm already holds the unclamped maximum
+  PETB_LAUNCH_CHECK(st);
+  exclusive_scan(st, arena, kcnt, pk.off, NC);
+  k_check_capacity<<<1, 1, 0, st.s>>>(pk.off, NC, maxm, e_cap, m_cap, overflow);
+  PETB_LAUNCH_CHECK(st);
+  k_clamp_offsets<<<cdiv(NC + 1, 256), 256, 0, st.s>>>(pk.off, NC, e_cap);
+  PETB_LAUNCH_CHECK(st);
+  const size_t Ea = e_cap > 0 ? e_cap : 1, Er = re.E > 0 ? re.E : 1;
+  // one block for the row arrays, cleared in one go: dead rows read as zeros
+  const size_t bytes = Ea * (4 * 4 + 3 * 8 + 8 + 4 + 4);
+  char* block = static_cast<char*>(arena.alloc_bytes(bytes + 64));
+  PETB_CUDA(cudaMemsetAsync(block, 0, bytes + 64, st.s));
+  pk.vec = reinterpret_cast<double*>(block), block += 24 * Ea;
+  pk.dist = reinterpret_cast<double*>(block), block += 8 * Ea;
+  pk.center = reinterpret_cast<int*>(block), block += 4 * Ea;
+  pk.nbr = reinterpret_cast<int*>(block), block += 4 * Ea;
+  pk.species = reinterpret_cast<int*>(block), block += 4 * Ea;
+  pk.raw_of = reinterpret_cast<int*>(block), block += 4 * Ea;
+  pk.cut = reinterpret_cast<float*>(block), block += 4 * Ea;
+  pk.reverse = reinterpret_cast<int*>(block);
+  pk.packed_of_raw = arena.alloc<int>(Er);
+  if (re.E > 0) {
+    k_pack<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re, pk, cs);
+    PETB_LAUNCH_CHECK(st);
+  }
+  if (e_cap > 0) {
+    k_pack_reverse<<<cdiv(e_cap, 256), 256, 0, st.s>>>(pk, re.reverse);
+    PETB_LAUNCH_CHECK(st);
   }
   return pk;
 }

@@ -96,5 +96,7 @@ PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int n_centr
 
 // int exclusive scan: out[0..n] (n+1 values, out[n] = total).
 void exclusive_scan(Stream& st, Arena& arena, const int* in, int* out, int n);
+PackedEdges pack_edges_fixed(Stream& st, Arena& arena, const RawEdges& re, int NC, const int* atom_species, const CutoffSpec& cs,
+                             int e_cap, int m_cap, double pairs, int* overflow);
 
 }  // namespace petb

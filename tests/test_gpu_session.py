@@ -137,3 +137,79 @@ def test_domain_decomposition_on_one_gpu(calc, world):
     assert abs(e - ref.energy[0]) <= 1e-5 * abs(ref.energy[0])
     assert np.abs(F - ref.forces).max() <= 1e-4 * max(1.0, np.abs(ref.forces).max())
     assert np.abs(W - ref.virial[0]).max() <= 1e-4 * max(1.0, np.abs(ref.virial).max())
+
+
+@pytest.mark.parametrize("gemm", ["native", "3xtf32"])
+def test_fixed_shape_stepping_equals_plain_stepping(lib_path, models, gemm):
+    """Options::md_fixed_shapes (include/pet/calculator.hpp:111-116): capacities for the kept edges and the neighbour
+    count, sized by the first step and kept while the atoms move, so nothing is read back and the recorded pass is
+    replayed although the number of kept edges changes; a step that outgrows them is redone. Every step must give the
+    bits of a calculator without fixed shapes."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("tiny", "feedforward", "scaled", 1)
+    plain = Calculator(jp, sp, gemm=gemm)
+    fixed = Calculator(jp, sp, gemm=gemm, md_fixed_shapes=True)
+    s = st.diamond(2, jitter=0.05, seed=4)
+    view = full_list(s, plain.cutoff, skin=1.0)
+    plain.set_neighbors(view)
+    fixed.set_neighbors(view)
+    rng = np.random.default_rng(3)
+    x = s["positions"].copy()
+    edges = []
+    for step in range(8):
+        if step == 5:  # squeeze: many listed pairs come inside the cutoff at once, more than the capacity's headroom
+            x = x * 0.93
+            cell = s["cell"] * 0.93
+        else:
+            x = x + rng.normal(0, 0.02, x.shape)
+            cell = s["cell"] if step < 5 else s["cell"] * 0.93
+        a, b = plain.compute_step(x, cell), fixed.compute_step(x, cell)
+        edges.append(plain.last_shapes()[1])
+        assert (a.energy == b.energy).all() and (a.forces == b.forces).all() and (a.virial == b.virial).all(), step
+    assert len(set(edges)) > 2, "the number of kept edges has to change for this test to mean anything"
+    assert edges[5] > 1.05 * edges[4] + 64, "the squeeze has to outgrow the capacity"
+    assert fixed.graph_replays >= 3 and plain.graph_replays == 0
+    plain.close()
+    fixed.close()
+
+
+@pytest.mark.parametrize("fixed", [False, True])
+def test_device_arrays_step_adds_into_the_engines_arrays(lib_path, models, fixed):
+    """Calculator::compute_step(const DeviceArrays&, cell) (include/pet/calculator.hpp:248-259): positions read from
+    and forces, per-atom energies and per-atom virials added into device arrays; only the totals come back. Checked
+    against the host-array compute_step, over steps that change the number of kept edges and (with fixed shapes) one
+    that outgrows the capacities and is redone without adding twice."""
+    import torch
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("tiny", "feedforward", "scaled", 1)
+    host = Calculator(jp, sp)
+    dev = Calculator(jp, sp, md_fixed_shapes=fixed)
+    s = st.diamond(2, jitter=0.05, seed=5)
+    view = full_list(s, host.cutoff, skin=1.0)
+    host.set_neighbors(view)
+    dev.set_neighbors(view)
+    N = s["n_atoms"]
+    rng = np.random.default_rng(7)
+    x = s["positions"].copy()
+    for step in range(6):
+        squeeze = step >= 4
+        if step == 4:
+            x = x * 0.93
+        else:
+            x = x + rng.normal(0, 0.02, x.shape)
+        cell = s["cell"] * (0.93 if squeeze else 1.0)
+        ref = host.compute_step(x, cell)
+        d_x = torch.tensor(x, dtype=torch.float64, device="cuda")
+        d_f = torch.full((N, 3), 1.5, dtype=torch.float64, device="cuda")     # "added into": start from something
+        d_e = torch.full((N,), -2.0, dtype=torch.float64, device="cuda")
+        d_w = torch.zeros((N, 6), dtype=torch.float64, device="cuda")
+        torch.cuda.synchronize()
+        energy, virial = dev.compute_step_device(d_x.data_ptr(), d_f.data_ptr(), d_e.data_ptr(), d_w.data_ptr(), -1.0, cell)
+        torch.cuda.synchronize()
+        assert energy == ref.energy[0] and (virial == ref.virial[0]).all()
+        assert (d_f.cpu().numpy() - 1.5 == ref.forces).all() or np.abs(d_f.cpu().numpy() - 1.5 - ref.forces).max() <= 1e-12
+        np.testing.assert_allclose(d_e.cpu().numpy() + 2.0, ref.per_atom_energy, rtol=0, atol=1e-12)
+        np.testing.assert_allclose(d_w.cpu().numpy().sum(0), -1.0 * ref.virial[0], rtol=0,
+                                   atol=1e-9 * max(1.0, np.abs(ref.virial).max()))
+    host.close()
+    dev.close()
