@@ -208,6 +208,74 @@ def cosine_cutoff_f32(d, rc, width):
     return 0.5 * (1.0 + np.cos(np.float32(math.pi) * x).astype(np.float64))
 
 
+def bump_dcutoff_dr_f32(d, rc, width):
+    """include/pet/cutoff.hpp:44-51 (dev_bump_dcutoff_dr): d(bump)/d(rc), transcendentals in float32."""
+    x = ((d - (rc - width)) / width).astype(np.float32)
+    ps = np.float32(math.pi) * np.clip(x, np.float32(1e-6), np.float32(1) - np.float32(1e-6))
+    si = np.sin(ps)
+    tt = np.tanh(np.cos(ps) / si)
+    val = 0.5 * (1.0 - (tt * tt).astype(np.float64)) * ((np.float32(math.pi) / (si * si)) / np.float32(width)).astype(np.float64)
+    return np.where((x <= 0) | (x >= 1), 0.0, val)
+
+
+def adaptive_probes(cutoff, width_adaptive):
+    """src/neighbors.cpp:23-27: from 0.5 A to the cutoff, a quarter of the taper width apart."""
+    p, r = [], 0.5
+    while r < cutoff - 1e-12:
+        p.append(r)
+        r += width_adaptive / 4.0
+    return np.array(p)
+
+
+SOLVER_MIN_CUTOFF_FACTOR, SOLVER_ITERS, SOLVER_DN_FLOOR = 1.0 / 16.0, 10, 1e-6  # include/pet/cutoff.hpp:53-57
+
+
+def adaptive_cutoffs_solver(N, center, dist, cutoff, width, target):
+    """src/device_neighbors.cpp:26-67 (solver_cutoffs): Newton-bisection for n_total(r) = target, then one
+    implicit-function step. Returns (cutoff, root r, slope dn with 0 for a clamped atom), each [N]."""
+    rmax, lo_bound = cutoff, cutoff * SOLVER_MIN_CUTOFF_FACTOR
+
+    def count(r):
+        n = np.bincount(center, weights=bump_cutoff_f32(dist, r[center], width), minlength=N)
+        dn = np.bincount(center, weights=bump_dcutoff_dr_f32(dist, r[center], width), minlength=N)
+        x = r / rmax
+        return n + target * x ** 3, dn + 3.0 * target * x * x / rmax
+    r_lo, r_hi, r = np.zeros(N), np.full(N, rmax), np.full(N, 0.5 * rmax)
+    for _ in range(SOLVER_ITERS):
+        n, dn = count(r)
+        f = n - target
+        r_lo, r_hi = np.where(f <= 0, r, r_lo), np.where(f <= 0, r_hi, r)
+        newton = r - f / np.maximum(dn, SOLVER_DN_FLOOR)
+        r = np.where((newton >= r_lo) & (newton <= r_hi), newton, 0.5 * (r_lo + r_hi))
+    n, dn = count(r)
+    dn_root = np.maximum(dn, SOLVER_DN_FLOOR)
+    adapted = np.minimum(np.maximum(r - (n - target) / dn_root, lo_bound), rmax)
+    return adapted, r, np.where((adapted > lo_bound) & (adapted < rmax), dn_root, 0.0)
+
+
+def adaptive_cutoffs_grid(N, center, dist, cutoff, width, target):
+    """src/device_neighbors.cpp:69-136 (grid_cutoffs): a softmax-weighted average of probe radii."""
+    probes = adaptive_probes(cutoff, width)
+    P = len(probes)
+    if P == 0:
+        return np.full(N, cutoff)
+    eff = np.zeros((N, P))
+    for p in range(P):
+        eff[:, p] = np.bincount(center, weights=bump_cutoff_f32(dist, np.full_like(dist, probes[p]), width), minlength=N)
+    x = np.arange(P) / (P - 1) if P > 1 else np.zeros(1)
+    diff = eff - target + target * x ** 3
+    if P == 1:
+        grad = np.abs(diff) * 0.5 + 1e-12
+    else:
+        g = np.empty_like(diff)
+        g[:, 0], g[:, -1] = diff[:, 1] - diff[:, 0], diff[:, -1] - diff[:, -2]
+        g[:, 1:-1] = 0.5 * (diff[:, 2:] - diff[:, :-2])
+        grad = np.maximum(np.abs(g), 1e-12)
+    lw = -0.5 * (diff / grad) ** 2
+    w = np.exp(lw - lw.max(1, keepdims=True))
+    return (w * probes).sum(1) / w.sum(1)
+
+
 def reverse_edges(idx, offsets):
     """Partner (j, i, -shift) of every edge, -1 if none (src/device_neighbors.cpp:157-176)."""
     key = {}
@@ -216,7 +284,7 @@ def reverse_edges(idx, offsets):
     return np.array([key.get((j, i, -a, -b, -c), -1) for (i, j, a, b, c) in idx.tolist()], np.int64)
 
 
-def build_edges(systems, species_to_index, cutoff, width, cutoff_function="Bump", search="cells"):
+def build_edges(systems, species_to_index, cutoff, width, cutoff_function="Bump", search="cells", adaptive=None):
     """Packed model edges for a batch: the reference's edge_geometry + pack_edges, no adaptive cutoff.
 
     src/device_neighbors.cpp:242-323 (keep d <= rc, cutoff factor, slot = number
@@ -239,9 +307,19 @@ def build_edges(systems, species_to_index, cutoff, width, cutoff_function="Bump"
     dist = np.concatenate([p[2] for p in parts])
     raw = np.concatenate([gi[:, None], gj[:, None], shift], 1)
     raw_rev = reverse_edges(raw, None)
-    keep = dist <= cutoff
+    # Each edge's cutoff: the model's, or with an adaptive cutoff the mean of its two atoms'
+    # (src/device_neighbors.cpp:243-252). adaptive = {"method": "solver"|"grid", "target": n, "width": w}.
+    rc = np.full_like(dist, cutoff)
+    acut = None
+    if adaptive:
+        if adaptive["method"] == "solver":
+            acut, _, _ = adaptive_cutoffs_solver(N, gi, dist, cutoff, adaptive["width"], adaptive["target"])
+        else:
+            acut = adaptive_cutoffs_grid(N, gi, dist, cutoff, adaptive["width"], adaptive["target"])
+        rc = 0.5 * (acut[gi] + acut[gj])
+    keep = dist <= rc
     fn = bump_cutoff_f32 if cutoff_function == "Bump" else cosine_cutoff_f32
-    cut = fn(dist, np.full_like(dist, cutoff), width).astype(np.float32)
+    cut = fn(dist, rc, width).astype(np.float32)
     kept_idx = np.nonzero(keep)[0]
     packed_of_raw = np.full(len(dist), -1, np.int64)
     packed_of_raw[kept_idx] = np.arange(len(kept_idx))
@@ -257,6 +335,8 @@ def build_edges(systems, species_to_index, cutoff, width, cutoff_function="Bump"
         "vec": vec[kept_idx], "dist": dist[kept_idx], "cut": cut[kept_idx],
         "max_neighbors": int(max(counts.max() if N else 0, 1)),
         "raw": raw, "raw_vec": vec, "raw_dist": dist,
+        "raw_center": gi, "raw_neighbor": gj, "raw_reverse": raw_rev, "kept_idx": kept_idx, "rc": rc[kept_idx],
+        "atom_cutoff": acut,
     }
 
 

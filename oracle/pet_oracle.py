@@ -115,6 +115,65 @@ def cosine_cutoff_t(d, rc, width, dtype):
     return 0.5 * (1.0 + torch.cos(math.pi * x))
 
 
+def bump_dcutoff_dr_t(d, rc, width, dtype):
+    """include/pet/cutoff.hpp:44-51, the slope the solver root-finds with (not differentiated)."""
+    x = ((d - (rc - width)) / width).to(dtype)
+    ps = math.pi * x.clamp(1e-6, 1 - 1e-6)
+    si = torch.sin(ps)
+    tt = torch.tanh(torch.cos(ps) / si)
+    val = 0.5 * (1.0 - (tt * tt).double()) * ((math.pi / (si * si)) / width).double()
+    return torch.where((x <= 0) | (x >= 1), torch.zeros_like(val), val)
+
+
+def adaptive_cutoffs_t(h, N, center, dist, dtype):
+    """Each atom's adaptive cutoff as a differentiable function of ALL its raw distances.
+
+    Solver (src/device_neighbors.cpp:26-67): the iterations run without gradient; the last line, one
+    implicit-function step cutoff = r - (n_total(r) - target) / dn with r and dn held constant, carries it
+    (src/forces.cpp:93-110). Grid (src/device_neighbors.cpp:69-136; backward src/forces.cpp:111-196): differentiated
+    as written. Both taper the neighbour count with the bump whatever the model's own cutoff function."""
+    rmax, width, target = h["cutoff"], h["cutoff_width_adaptive"], float(h["num_neighbors_adaptive"])
+    c = torch.from_numpy(np.asarray(center))
+    bump = lambda d, r: bump_cutoff_t(d, r, width, dtype).double()
+    if h["adaptive_cutoff_method"] == "solver":
+        lo_bound = rmax * nbo.SOLVER_MIN_CUTOFF_FACTOR
+
+        def count(r, d):
+            n = torch.zeros(N, dtype=torch.float64).index_add(0, c, bump(d, r[c]))
+            dn = torch.zeros(N, dtype=torch.float64).index_add(0, c, bump_dcutoff_dr_t(d, r[c], width, dtype))
+            x = r / rmax
+            return n + target * x ** 3, dn + 3.0 * target * x * x / rmax
+        with torch.no_grad():
+            dd = dist.detach()
+            r_lo, r_hi = torch.zeros(N, dtype=torch.float64), torch.full((N,), rmax, dtype=torch.float64)
+            r = torch.full((N,), 0.5 * rmax, dtype=torch.float64)
+            for _ in range(nbo.SOLVER_ITERS):
+                n, dn = count(r, dd)
+                f = n - target
+                r_lo, r_hi = torch.where(f <= 0, r, r_lo), torch.where(f <= 0, r_hi, r)
+                newton = r - f / dn.clamp(min=nbo.SOLVER_DN_FLOOR)
+                r = torch.where((newton >= r_lo) & (newton <= r_hi), newton, 0.5 * (r_lo + r_hi))
+            _, dn = count(r, dd)
+            dn_root = dn.clamp(min=nbo.SOLVER_DN_FLOOR)
+        n = torch.zeros(N, dtype=torch.float64).index_add(0, c, bump(dist, r[c])) + target * (r / rmax) ** 3
+        return (r - (n - target) / dn_root).clamp(lo_bound, rmax)
+    probes = torch.from_numpy(nbo.adaptive_probes(rmax, width))
+    P = len(probes)
+    if P == 0:
+        return torch.full((N,), rmax, dtype=torch.float64)
+    eff = torch.stack([torch.zeros(N, dtype=torch.float64).index_add(0, c, bump(dist, torch.full_like(dist, float(probes[p]))))
+                       for p in range(P)], 1)
+    x = torch.arange(P, dtype=torch.float64) / (P - 1) if P > 1 else torch.zeros(1, dtype=torch.float64)
+    diff = eff - target + target * x ** 3
+    if P == 1:
+        grad = diff.abs() * 0.5 + 1e-12
+    else:
+        g = torch.cat([(diff[:, 1] - diff[:, 0])[:, None], 0.5 * (diff[:, 2:] - diff[:, :-2]), (diff[:, -1] - diff[:, -2])[:, None]], 1)
+        grad = g.abs().clamp(min=1e-12)
+    w = torch.softmax(-0.5 * (diff / grad) ** 2, 1)
+    return (w * probes).sum(1)
+
+
 def attention(qkv, cf, tok_index, tok_valid, N, H, hd, temperature):
     """Per-atom multi-head attention with the log-cutoff key bias.
 
@@ -156,7 +215,7 @@ def token_index(off, N):
     return idx
 
 
-def forward_feedforward(W: Weights, ed, vec, want=None):
+def forward_feedforward(W: Weights, ed, vec, want=None, rc=None):
     """The feedforward featurizer's energy: src/feedforward.cpp:34-197 (ff_layer) and :338-394 (ff_pass).
 
     ed: packed edges from neighbors_oracle.build_edges; vec: [E,3] float64 tensor
@@ -175,7 +234,7 @@ def forward_feedforward(W: Weights, ed, vec, want=None):
 
     dist = torch.sqrt((vec * vec).sum(-1))
     fn = bump_cutoff_t if h["cutoff_function"] == "Bump" else cosine_cutoff_t
-    cut = fn(dist, h["cutoff"], h["cutoff_width"], dt)               # [E] network dtype
+    cut = fn(dist, h["cutoff"] if rc is None else rc, h["cutoff_width"], dt)   # [E] network dtype; rc: per-edge cutoffs
     tok_index = torch.from_numpy(token_index(off, N))
     tok_valid = tok_index >= 0
     S = tok_index.shape[1]
@@ -245,7 +304,7 @@ def forward_feedforward(W: Weights, ed, vec, want=None):
     return per_atom
 
 
-def forward_residual(W: Weights, ed, vec, want=None):
+def forward_residual(W: Weights, ed, vec, want=None, rc=None):
     """The residual featurizer: src/residual.cpp:13-62 (residual_layer) and :64-133 (residual_pass forward)."""
     h, dt = W.h, W.dtype
     N, E = ed["n_atoms"], len(ed["center"])
@@ -258,7 +317,7 @@ def forward_residual(W: Weights, ed, vec, want=None):
     center = torch.from_numpy(ed["center"])
     dist = torch.sqrt((vec * vec).sum(-1))
     fn = bump_cutoff_t if h["cutoff_function"] == "Bump" else cosine_cutoff_t
-    cut = fn(dist, h["cutoff"], h["cutoff_width"], dt)
+    cut = fn(dist, h["cutoff"] if rc is None else rc, h["cutoff_width"], dt)
     tok_index = torch.from_numpy(token_index(off, N))
     tok_valid = tok_index >= 0
     S = tok_index.shape[1]
@@ -311,6 +370,37 @@ def forward_residual(W: Weights, ed, vec, want=None):
     return W.meta["energy_scale"] * net.double() + comp[species]
 
 
+def _evaluate_adaptive(h, W, fwd, ed, dtype, forces, want):
+    """With an adaptive cutoff every raw edge's distance shapes its atom's cutoff, so the differentiable input is the
+    raw list, kept or not, and forces and virial are folded over it (src/forces.cpp:80-260,308-341)."""
+    N, B = ed["n_atoms"], ed["n_struct"]
+    raw_vec = torch.from_numpy(ed["raw_vec"]).clone().requires_grad_(forces)
+    kept = torch.from_numpy(ed["kept_idx"])
+    ri, rj = torch.from_numpy(ed["raw_center"]), torch.from_numpy(ed["raw_neighbor"])
+    with torch.set_grad_enabled(forces):
+        raw_dist = torch.sqrt((raw_vec * raw_vec).sum(-1))
+        acut = adaptive_cutoffs_t(h, N, ed["raw_center"], raw_dist, dtype)
+        rc = 0.5 * (acut[ri] + acut[rj])[kept]
+        per_atom = fwd(W, ed, raw_vec[kept], want, rc=rc)
+        sid = torch.from_numpy(ed["struct_id"])
+        energy = torch.zeros(B, dtype=torch.float64).index_add(0, sid, per_atom)
+        out = {"energy": energy.detach().numpy(), "per_atom_energy": per_atom.detach().numpy(), "edges": ed,
+               "atom_cutoff": acut.detach().numpy()}
+        if not forces:
+            return out
+        (g,) = torch.autograd.grad(per_atom.sum(), raw_vec)
+    g = g.double()
+    rev = torch.from_numpy(ed["raw_reverse"])
+    back = torch.where((rev >= 0)[:, None], g[rev.clamp(min=0)], torch.zeros_like(g))
+    F = torch.zeros(N, 3, dtype=torch.float64).index_add(0, ri, g - back)
+    w9 = (raw_vec.detach()[:, :, None] * g[:, None, :]).reshape(-1, 9)
+    W9 = torch.zeros(B, 9, dtype=torch.float64).index_add(0, sid[ri], w9)
+    voigt = torch.stack([W9[:, 0], W9[:, 4], W9[:, 8], 0.5 * (W9[:, 1] + W9[:, 3]), 0.5 * (W9[:, 2] + W9[:, 6]),
+                         0.5 * (W9[:, 5] + W9[:, 7])], 1)
+    out.update(forces=F.numpy(), virial=voigt.numpy(), edge_gradient=g.numpy())
+    return out
+
+
 def evaluate(meta, tensors, systems, dtype=torch.float32, forces=True, want=None, search="cells", threads=None):
     """Energy, per-atom energy, forces [N,3], virial [B,6] (Voigt xx yy zz xy xz yz) for a batch.
 
@@ -324,11 +414,17 @@ def evaluate(meta, tensors, systems, dtype=torch.float32, forces=True, want=None
     if isinstance(systems, dict) and "off" in systems:  # packed edges made elsewhere (an engine's own list)
         ed = systems
     else:
+        adaptive = None
+        if h.get("num_neighbors_adaptive"):
+            adaptive = {"method": h["adaptive_cutoff_method"], "target": float(h["num_neighbors_adaptive"]),
+                        "width": h["cutoff_width_adaptive"]}
         ed = nbo.build_edges(systems, meta["species_to_index"], h["cutoff"], h["cutoff_width"], h["cutoff_function"],
-                             search=search)
+                             search=search, adaptive=adaptive)
     W = Weights(meta, tensors, dtype)
-    vec = torch.from_numpy(ed["vec"]).clone().requires_grad_(forces)
     fwd = forward_feedforward if h["featurizer_type"] == "feedforward" else forward_residual
+    if ed.get("atom_cutoff") is not None:
+        return _evaluate_adaptive(h, W, fwd, ed, dtype, forces, want)
+    vec = torch.from_numpy(ed["vec"]).clone().requires_grad_(forces)
     with torch.set_grad_enabled(forces):
         per_atom = fwd(W, ed, vec, want)
         N, B = ed["n_atoms"], ed["n_struct"]

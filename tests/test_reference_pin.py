@@ -149,3 +149,20 @@ def test_engine_list_and_stepping_match_the_reference(reference, models, featuri
     for k in range(3):
         g = restated(moved[k])
         bands(g, {"energy": steps["energy"][k:k + 1], "forces": steps["forces"][k], "virial": steps["virial"][k:k + 1]})
+
+
+@pytest.mark.parametrize("method", ["solver", "grid"])
+def test_adaptive_cutoff_matches_the_reference(reference, tmp_path, method):
+    """The adaptive cutoff, both schemes (src/device_neighbors.cpp:26-136; backward src/forces.cpp:80-260,308-341):
+    each atom's cutoff from all its raw distances, pairs kept within the mean of their atoms' cutoffs, forces and
+    virial folded over the raw list. The reference implements it for the feedforward featurizer only."""
+    jp, sp = ck.write_random_checkpoint(tmp_path / f"ad_{method}", "tiny", "feedforward", seed=5, init="scaled",
+                                        num_neighbors_adaptive=16.0, adaptive_cutoff_method=method, cutoff=5.5)
+    meta, tens = ck.load_checkpoint(jp, sp)
+    systems = [st.diamond(2, jitter=0.08, seed=1), st.random_mixture(30, 8.0, seed=4), cluster(8, 3)]
+    ref = reference.ReferenceCalculator(str(jp), str(sp)).compute(systems)
+    got = po.evaluate(meta, tens, systems, dtype=torch.float32)
+    bands(got, ref)
+    ed = got["edges"]
+    assert len(ed["center"]) < 0.5 * len(ed["raw"]), "the adaptive cutoff has to drop edges for this test to mean anything"
+    assert got["atom_cutoff"].min() < 0.8 * got["atom_cutoff"].max()
