@@ -108,8 +108,11 @@ int pet_neighbor_list(pet_calc* c, const pet_system* systems, int n, pet_raw_edg
 
 double pet_cutoff(const pet_calc* c) { return c && c->e ? c->e->ckpt.hypers.cutoff : 0.0; }
 double pet_ghost_cutoff(const pet_calc* c) {
-  // One cutoff per message-passing layer (Calculator::ghost_cutoff, src/calculator.cpp:890-894).
-  return c && c->e ? c->e->ckpt.hypers.num_gnn_layers * c->e->ckpt.hypers.cutoff : 0.0;
+  // One cutoff per message-passing layer, and one more for an adaptive cutoff, which needs each of those atoms'
+  // complete neighbourhoods (Calculator::ghost_cutoff, src/calculator.cpp:890-894).
+  if (!c || !c->e) return 0.0;
+  const petb::Hypers& h = c->e->ckpt.hypers;
+  return (h.num_gnn_layers + (h.adaptive() ? 1 : 0)) * h.cutoff;
 }
 double pet_exchange_ghost_cutoff(const pet_calc* c) { return pet_cutoff(c); }
 double pet_energy_scale(const pet_calc* c) { return c && c->e ? c->e->ckpt.energy_scale : 0.0; }

@@ -188,7 +188,12 @@ Checkpoint::Checkpoint(const std::string& json_path, const std::string& safetens
     if (h.bool_or("zbl", false)) throw Error(1, "checkpoint: the ZBL term is not supported");
     if (h.bool_or("system_conditioning", false))
       throw Error(1, "checkpoint: system_conditioning models are outside this evaluator's scope");
-    if (p.adaptive()) throw Error(1, "checkpoint: adaptive-cutoff models are not implemented by this evaluator yet");
+    if (p.adaptive()) {
+      p.adaptive_solver = !choose("adaptive_cutoff_method", h.at("adaptive_cutoff_method").string(), "grid", "solver");
+      p.cutoff_width_adaptive = h.number_or("cutoff_width_adaptive", 0.5);
+      // as the reference (src/model.cpp): the adaptive cutoff is implemented for the feedforward featurizer
+      if (!p.feedforward) throw Error(1, "checkpoint: the residual featurizer with an adaptive cutoff is not implemented");
+    }
     energy_scale = j.at("energy_scale").number();
     n_species = j.at("n_species").integer();
     for (const auto& v : j.at("species_to_index").arr) species_to_index.push_back(v.integer());

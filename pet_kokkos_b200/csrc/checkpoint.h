@@ -45,6 +45,8 @@ struct Hypers {
   int cutoff_function = 0;  // 0 Bump, 1 Cosine
   double attention_temperature = 1.0, cutoff = 7.5, cutoff_width = 0.5;
   double num_neighbors_adaptive = -1.0;
+  bool adaptive_solver = false;        // adaptive_cutoff_method: grid | solver
+  double cutoff_width_adaptive = 0.5;
   bool adaptive() const { return num_neighbors_adaptive > 0.0; }
   bool expanded_node() const { return d_node != d_pet; }
 };

@@ -53,6 +53,13 @@ __global__ void k_live_fill(int* __restrict__ live, int* __restrict__ live_packe
   live[l] = r, live_packed[l] = k, remote_of[k] = l;
 }
 
+// eg(e) += gmag(e) v(e)
+__global__ void k_add_radial(double* __restrict__ eg, const double* __restrict__ gmag, const double* __restrict__ vec, int E) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  for (int c = 0; c < 3; ++c) eg[3 * size_t(e) + c] += gmag[e] * vec[3 * size_t(e) + c];
+}
+
 // An edge with no partner gives its target's share of the force itself (orphan_forces, src/forces.cpp:400-410).
 __global__ void k_orphan_forces(double* __restrict__ forces, const double* __restrict__ eg, const int* __restrict__ ooff,
                                 const int* __restrict__ oedge, int N) {
@@ -337,7 +344,9 @@ void Engine::compute_staged(bool forces) {
   wrap_positions(st, g, posw);
   RawEdges re = cell_list_search(st, nbr_arena, g, posw, ckpt.hypers.cutoff);
   find_reverse(st, re, g.Ntot);
-  PackedEdges pk = pack_edges(st, nbr_arena, re, g.Ntot, g.spec, model->cutoff_spec(), pinned);
+  const CutoffSpec cs = model->cutoff_spec();
+  const AdaptiveCut ad = adaptive_cutoffs(st, nbr_arena, re, g.Ntot, cs);
+  PackedEdges pk = pack_edges(st, nbr_arena, re, g.Ntot, g.spec, cs, pinned, ad);
   pk.n_atoms = g.Ntot, pk.n_local = g.Ntot, pk.B = g.B, pk.sid = g.sid, pk.soff = g.soff;
   last_B = g.B, last_N = g.Ntot;
   if (g.Ntot > 0 && g.B > 0) run_model(pk, forces);
@@ -395,7 +404,9 @@ void Engine::neighbor_list(const pet_system* systems, int B, pet_raw_edges* out)
     if (out->dist) PETB_CUDA(cudaMemcpyAsync(out->dist, re.dist, 8 * E, cudaMemcpyDeviceToHost, st.s));
     if (out->reverse) PETB_CUDA(cudaMemcpyAsync(out->reverse, re.reverse, 4 * E, cudaMemcpyDeviceToHost, st.s));
     if (out->cutoff) {
-      PackedEdges pk = pack_edges(st, nbr_arena, re, g.Ntot, g.spec, model->cutoff_spec(), pinned);
+      CutoffSpec cs = model->cutoff_spec();
+      cs.adaptive = 0;  // the raw list's own factors: the model's fixed cutoff
+      PackedEdges pk = pack_edges(st, nbr_arena, re, g.Ntot, g.spec, cs, pinned);
       if (pk.E != re.E) throw Error(3, "pet: a raw edge lies past the cutoff");
       PETB_CUDA(cudaMemcpyAsync(out->cutoff, pk.cut, 4 * E, cudaMemcpyDeviceToHost, st.s));
     }
@@ -545,11 +556,16 @@ static StepOut session_step(Engine& I, const double* positions, bool on_device, 
   // With an exchange only the owned atoms are centres (token rows); ghosts are neighbours.
   const int NC = s.has_exchange ? s.n_local : N;
   const bool fixed = I.md_fixed && s.caps_valid && !s.has_exchange && N > 0;
+  const CutoffSpec cs = I.model->cutoff_spec();
+  if (cs.adaptive && s.has_exchange)
+    throw Error(1, "pet: an adaptive cutoff over an exchange needs the per-atom moves (atoms_forward/atoms_reverse), which are not built");
+  // every listed atom's adaptive cutoff from the pairs it lists (ghosts without pairs keep the model's reach)
+  const AdaptiveCut ad = adaptive_cutoffs(st, I.nbr_arena, s.re, N, cs);
   PackedEdges pk;
   if (fixed) {  // nothing is read back: the shapes are the capacities, the overflow flag travels with the results
-    pk = pack_edges_fixed(st, I.nbr_arena, s.re, NC, s.species, I.model->cutoff_spec(), s.e_cap, s.m_cap, s.pairs, s.overflow);
+    pk = pack_edges_fixed(st, I.nbr_arena, s.re, NC, s.species, cs, s.e_cap, s.m_cap, s.pairs, s.overflow, ad);
   } else {
-    pk = pack_edges(st, I.nbr_arena, s.re, NC, s.species, I.model->cutoff_spec(), I.pinned);
+    pk = pack_edges(st, I.nbr_arena, s.re, NC, s.species, cs, I.pinned, ad);
     if (I.md_fixed && !s.has_exchange) {  // size the capacities with room to move (src/device_geometry.cpp:749-777)
       s.e_cap = pk.E + pk.E / 20 + 64, s.m_cap = pk.M + 2, s.pairs = pk.pairs, s.caps_valid = true;
       PETB_CUDA(cudaMemsetAsync(s.overflow, 0, sizeof(int), st.s));
@@ -589,6 +605,10 @@ static StepOut session_step(Engine& I, const double* positions, bool on_device, 
     k_raw_edge_grad<<<cdiv(s.E, 256), 256, 0, st.s>>>(so.eg_raw, I.last_out.f.edge_grad, pk.packed_of_raw, s.E,
                                                       I.model->energy_scale());
     PETB_LAUNCH_CHECK(st);
+    if (I.last_out.f.adaptive_gmag) {  // the adaptive cutoff's radial share, on every listed pair (src/forces.cpp:198-203)
+      k_add_radial<<<cdiv(s.E, 256), 256, 0, st.s>>>(so.eg_raw, I.last_out.f.adaptive_gmag, s.re.vec, s.E);
+      PETB_LAUNCH_CHECK(st);
+    }
     if (s.n_orphan > 0) {
       k_orphan_forces<<<cdiv(N, 256), 256, 0, st.s>>>(I.last_out.f.forces, so.eg_raw, s.ooff, s.oedge, N);
       PETB_LAUNCH_CHECK(st);

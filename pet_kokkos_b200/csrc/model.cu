@@ -171,11 +171,19 @@ Model::Model(const Checkpoint& ck) : h_(ck.hypers), scale_(ck.energy_scale) {
   const size_t ns = ck.composition_energies.size();
   PETB_CUDA(cudaMalloc(&comp_, (ns ? ns : 1) * sizeof(double)));
   PETB_CUDA(cudaMemcpy(comp_, ck.composition_energies.data(), ns * sizeof(double), cudaMemcpyHostToDevice));
+  if (h_.adaptive() && !h_.adaptive_solver) {  // from 0.5 A to the cutoff, a quarter of the taper width apart
+    std::vector<double> probes;
+    for (double r = 0.5; r < h_.cutoff - 1e-12; r += h_.cutoff_width_adaptive / 4.0) probes.push_back(r);
+    n_probes_ = int(probes.size());
+    PETB_CUDA(cudaMalloc(&probes_, (probes.size() ? probes.size() : 1) * sizeof(double)));
+    PETB_CUDA(cudaMemcpy(probes_, probes.data(), probes.size() * sizeof(double), cudaMemcpyHostToDevice));
+  }
 }
 
 Model::~Model() {
   for (void* p : owned_) cudaFree(p);
   cudaFree(comp_);
+  cudaFree(probes_);
 }
 
 // ---- the GEMM calls, by role ------------------------------------------------------
@@ -283,7 +291,7 @@ PassOut Model::finish(Stream& st, Arena& save, const PackedEdges& pk, bool grad,
   out.f.vir_atom = save.alloc<double>(9 * size_t(pk.n_atoms));
   out.f.vir9 = save.alloc<double>(9 * size_t(pk.B));
   out.f.vir6 = save.alloc<double>(6 * size_t(pk.B));
-  forces_and_virial(st, out.f, pk, x4_adj, cutoff_adj, cf_adj, cutoff_spec(), scale_);
+  forces_and_virial(st, save, out.f, pk, x4_adj, cutoff_adj, cf_adj, cutoff_spec(), scale_);
   return out;
 }
 

@@ -40,7 +40,15 @@ class Model {
 
   const Hypers& hypers() const { return h_; }
   double energy_scale() const { return scale_; }
-  CutoffSpec cutoff_spec() const { return {h_.cutoff, h_.cutoff_width, h_.cutoff_function}; }
+  CutoffSpec cutoff_spec() const {
+    CutoffSpec cs{h_.cutoff, h_.cutoff_width, h_.cutoff_function};
+    if (h_.adaptive()) {
+      cs.adaptive = h_.adaptive_solver ? 2 : 1;
+      cs.target = h_.num_neighbors_adaptive, cs.width_adaptive = h_.cutoff_width_adaptive;
+      cs.probes = probes_, cs.n_probes = n_probes_;
+    }
+    return cs;
+  }
 
   // One evaluation over packed edges. Saved activations come from `save`, temporaries
   // from `tmp`; both are rewound by the caller. With `taps`, named intermediates are
@@ -64,6 +72,8 @@ class Model {
   Hypers h_;
   double scale_ = 1.0;
   double* comp_ = nullptr;  // [n_species] composition energies
+  double* probes_ = nullptr;  // [n_probes_] the grid adaptive cutoff's radii (adaptive_probes, src/neighbors.cpp:23-27)
+  int n_probes_ = 0;
   std::map<std::string, Mat> mat_;
   std::map<std::string, const float*> vec_;
   std::vector<void*> owned_;

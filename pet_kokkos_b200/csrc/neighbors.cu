@@ -347,12 +347,18 @@ __device__ inline double cutoff_value(double d, double rc, double width, int kin
 }
 
 // One warp per centre atom: its kept-edge count (d <= rc), and the largest count.
+// An edge's own cutoff: the model's, or the mean of its two atoms' adaptive cutoffs (src/device_neighbors.cpp:243-246).
+__device__ __forceinline__ double edge_cutoff(const double* acut, const int* nbr, int a, int e, double rc) {
+  return acut ? 0.5 * (acut[a] + acut[nbr[e]]) : rc;
+}
+
 __global__ void k_keep_count(int NC, const int* __restrict__ roff, const double* __restrict__ dist, double rc,
-                             int* __restrict__ kcnt, int* __restrict__ maxm, unsigned long long* __restrict__ pairs) {
+                             int* __restrict__ kcnt, int* __restrict__ maxm, unsigned long long* __restrict__ pairs,
+                             const double* __restrict__ acut, const int* __restrict__ nbr) {
   const int a = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (a >= NC) return;
   int c = 0;
-  for (int e = roff[a] + lane; e < roff[a + 1]; e += 32) c += dist[e] <= rc;
+  for (int e = roff[a] + lane; e < roff[a + 1]; e += 32) c += dist[e] <= edge_cutoff(acut, nbr, a, e, rc);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
   if (lane == 0) {
@@ -371,7 +377,8 @@ __global__ void k_pack(int NC, RawEdges re, PackedEdges pk, CutoffSpec cs) {
   const int e1 = re.off[a + 1];
   for (int e0 = re.off[a]; e0 < e1; e0 += 32) {
     const int e = e0 + lane;
-    const bool keep = e < e1 && re.dist[e] <= cs.cutoff;
+    const double rc = e < e1 ? edge_cutoff(pk.adaptive.acut, re.j, a, e, cs.cutoff) : 0.0;
+    const bool keep = e < e1 && re.dist[e] <= rc;
     const unsigned m = __ballot_sync(0xffffffffu, keep);
     if (e < e1) {
       const int p = row + __popc(m & ((1u << lane) - 1u));
@@ -384,7 +391,8 @@ __global__ void k_pack(int NC, RawEdges re, PackedEdges pk, CutoffSpec cs) {
         pk.species[p] = pk.atom_species[j];
         pk.vec[3 * p] = re.vec[3 * e], pk.vec[3 * p + 1] = re.vec[3 * e + 1], pk.vec[3 * p + 2] = re.vec[3 * e + 2];
         pk.dist[p] = re.dist[e];
-        pk.cut[p] = (float) cutoff_value(re.dist[e], cs.cutoff, cs.width, cs.kind);
+        pk.cut[p] = (float) cutoff_value(re.dist[e], rc, cs.width, cs.kind);
+        if (pk.rc) pk.rc[p] = rc;
       } else {
         pk.packed_of_raw[e] = -1;
       }
@@ -490,9 +498,10 @@ void edge_vectors(Stream& st, const RawEdges& re, const double* pos, const doubl
 }
 
 PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int NC, const int* atom_species,
-                       const CutoffSpec& cs, int* pinned) {
+                       const CutoffSpec& cs, int* pinned, const AdaptiveCut& ad) {
   PackedEdges pk;
   pk.N = NC;
+  pk.adaptive = ad;
   pk.atom_species = atom_species;
   pk.off = arena.alloc<int>(NC + 1);
   const ProfScope ps(st, PC_GEOMETRY, 0.0, 60.0 * double(re.E) + 8.0 * NC);
@@ -502,7 +511,7 @@ PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int NC, con
   PETB_CUDA(cudaMemsetAsync(maxm, 0, sizeof(int), st.s));
   PETB_CUDA(cudaMemsetAsync(pairs, 0, 8, st.s));
   if (NC > 0) {
-    k_keep_count<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re.off, re.dist, cs.cutoff, kcnt, maxm, pairs);
+    k_keep_count<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re.off, re.dist, cs.cutoff, kcnt, maxm, pairs, ad.acut, re.j);
     PETB_LAUNCH_CHECK(st);
   }
   exclusive_scan(st, arena, kcnt, pk.off, NC);
@@ -521,6 +530,7 @@ PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int NC, con
   pk.vec = arena.alloc<double>(3 * Ea);
   pk.dist = arena.alloc<double>(Ea);
   pk.cut = arena.alloc<float>(Ea);
+  if (ad.acut) pk.rc = arena.alloc<double>(Ea);
   pk.raw_of = arena.alloc<int>(Ea);
   pk.packed_of_raw = arena.alloc<int>(Er);
   if (NC > 0 && re.E > 0) {
@@ -540,9 +550,10 @@ PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int NC, con
 // is read back and a stepping loop keeps one set of shapes (the reference's edge_capacity, src/model.cpp:549-567).
 // *overflow is set on the device when the step does not fit; the caller reads it with the results.
 PackedEdges pack_edges_fixed(Stream& st, Arena& arena, const RawEdges& re, int NC, const int* atom_species, const CutoffSpec& cs,
-                             int e_cap, int m_cap, double pairs, int* overflow) {
+                             int e_cap, int m_cap, double pairs, int* overflow, const AdaptiveCut& ad) {
   PackedEdges pk;
   pk.N = NC, pk.E = e_cap, pk.M = m_cap, pk.pairs = pairs;
+  pk.adaptive = ad;
   pk.atom_species = atom_species;
   pk.off = arena.alloc<int>(NC + 1);
   const ProfScope ps(st, PC_GEOMETRY, 0.0, 60.0 * double(re.E) + 8.0 * NC);
@@ -551,7 +562,7 @@ PackedEdges pack_edges_fixed(Stream& st, Arena& arena, const RawEdges& re, int N
   unsigned long long* pr = reinterpret_cast<unsigned long long*>(arena.alloc_bytes(8));
   PETB_CUDA(cudaMemsetAsync(maxm, 0, sizeof(int), st.s));
   PETB_CUDA(cudaMemsetAsync(pr, 0, 8, st.s));
-  k_keep_count<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re.off, re.dist, cs.cutoff, kcnt, maxm, pr);
+  k_keep_count<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re.off, re.dist, cs.cutoff, kcnt, maxm, pr, ad.acut, re.j);
   PETB_LAUNCH_CHECK(st);
   k_clamp_counts<<<cdiv(NC, 256), 256, 0, st.s>>>(kcnt, NC, m_cap);  // maxm already holds the unclamped maximum
   PETB_LAUNCH_CHECK(st);
@@ -573,6 +584,10 @@ PackedEdges pack_edges_fixed(Stream& st, Arena& arena, const RawEdges& re, int N
   pk.raw_of = reinterpret_cast<int*>(block), block += 4 * Ea;
   pk.cut = reinterpret_cast<float*>(block), block += 4 * Ea;
   pk.reverse = reinterpret_cast<int*>(block);
+  if (ad.acut) {
+    pk.rc = arena.alloc<double>(Ea);
+    PETB_CUDA(cudaMemsetAsync(pk.rc, 0, 8 * Ea, st.s));
+  }
   pk.packed_of_raw = arena.alloc<int>(Er);
   if (re.E > 0) {
     k_pack<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(NC, re, pk, cs);

@@ -42,6 +42,18 @@ struct RawEdges {
   int* reverse = nullptr;  // [E] partner (j,i,-shift) or -1
 };
 
+// What an adaptive cutoff's forward leaves for its backward (device pointers; all null for a fixed cutoff).
+struct AdaptiveCut {
+  const double* acut = nullptr;    // [n_atoms] each atom's cutoff
+  const double* root = nullptr;    // [n_atoms] solver: the root r of the neighbour-count equation
+  const double* slope = nullptr;   // [n_atoms] solver: dn/dr there, 0 for a clamped cutoff
+  const double* eff = nullptr;     // [n_atoms, P] grid: each probe's smoothed neighbour count
+  const double* probes = nullptr;  // [P] grid: the probe radii
+  int P = 0;
+  int n_atoms = 0;
+  RawEdges raw;                    // the list the cutoffs were computed from: every edge of it carries gradient
+};
+
 // The kept edges as the network reads them (the reference's PackedEdges).
 struct PackedEdges {
   int N = 0;          // centre atoms (token rows 0..N-1)
@@ -59,6 +71,8 @@ struct PackedEdges {
   double* vec = nullptr;    // [E,3]
   double* dist = nullptr;   // [E]
   float* cut = nullptr;     // [E] smooth cutoff factor
+  double* rc = nullptr;     // [E] each edge's own cutoff (the mean of its atoms' adaptive cutoffs); null: the model's
+  AdaptiveCut adaptive;
   int* raw_of = nullptr;    // [E] the raw edge this row came from
   int* packed_of_raw = nullptr;  // [E_raw] or -1
   const int* atom_species = nullptr;  // [n_atoms]
@@ -75,6 +89,11 @@ struct PackedEdges {
 struct CutoffSpec {
   double cutoff, width;
   int kind;  // 0 bump, 1 cosine
+  // The adaptive cutoff (Hypers::adaptive, include/pet/config.hpp): 0 none, 1 grid, 2 solver.
+  int adaptive = 0;
+  double target = 0.0, width_adaptive = 0.5;
+  const double* probes = nullptr;  // [n_probes] device, the grid scheme's radii
+  int n_probes = 0;
 };
 
 // Host-side grid choice for one structure (bins per axis, reach), the reference's cl_grid.
@@ -92,11 +111,13 @@ void find_reverse(Stream& st, const RawEdges& re, int N);
 void edge_vectors(Stream& st, const RawEdges& re, const double* pos, const double* cell9);
 // Keep test, cutoff factors, slots and packing. n_centres <= n_atoms atoms have edges.
 PackedEdges pack_edges(Stream& st, Arena& arena, const RawEdges& re, int n_centres, const int* atom_species,
-                       const CutoffSpec& cs, int* pinned_scratch);
+                       const CutoffSpec& cs, int* pinned_scratch, const AdaptiveCut& ad = AdaptiveCut());
 
 // int exclusive scan: out[0..n] (n+1 values, out[n] = total).
 void exclusive_scan(Stream& st, Arena& arena, const int* in, int* out, int n);
+// Each atom's adaptive cutoff from the raw list (adaptive.cu); an empty result for a model without one.
+AdaptiveCut adaptive_cutoffs(Stream& st, Arena& arena, const RawEdges& re, int n_atoms, const CutoffSpec& cs);
 PackedEdges pack_edges_fixed(Stream& st, Arena& arena, const RawEdges& re, int NC, const int* atom_species, const CutoffSpec& cs,
-                             int e_cap, int m_cap, double pairs, int* overflow);
+                             int e_cap, int m_cap, double pairs, int* overflow, const AdaptiveCut& ad = AdaptiveCut());
 
 }  // namespace petb

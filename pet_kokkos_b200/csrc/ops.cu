@@ -323,14 +323,24 @@ __device__ inline double cutoff_ddist(double d, double rc, double w, int kind) {
   return 0.5 * (double) (-pi * sinf(pi * x)) / w;
 }
 
+// pc_adj, unless null, receives the adjoint of the edge's own cutoff (an adaptive cutoff): the factor depends on
+// d - rc, so it is minus the distance's share (src/forces.cpp:372-377).
 __global__ void k_edge_grad(double* __restrict__ grad, PackedEdges pk, const float* __restrict__ x4_adj,
-                            const float* __restrict__ cutoff_adj, const float* __restrict__ cf_adj, CutoffSpec cs) {
+                            const float* __restrict__ cutoff_adj, const float* __restrict__ cf_adj, CutoffSpec cs,
+                            double* __restrict__ pc_adj) {
   const int k = blockIdx.x * blockDim.x + threadIdx.x;
   if (k >= pk.E) return;
+  if (pc_adj && k >= pk.off[pk.N]) {  // a capacity's dead row
+    pc_adj[k] = 0.0;
+    for (int c = 0; c < 3; ++c) grad[3 * size_t(k) + c] = 0.0;
+    return;
+  }
   const bool own = pk.center[k] < pk.n_local;
   const double cutoff_total = (own ? (double) cutoff_adj[k] : 0.0) + (double) cf_adj[k];
   const double d = pk.dist[k];
-  const double dist_adj = (double) x4_adj[4 * size_t(k) + 3] + cutoff_total * cutoff_ddist(d, cs.cutoff, cs.width, cs.kind);
+  const double dcut_dd = cutoff_ddist(d, pk.rc ? pk.rc[k] : cs.cutoff, cs.width, cs.kind);
+  if (pc_adj) pc_adj[k] = -cutoff_total * dcut_dd;
+  const double dist_adj = (double) x4_adj[4 * size_t(k) + 3] + cutoff_total * dcut_dd;
   const double invd = d > 0.0 ? 1.0 / d : 0.0;
   for (int c = 0; c < 3; ++c) grad[3 * size_t(k) + c] = (double) x4_adj[4 * size_t(k) + c] + dist_adj * pk.vec[3 * size_t(k) + c] * invd;
 }
@@ -502,17 +512,20 @@ void message_average_bwd(Stream& st, float* ie_adj_out, float* oe_adj, const flo
   PETB_LAUNCH_CHECK(st);
 }
 
-void forces_and_virial(Stream& st, const ForceOut& out, const PackedEdges& pk, const float* x4_adj, const float* cutoff_adj,
+void forces_and_virial(Stream& st, Arena& arena, ForceOut& out, const PackedEdges& pk, const float* x4_adj, const float* cutoff_adj,
                        const float* cf_adj, const CutoffSpec& cs, double scale) {
   const ProfScope ps(st, PC_FORCES, 40.0 * pk.E, 100.0 * double(pk.E) + 96.0 * pk.n_atoms);
+  double* pc_adj = pk.adaptive.acut ? arena.alloc<double>(pk.E > 0 ? pk.E : 1) : nullptr;
   if (pk.E > 0) {
-    k_edge_grad<<<blocks_for(pk.E, 256), 256, 0, st.s>>>(out.edge_grad, pk, x4_adj, cutoff_adj, cf_adj, cs);
+    k_edge_grad<<<blocks_for(pk.E, 256), 256, 0, st.s>>>(out.edge_grad, pk, x4_adj, cutoff_adj, cf_adj, cs, pc_adj);
     PETB_LAUNCH_CHECK(st);
   }
   if (pk.n_atoms > 0) {
     k_fold_forces<<<blocks_for(size_t(pk.n_atoms) * 32, 256), 256, 0, st.s>>>(out, pk, scale);
     PETB_LAUNCH_CHECK(st);
   }
+  // the adaptive cutoff's share, folded over the raw list, before the per-structure sums
+  if (pc_adj) adaptive_backward(st, arena, pk, cs, pc_adj, scale, out.forces, out.vir_atom, &out.adaptive_gmag);
   k_struct_sum<<<blocks_for(size_t(pk.B) * 9 * 32, 256), 256, 0, st.s>>>(out.vir9, out.vir_atom, pk.soff, pk.B, 9);
   PETB_LAUNCH_CHECK(st);
   k_voigt<<<blocks_for(pk.B, 128), 128, 0, st.s>>>(out.vir6, out.vir9, pk.B);

@@ -79,11 +79,16 @@ struct ForceOut {
   double* vir9 = nullptr;       // [B,9]
   double* vir6 = nullptr;       // [B,6]
   double* energy = nullptr;     // [B]
+  // With an adaptive cutoff: the radial gradient it puts on every raw edge, scale included (dE/dv += gmag v).
+  double* adaptive_gmag = nullptr;  // [E_raw]
 };
 // dE/dv per edge, the per-atom fold, and each structure's ordered sums
 // (forces_and_virial, fold_edge_gradients, sum_by_structure: src/forces.cpp:50-70,287-302,345-411; Voigt: src/model.cpp:983-993)
-void forces_and_virial(Stream& st, const ForceOut& out, const PackedEdges& pk, const float* x4_adj, const float* cutoff_adj,
+void forces_and_virial(Stream& st, Arena& arena, ForceOut& out, const PackedEdges& pk, const float* x4_adj, const float* cutoff_adj,
                        const float* cf_adj, const CutoffSpec& cs, double scale);
+// The adaptive cutoff's share of forces and virial (adaptive.cu): pc_adj [E] is each kept edge's pair-cutoff adjoint.
+void adaptive_backward(Stream& st, Arena& arena, const PackedEdges& pk, const CutoffSpec& cs, const double* pc_adj, double scale,
+                       double* forces, double* vir_atom, double** gmag_out);
 // energy(b) = ordered sum of per_atom over the structure's atoms
 void structure_energy(Stream& st, double* energy, const double* per_atom, const int* soff, int B);
 

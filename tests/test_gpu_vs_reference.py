@@ -170,3 +170,60 @@ def test_ghost_list_matches_the_reference(reference, lib_path, models):
     r = c.compute_edges(view, True, False)
     bands(r, ref)
     c.close()
+
+
+def adaptive_model(tmp_path, method):
+    from pet_kokkos_b200 import checkpoint as ck
+    return ck.write_random_checkpoint(tmp_path / f"ad_{method}", "tiny", "feedforward", seed=5, init="scaled",
+                                      num_neighbors_adaptive=16.0, adaptive_cutoff_method=method, cutoff=5.5)
+
+
+@pytest.mark.parametrize("gemm", ["native", "3xtf32"])
+@pytest.mark.parametrize("method", ["solver", "grid"])
+def test_adaptive_cutoff_matches_the_reference(reference, lib_path, tmp_path, method, gemm):
+    """Both adaptive-cutoff schemes (src/device_neighbors.cpp:26-136, src/forces.cpp:80-260,308-341): the atoms'
+    cutoffs, the pairs kept within the mean of their atoms' cutoffs, and the gradient that flows back through the
+    cutoffs to every raw pair, against the reference on a batch with a dense cell, a sparse mixture and a cluster."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = adaptive_model(tmp_path, method)
+    systems = [st.diamond(2, jitter=0.08, seed=1), st.random_mixture(30, 8.0, seed=4), cluster(8, 3)]
+    ref = reference.ReferenceCalculator(str(jp), str(sp)).compute(systems)
+    c = Calculator(jp, sp, gemm=gemm)
+    r = c.compute(systems)
+    bands(r, ref, LOOSE[gemm])
+    raw = c.neighbor_list(systems)
+    assert c.last_shapes()[1] < 0.5 * len(raw["i"]), "the adaptive cutoff has to drop edges for this test to mean anything"
+    assert c.ghost_cutoff == 3 * c.cutoff
+    c.close()
+
+
+@pytest.mark.parametrize("method", ["solver", "grid"])
+def test_adaptive_cutoff_with_an_engine_list_matches_the_reference(reference, lib_path, tmp_path, method):
+    """compute_edges with edge gradients and stepping (plain and with fixed shapes) on an adaptive model: the listed
+    pairs reach past the model cutoff, every pair within it carries gradient whether the network keeps it or not."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = adaptive_model(tmp_path, method)
+    s = st.diamond(2, jitter=0.08, seed=13)
+    off, nbr, sh = engine_list(s, 5.5, 0.5)
+    lst = {"positions": s["positions"], "atomic_numbers": s["atomic_numbers"], "offsets": off, "neighbors": nbr,
+           "shifts": sh, "cell": s["cell"], "n_local": -1, "half": False}
+    rcalc = reference.ReferenceCalculator(str(jp), str(sp))
+    ref = rcalc.compute_edges(lst)
+    c = Calculator(jp, sp)
+    view = EdgeListView(s["positions"], s["atomic_numbers"], off, nbr, sh, s["cell"])
+    r = c.compute_edges(view, True, True)
+    bands(r, ref)
+    assert np.abs(r.edge_gradient - ref["edge_gradient"]).max() <= 1e-5 * max(1.0, np.abs(ref["edge_gradient"]).max())
+    rng = np.random.default_rng(5)
+    moved = np.stack([s["positions"] + rng.normal(0, 0.03, s["positions"].shape) for _ in range(3)])
+    steps = rcalc.steps(lst, moved)
+    fixed = Calculator(jp, sp, md_fixed_shapes=True)
+    for calc in (c, fixed):
+        calc.set_neighbors(view)
+        for k in range(3):
+            rk = calc.compute_step(moved[k], s["cell"])
+            assert abs(rk.energy[0] - steps["energy"][k]) <= 1e-6 * max(abs(steps["energy"][k]), np.abs(ref["per_atom_energy"]).sum())
+            assert np.abs(rk.forces - steps["forces"][k]).max() <= 1e-5 * max(1.0, np.abs(steps["forces"][k]).max())
+            assert np.abs(rk.virial[0] - steps["virial"][k]).max() <= 1e-5 * max(1.0, np.abs(steps["virial"][k]).max())
+    c.close()
+    fixed.close()
