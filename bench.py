@@ -377,6 +377,12 @@ def run_ours(args):
                         "traffic_source": "ncu dram bytes per launch on water648 (profiles/k_gemm_tc_water648_s_3xtf32.md), "
                                           "scaled by token rows",
                         "launches": p["launches"], "avg_launch_ms": per_launch_ms}
+                # what the mode asks of the tensor cores: an fp32-accurate product is three tf32 MMAs, and tf32 runs at
+                # half the bf16 rate, so the algorithmic ceiling of this mode is a sixth of the bf16 peak
+                passes = {"3xtf32": 3, "tf32": 1, "bf16": 1}.get(args.gemm)
+                if passes:
+                    roof["mma_tflops"] = passes * ach
+                    roof["mode_ceiling_frac_of_peak"] = 0.5 / passes
             else:
                 ach = p["bytes"] / (p["ms"] * 1e-3) / 1e9
                 roof = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -385,6 +391,26 @@ def run_ours(args):
         classes = {k: {"ms_per_step": v["ms"] / 2, "share": v["ms"] / max(sum(x["ms"] for x in prof.values()), 1e-9),
                        "tflops": v["flops"] / max(v["ms"], 1e-9) / 1e9, "gbs": v["bytes"] / max(v["ms"], 1e-9) / 1e6}
                    for k, v in prof.items()}
+        # the other GEMM/attention modes on the same staged structures (N = 1 only), three steps each after two:
+        # native = fp32 on the CUDA cores (the default correctness mode), tf32 = one tensor-core pass (a speed mode)
+        modes = None
+        if world == 1 and not args.no_cpu:
+            modes = {}
+            for other in ("native", "tf32"):
+                if other == args.gemm:
+                    continue
+                c2 = Calculator(jp, sp, gemm=other, device=local)
+                c2.stage(systems)
+                for _ in range(2):
+                    c2.compute_staged(True)
+                    c2.fetch()
+                ms = []
+                for _ in range(3):
+                    c2.compute_staged(True)
+                    c2.fetch()
+                    ms.append(c2.last_device_ms)
+                modes[other] = {"device_ms_per_step": float(np.mean(ms))}
+                c2.close()
         # the CPU arm beside it (N = 1 only): the reference's path on the host cores, on a bounded sample
         cpu = None
         if world == 1 and not args.no_cpu:
@@ -403,7 +429,8 @@ def run_ours(args):
                        "sharding": "one structure per GPU, no data-path collective"},
             "e2e": {"value": total_atoms * args.steps / e2e_wall, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_wall / args.steps * 1e3},
-            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "classes": classes, "cpu_baseline": cpu}))
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "classes": classes, "other_modes": modes,
+            "cpu_baseline": cpu}))
     calc.close()
     if world > 1:
         dist.destroy_process_group()
