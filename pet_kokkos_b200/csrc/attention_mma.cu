@@ -83,17 +83,26 @@ __host__ __device__ inline int round16(int s) { return (s + 15) / 16 * 16; }
 // Pitch of the S x S tables: the smallest value >= S16 that is 4 modulo 32 (see the header).
 __host__ __device__ inline int table_pitch(int S16) { return (S16 + 27) / 32 * 32 + 4; }
 
+// Asynchronous 16-byte copies global -> shared: every tile's loads are in flight together, and no register waits on
+// them; stage_wait() before the barrier that publishes the tiles.
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t) __cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void stage_wait() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
 template <int HD>
 __device__ __forceinline__ void stage(float* dst, const float* src, size_t ld, int col, int n, int N, int e0, int cnt, int rows) {
   constexpr int Q = HD / 4, P = HD + 4;
   for (int t = threadIdx.x; t < rows * Q; t += blockDim.x) {
     const int r = t / Q, c = (t % Q) * 4;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (r < cnt) {
       const size_t row = r == 0 ? size_t(n) : size_t(N) + e0 + r - 1;
-      v = ld4(src + row * ld + col + c);
+      cp_async16(dst + r * P + c, src + row * ld + col + c);
+    } else {
+      *reinterpret_cast<float4*>(dst + r * P + c) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    *reinterpret_cast<float4*>(dst + r * P + c) = v;
   }
 }
 
@@ -129,6 +138,7 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
     const float cf = r == 0 ? 1.0f : (r < cnt ? p.cut[e0 + r - 1] : 0.f);
     slc[r] = cf > 0.f ? __logf(cf) : kOff;
   }
+  stage_wait();
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int r0 = 16 * warp;
@@ -234,27 +244,27 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
   stage<HD>(sv, p.qkv, 3 * size_t(D), 2 * D + h * HD, n, p.N, e0, cnt, S16);
   stage<HD>(sg, p.dmerged, size_t(D), h * HD, n, p.N, e0, cnt, S16);
   for (int r = threadIdx.x; r < S16; r += blockDim.x) {
-    float lc = kOff, m = 0.f, il = 0.f;
+    float lc = kOff, m = 0.f, il = 0.f, dqv = 0.f;
     if (r < cnt) {
       const size_t row = r == 0 ? size_t(n) : size_t(p.N) + e0 + r - 1;
       const float cf = r == 0 ? 1.0f : p.cut[e0 + r - 1];
       lc = cf > 0.f ? __logf(cf) : kOff;
       m = p.ml[(row * p.H + h) * 2], il = p.ml[(row * p.H + h) * 2 + 1];
+      // Dq = dO . O of this query's head slice, both rows straight from global memory: a thread per row, its loads
+      // all in flight together
+      const float4* o4 = reinterpret_cast<const float4*>(p.merged + row * D + h * HD);
+      const float4* g4 = reinterpret_cast<const float4*>(p.dmerged + row * D + h * HD);
+#pragma unroll
+      for (int c = 0; c < HD / 4; ++c) {
+        const float4 a = o4[c], b = g4[c];
+        dqv += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+      }
     }
-    slc[r] = lc, sm[r] = m, sl[r] = il;
+    slc[r] = lc, sm[r] = m, sl[r] = il, sd[r] = dqv;
   }
+  stage_wait();
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
-  for (int q = warp; q < S16; q += nw) {  // Dq = dO . O, a warp per query row (O from global memory)
-    float s = 0.f;
-    if (q < cnt) {
-      const size_t grow = q == 0 ? size_t(n) : size_t(p.N) + e0 + q - 1;
-      for (int d = lane; d < HD; d += 32) s += p.merged[grow * D + h * HD + d] * sg[q * P + d];
-    }
-    s = warp_sum(s);
-    if (lane == 0) sd[q] = s;
-  }
-  __syncthreads();
   // The first half of the warps take 16 queries each (dQ), the second half 16 keys each (dK, dV and
   // the keys' cutoff shares), both recomputing the weights they need: no S x S table, no further barrier.
   // With more blocks than warps of a kind (long neighbour lists) a warp takes every half-th block in turn.
