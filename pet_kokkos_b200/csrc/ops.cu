@@ -85,6 +85,56 @@ __global__ void k_gather_live(float* __restrict__ out, const float* __restrict__
   reinterpret_cast<float4*>(out)[t] = k >= 0 ? ld4(src + size_t(k) * ld + col0 + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
+// The same with each lane holding NV runs of four consecutive values in registers (D = 128 NV): the row is read
+// once, 16 bytes at a time, for the statistics and for the output.
+template <int NV>
+__global__ void __launch_bounds__(256) k_norm_fwd_v(float* __restrict__ out, float* __restrict__ in, const float* __restrict__ add,
+                                                    const float* __restrict__ w, const float* __restrict__ bias, int R) {
+  constexpr int D = 128 * NV;
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (r >= R) return;
+  float* x = in + size_t(r) * D;
+  const bool ln = bias != nullptr;
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) v[i] = ld4(x + 128 * i + 4 * lane);
+  if (add) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const float4 a = ld4(add + size_t(r) * D + 128 * i + 4 * lane);
+      v[i].x += a.x, v[i].y += a.y, v[i].z += a.z, v[i].w += a.w;
+      st4(x + 128 * i + 4 * lane, v[i]);
+    }
+  }
+  float mu = 0.f;
+  if (ln) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    mu = warp_sum(s) / D;
+  }
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const float a = v[i].x - mu, b = v[i].y - mu, c = v[i].z - mu, d = v[i].w - mu;
+    q += (a * a + b * b) + (c * c + d * d);
+  }
+  q = warp_sum(q);
+  const float inv = 1.0f / sqrtf(q / D + (ln ? kLnEps : kRmsEps));
+  float* o = out + size_t(r) * D;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const float4 ww = ld4(w + 128 * i + 4 * lane);
+    float4 y = make_float4((v[i].x - mu) * inv * ww.x, (v[i].y - mu) * inv * ww.y, (v[i].z - mu) * inv * ww.z,
+                           (v[i].w - mu) * inv * ww.w);
+    if (ln) {
+      const float4 bb = ld4(bias + 128 * i + 4 * lane);
+      y.x += bb.x, y.y += bb.y, y.z += bb.z, y.w += bb.w;
+    }
+    st4(o + 128 * i + 4 * lane, y);
+  }
+}
+
 __global__ void __launch_bounds__(256) k_concat_norm_fwd(float* __restrict__ out, const float* __restrict__ oe,
                                                          const int* __restrict__ rev, float* __restrict__ ie,
                                                          const float* __restrict__ w, const float* __restrict__ bias, int E,
@@ -147,6 +197,53 @@ __global__ void __launch_bounds__(256) k_norm_bwd(float* __restrict__ in_adj, co
     const float v = acc ? o[d] + g : g;
     o[d] = v;
     if (also) also[size_t(r) * D + d] = v;
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) k_norm_bwd_v(float* __restrict__ in_adj, const float* __restrict__ out_adj,
+                                                    const float* __restrict__ in, const float* __restrict__ w, bool ln, int R,
+                                                    int acc_row0, float* __restrict__ also) {
+  constexpr int D = 128 * NV;
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (r >= R) return;
+  float4 x[NV], gw[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    x[i] = ld4(in + size_t(r) * D + 128 * i + 4 * lane);
+    const float4 g = ld4(out_adj + size_t(r) * D + 128 * i + 4 * lane), ww = ld4(w + 128 * i + 4 * lane);
+    gw[i] = make_float4(g.x * ww.x, g.y * ww.y, g.z * ww.z, g.w * ww.w);
+  }
+  float mu = 0.f;
+  if (ln) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) s += (x[i].x + x[i].y) + (x[i].z + x[i].w);
+    mu = warp_sum(s) / D;
+  }
+  float sq = 0.f, sg = 0.f, sgx = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    x[i].x -= mu, x[i].y -= mu, x[i].z -= mu, x[i].w -= mu;
+    sq += (x[i].x * x[i].x + x[i].y * x[i].y) + (x[i].z * x[i].z + x[i].w * x[i].w);
+    sg += (gw[i].x + gw[i].y) + (gw[i].z + gw[i].w);
+    sgx += (gw[i].x * x[i].x + gw[i].y * x[i].y) + (gw[i].z * x[i].z + gw[i].w * x[i].w);
+  }
+  sq = warp_sum(sq), sg = warp_sum(sg), sgx = warp_sum(sgx);
+  const float inv = 1.0f / sqrtf(sq / D + (ln ? kLnEps : kRmsEps));
+  const float mg = ln ? sg / D : 0.f, mgx = sgx * inv / D;
+  float* o = in_adj + size_t(r) * D;
+  const bool acc = r >= acc_row0;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float4 g = make_float4(inv * (gw[i].x - mg - x[i].x * inv * mgx), inv * (gw[i].y - mg - x[i].y * inv * mgx),
+                           inv * (gw[i].z - mg - x[i].z * inv * mgx), inv * (gw[i].w - mg - x[i].w * inv * mgx));
+    if (acc) {
+      const float4 old = ld4(o + 128 * i + 4 * lane);
+      g.x += old.x, g.y += old.y, g.z += old.z, g.w += old.w;
+    }
+    st4(o + 128 * i + 4 * lane, g);
+    if (also) st4(also + size_t(r) * D + 128 * i + 4 * lane, g);
   }
 }
 
@@ -413,7 +510,14 @@ void compress0(Stream& st, float* out, float* pre, const float* b, const float* 
 void norm_fwd(Stream& st, float* out, float* in, const float* add, const float* w, const float* bias, int R, int D) {
   if (R == 0) return;
   const ProfScope ps(st, PC_NORM, 6.0 * double(R) * D, (add ? 16.0 : 8.0) * double(R) * D);
-  k_norm_fwd<<<blocks_for(size_t(R) * 32, 256), 256, 0, st.s>>>(out, in, add, w, bias, R, D);
+  const unsigned blocks = blocks_for(size_t(R) * 32, 256);
+  switch (D) {  // whole rows in registers for the usual widths
+    case 128: k_norm_fwd_v<1><<<blocks, 256, 0, st.s>>>(out, in, add, w, bias, R); break;
+    case 256: k_norm_fwd_v<2><<<blocks, 256, 0, st.s>>>(out, in, add, w, bias, R); break;
+    case 512: k_norm_fwd_v<4><<<blocks, 256, 0, st.s>>>(out, in, add, w, bias, R); break;
+    case 1024: k_norm_fwd_v<8><<<blocks, 256, 0, st.s>>>(out, in, add, w, bias, R); break;
+    default: k_norm_fwd<<<blocks, 256, 0, st.s>>>(out, in, add, w, bias, R, D);
+  }
   PETB_LAUNCH_CHECK(st);
 }
 
@@ -436,7 +540,14 @@ void norm_bwd(Stream& st, float* in_adj, const float* out_adj, const float* in, 
               int acc_row0, float* also) {
   if (R == 0) return;
   const ProfScope ps(st, PC_NORM, 10.0 * double(R) * D, (acc_row0 < R ? 16.0 : 12.0) * double(R) * D);
-  k_norm_bwd<<<blocks_for(size_t(R) * 32, 256), 256, 0, st.s>>>(in_adj, out_adj, in, w, layernorm, R, D, acc_row0, also);
+  const unsigned blocks = blocks_for(size_t(R) * 32, 256);
+  switch (D) {
+    case 128: k_norm_bwd_v<1><<<blocks, 256, 0, st.s>>>(in_adj, out_adj, in, w, layernorm, R, acc_row0, also); break;
+    case 256: k_norm_bwd_v<2><<<blocks, 256, 0, st.s>>>(in_adj, out_adj, in, w, layernorm, R, acc_row0, also); break;
+    case 512: k_norm_bwd_v<4><<<blocks, 256, 0, st.s>>>(in_adj, out_adj, in, w, layernorm, R, acc_row0, also); break;
+    case 1024: k_norm_bwd_v<8><<<blocks, 256, 0, st.s>>>(in_adj, out_adj, in, w, layernorm, R, acc_row0, also); break;
+    default: k_norm_bwd<<<blocks, 256, 0, st.s>>>(in_adj, out_adj, in, w, layernorm, R, D, acc_row0, also);
+  }
   PETB_LAUNCH_CHECK(st);
 }
 
