@@ -296,6 +296,91 @@ __global__ void __launch_bounds__(256) k_concat_norm_bwd(float* __restrict__ edg
   }
 }
 
+// The same, one warp per PAIR of partner rows (single-rank lists only). Row k's concat is [oe(k) | oe(r)] and row r's is
+// [oe(r) | oe(k)]: the same numbers, so one mean and one variance serve both, and each row is read once for the two
+// outputs. The warp of the larger index of a pair leaves; a row without a partner is a pair with a zero half.
+template <int NV>
+__global__ void __launch_bounds__(256) k_concat_norm_bwd_pair(float* __restrict__ edge_adj, const float* __restrict__ out_adj,
+                                                              const float* __restrict__ oe, const int* __restrict__ rev,
+                                                              const float* __restrict__ ie_adj, const float* __restrict__ w,
+                                                              int E) {
+  constexpr int D = 128 * NV, W = 2 * D;
+  const int k = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (k >= E) return;
+  const int r = rev[k];
+  const bool mutual = r >= 0 && rev[r] == k;
+  if (mutual && r < k) return;
+  if (r >= 0 && !mutual) {
+    // A list whose partner map is not an involution: this row alone, partner's statistics from its own partner.
+    const RemoteRows none{};
+    const RowStats sk = concat_stats(oe, oe + size_t(r) * D, out_adj, w, k, D, lane);
+    const float* xr2 = partner_row(oe, rev, none, r, D);
+    const RowStats sr = concat_stats(oe, xr2, out_adj, w, r, D, lane);
+    for (int d = lane; d < D; d += 32) {
+      const float gk = sk.inv * (out_adj[size_t(k) * W + d] * w[d] - sk.mg - (oe[size_t(k) * D + d] - sk.mu) * sk.inv * sk.mgx);
+      const float x = (xr2 ? xr2[d] : 0.f) - sr.mu;
+      const float back = sr.inv * (out_adj[size_t(r) * W + D + d] * w[D + d] - sr.mg - x * sr.inv * sr.mgx);
+      edge_adj[size_t(k) * D + d] = ie_adj[size_t(k) * D + d] + gk + back;
+    }
+    return;
+  }
+  float4 a[NV], b[NV], g0[NV], g1[NV], h0[NV], h1[NV];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = 128 * i + 4 * lane;
+    a[i] = ld4(oe + size_t(k) * D + c);
+    b[i] = mutual ? ld4(oe + size_t(r) * D + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 w0 = ld4(w + c), w1 = ld4(w + D + c);
+    const float4 p = ld4(out_adj + size_t(k) * W + c), q = ld4(out_adj + size_t(k) * W + D + c);
+    g0[i] = make_float4(p.x * w0.x, p.y * w0.y, p.z * w0.z, p.w * w0.w);
+    g1[i] = make_float4(q.x * w1.x, q.y * w1.y, q.z * w1.z, q.w * w1.w);
+    if (mutual) {
+      const float4 t = ld4(out_adj + size_t(r) * W + c), u = ld4(out_adj + size_t(r) * W + D + c);
+      h0[i] = make_float4(t.x * w0.x, t.y * w0.y, t.z * w0.z, t.w * w0.w);
+      h1[i] = make_float4(u.x * w1.x, u.y * w1.y, u.z * w1.z, u.w * w1.w);
+    } else {
+      h0[i] = h1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    s += ((a[i].x + b[i].x) + (a[i].y + b[i].y)) + ((a[i].z + b[i].z) + (a[i].w + b[i].w));
+  }
+  const float mu = warp_sum(s) / W;
+  float sq = 0.f, sgk = 0.f, sgxk = 0.f, sgr = 0.f, sgxr = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    a[i].x -= mu, a[i].y -= mu, a[i].z -= mu, a[i].w -= mu;
+    b[i].x -= mu, b[i].y -= mu, b[i].z -= mu, b[i].w -= mu;
+    sq += ((a[i].x * a[i].x + b[i].x * b[i].x) + (a[i].y * a[i].y + b[i].y * b[i].y)) +
+          ((a[i].z * a[i].z + b[i].z * b[i].z) + (a[i].w * a[i].w + b[i].w * b[i].w));
+    sgk += ((g0[i].x + g1[i].x) + (g0[i].y + g1[i].y)) + ((g0[i].z + g1[i].z) + (g0[i].w + g1[i].w));
+    sgxk += ((g0[i].x * a[i].x + g1[i].x * b[i].x) + (g0[i].y * a[i].y + g1[i].y * b[i].y)) +
+            ((g0[i].z * a[i].z + g1[i].z * b[i].z) + (g0[i].w * a[i].w + g1[i].w * b[i].w));
+    sgr += ((h0[i].x + h1[i].x) + (h0[i].y + h1[i].y)) + ((h0[i].z + h1[i].z) + (h0[i].w + h1[i].w));
+    sgxr += ((h0[i].x * b[i].x + h1[i].x * a[i].x) + (h0[i].y * b[i].y + h1[i].y * a[i].y)) +
+            ((h0[i].z * b[i].z + h1[i].z * a[i].z) + (h0[i].w * b[i].w + h1[i].w * a[i].w));
+  }
+  sq = warp_sum(sq), sgk = warp_sum(sgk), sgxk = warp_sum(sgxk), sgr = warp_sum(sgr), sgxr = warp_sum(sgxr);
+  const float inv = 1.0f / sqrtf(sq / W + kLnEps);
+  const float mgk = sgk / W, mgxk = sgxk * inv / W, mgr = sgr / W, mgxr = sgxr * inv / W;
+  // input adjoint of a concat row's element with centred value x and weighted output adjoint g, for row k's / r's statistics
+  auto in_k = [&](float g, float x) { return inv * (g - mgk - x * inv * mgxk); };
+  auto in_r = [&](float g, float x) { return inv * (g - mgr - x * inv * mgxr); };
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = 128 * i + 4 * lane;
+    float4 o = ld4(ie_adj + size_t(k) * D + c);
+    o.x += in_k(g0[i].x, a[i].x), o.y += in_k(g0[i].y, a[i].y), o.z += in_k(g0[i].z, a[i].z), o.w += in_k(g0[i].w, a[i].w);
+    if (mutual) {
+      o.x += in_r(h1[i].x, a[i].x), o.y += in_r(h1[i].y, a[i].y), o.z += in_r(h1[i].z, a[i].z), o.w += in_r(h1[i].w, a[i].w);
+      float4 t = ld4(ie_adj + size_t(r) * D + c);
+      t.x += in_r(h0[i].x, b[i].x) + in_k(g1[i].x, b[i].x), t.y += in_r(h0[i].y, b[i].y) + in_k(g1[i].y, b[i].y);
+      t.z += in_r(h0[i].z, b[i].z) + in_k(g1[i].z, b[i].z), t.w += in_r(h0[i].w, b[i].w) + in_k(g1[i].w, b[i].w);
+      st4(edge_adj + size_t(r) * D + c, t);
+    }
+    st4(edge_adj + size_t(k) * D + c, o);
+  }
+}
+
 // send(l, :) = the second half of the norm's input adjoint on live edge l's row: what its partner's rank adds.
 __global__ void __launch_bounds__(256) k_concat_norm_remote_bwd(float* __restrict__ send, const float* __restrict__ out_adj,
                                                                 const float* __restrict__ oe, const float* __restrict__ w,
@@ -555,8 +640,16 @@ void concat_norm_bwd(Stream& st, float* edge_adj, const float* out_adj, const fl
                      const float* w, int E, int D, RemoteRows remote, const float* remote_adj) {
   if (E == 0) return;
   const ProfScope ps(st, PC_NORM, 20.0 * double(E) * D, 24.0 * double(E) * D);
-  k_concat_norm_bwd<<<blocks_for(size_t(E) * 32, 256), 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E, D, remote,
-                                                                      remote_adj);
+  const auto grid = blocks_for(size_t(E) * 32, 256);
+  const bool one_rank = !remote.of && !remote_adj;
+  if (one_rank && D == 128)
+    k_concat_norm_bwd_pair<1><<<grid, 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E);
+  else if (one_rank && D == 256)
+    k_concat_norm_bwd_pair<2><<<grid, 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E);
+  else if (one_rank && D == 512)
+    k_concat_norm_bwd_pair<4><<<grid, 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E);
+  else
+    k_concat_norm_bwd<<<grid, 256, 0, st.s>>>(edge_adj, out_adj, oe, rev, ie_adj, w, E, D, remote, remote_adj);
   PETB_LAUNCH_CHECK(st);
 }
 
