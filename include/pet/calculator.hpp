@@ -33,6 +33,7 @@ struct Options {
   std::optional<GemmMode> gemm;
   bool graphs = true;
   bool md_fixed_shapes = false;
+  bool cache_neighbors = false;  // a Verlet cache for a staged batch being stepped (stage / compute_device)
   std::size_t memory_budget_bytes = 0;
   int max_batch_atoms = 0;
   int device = -1;
@@ -90,6 +91,7 @@ class Calculator {
     o.gemm_mode = opts.gemm ? int(*opts.gemm) : -1;
     o.graphs = opts.graphs ? 1 : 0;
     o.md_fixed_shapes = opts.md_fixed_shapes ? 1 : 0;
+    o.cache_neighbors = opts.cache_neighbors ? 1 : 0;
     o.memory_budget_bytes = opts.memory_budget_bytes;
     o.max_batch_atoms = opts.max_batch_atoms;
     const int rc = pet_calc_create(model_json.c_str(), model_weights.c_str(), &o, &h_);

@@ -52,7 +52,9 @@ typedef struct pet_options {
   int md_fixed_shapes;      /* Options::md_fixed_shapes; -1 unset                     */
   size_t memory_budget_bytes; /* 0: ask the device                                     */
   int max_batch_atoms;      /* 0: none                                                */
-  int reserved[8];
+  int cache_neighbors;      /* Options::cache_neighbors (calculator.hpp:39-40): 1 keeps a staged batch's pairs within
+                               cutoff + 1 A between evaluations; 0: PET_CACHE_NEIGHBORS, then off */
+  int reserved[7];
 } pet_options;
 
 /* pet::System (include/pet/neighbors.hpp:15-25). */
@@ -194,6 +196,10 @@ long long pet_kernel_launches(const pet_calc* c);
 /* Evaluations served by replaying a recorded CUDA graph (Options::graphs; the reference's GraphCache,
  * include/pet/graph.hpp:68-146: eager first, capture second, replay after). */
 long long pet_graph_replays(const pet_calc* c);
+/* Neighbour searches run for staged batches under Options::cache_neighbors, and the evaluations the cached
+ * pairs served instead (the reference's NefCache, include/pet/device_geometry.hpp:198-228). */
+long long pet_neighbor_searches(const pet_calc* c);
+long long pet_neighbor_reuses(const pet_calc* c);
 double pet_last_device_ms(const pet_calc* c);
 
 /* Per-class device timing of evaluations (no counterpart in the reference's API; its

@@ -29,7 +29,8 @@ class PetSystem(C.Structure):
 
 class PetOptions(C.Structure):
     _fields_ = [("device", C.c_int), ("gemm_mode", C.c_int), ("graphs", C.c_int), ("md_fixed_shapes", C.c_int),
-                ("memory_budget_bytes", C.c_size_t), ("max_batch_atoms", C.c_int), ("reserved", C.c_int * 8)]
+                ("memory_budget_bytes", C.c_size_t), ("max_batch_atoms", C.c_int), ("cache_neighbors", C.c_int),
+                ("reserved", C.c_int * 7)]
 
 
 class PetResults(C.Structure):
@@ -100,6 +101,8 @@ SIGNATURES = {
     "pet_kernel_launches": (C.c_longlong, [C.c_void_p]),
     "pet_last_device_ms": (C.c_double, [C.c_void_p]),
     "pet_graph_replays": (C.c_longlong, [C.c_void_p]),
+    "pet_neighbor_searches": (C.c_longlong, [C.c_void_p]),
+    "pet_neighbor_reuses": (C.c_longlong, [C.c_void_p]),
     "pet_profile": (C.c_int, [C.c_void_p, C.c_int]),
     "pet_profile_read": (C.c_int, [C.c_void_p, _P(PetProfileEntry), C.c_int, _P(C.c_int)]),
     "pet_debug_fetch": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_float), C.c_size_t, _P(C.c_size_t)]),
@@ -197,7 +200,8 @@ class EdgeListView:
 class Calculator:
     """A loaded model on one GPU.  Reuse one across calls: it holds the scratch pools."""
 
-    def __init__(self, model_json, model_weights=None, gemm=None, device=-1, graphs=None, md_fixed_shapes=None):
+    def __init__(self, model_json, model_weights=None, gemm=None, device=-1, graphs=None, md_fixed_shapes=None,
+                 cache_neighbors=None):
         self._h = None
         self._lib = load_library()
         if model_weights is None:  # a path prefix, as the reference's resolve_model accepts
@@ -210,6 +214,8 @@ class Calculator:
             o.graphs = int(bool(graphs))
         if md_fixed_shapes is not None:  # Options::md_fixed_shapes (calculator.hpp:111-116)
             o.md_fixed_shapes = int(bool(md_fixed_shapes))
+        if cache_neighbors:  # Options::cache_neighbors (calculator.hpp:36-40): a Verlet cache for staged batches
+            o.cache_neighbors = 1
         h = C.c_void_p()
         rc = self._lib.pet_calc_create(os.fsencode(model_json), os.fsencode(model_weights), C.byref(o), C.byref(h))
         if rc:
@@ -264,6 +270,15 @@ class Calculator:
     @property
     def graph_replays(self):
         return self._lib.pet_graph_replays(self._h)
+
+    @property
+    def neighbor_searches(self):
+        """Searches run for staged batches under cache_neighbors; neighbor_reuses counts the evaluations between."""
+        return self._lib.pet_neighbor_searches(self._h)
+
+    @property
+    def neighbor_reuses(self):
+        return self._lib.pet_neighbor_reuses(self._h)
 
     @property
     def last_device_ms(self):

@@ -107,7 +107,7 @@ __global__ void k_atom_virial(double* __restrict__ w, const double* __restrict__
 
 Engine::Engine(const std::string& json, const std::string& weights, const pet_options* opts)
     : ckpt(json, weights), geom_arena(size_t(1) << 20), nbr_arena(size_t(16) << 20), save_arena(size_t(64) << 20),
-      tmp_arena(size_t(64) << 20), session_arena(size_t(4) << 20) {
+      tmp_arena(size_t(64) << 20), session_arena(size_t(4) << 20), cache_arena(size_t(4) << 20) {
   int count = 0;
   if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
     throw Error(5, "no CUDA device: this evaluator has no CPU path");
@@ -117,6 +117,7 @@ Engine::Engine(const std::string& json, const std::string& weights, const pet_op
   gemm_mode = opts && opts->gemm_mode >= 0 ? opts->gemm_mode : env_gemm_mode();
   graphs = (opts && opts->graphs >= 0 ? opts->graphs : env_int("PET_GRAPHS", 1)) != 0;
   md_fixed = (opts && opts->md_fixed_shapes >= 0 ? opts->md_fixed_shapes : env_int("PET_MD_FIXED", 0)) != 0;
+  cache_neighbors = (opts && opts->cache_neighbors > 0) || env_int("PET_CACHE_NEIGHBORS", 0) != 0;
   PETB_CUDA(cudaStreamCreateWithFlags(&st.s, cudaStreamNonBlocking));
   PETB_CUDA(cudaEventCreate(&ev0));
   PETB_CUDA(cudaEventCreate(&ev1));
@@ -218,6 +219,7 @@ void Engine::stage(const pet_system* systems, int B) {
   g.gnr = g.gnc + 3 * B;
   g.goff = g.gnr + 3 * B;
   geom = g;
+  verlet.valid = false;  // staging resets the neighbour cache (include/pet/calculator.hpp:210-212)
   // the copy must finish before the staging block is reused by another stage()
   PETB_CUDA(cudaStreamSynchronize(st.s));
 }
@@ -340,10 +342,15 @@ void Engine::compute_staged(bool forces) {
   tmp_arena.reset();
   PETB_CUDA(cudaEventRecord(ev0, st.s));
   const Geom& g = geom;
-  posw = nbr_arena.alloc<double>(3 * size_t(g.Ntot > 0 ? g.Ntot : 1));
-  wrap_positions(st, g, posw);
-  RawEdges re = cell_list_search(st, nbr_arena, g, posw, ckpt.hypers.cutoff);
-  find_reverse(st, re, g.Ntot);
+  RawEdges re;
+  if (cache_neighbors) {
+    re = cached_edges();
+  } else {
+    posw = nbr_arena.alloc<double>(3 * size_t(g.Ntot > 0 ? g.Ntot : 1));
+    wrap_positions(st, g, posw);
+    re = cell_list_search(st, nbr_arena, g, posw, ckpt.hypers.cutoff);
+    find_reverse(st, re, g.Ntot);
+  }
   const CutoffSpec cs = model->cutoff_spec();
   const AdaptiveCut ad = adaptive_cutoffs(st, nbr_arena, re, g.Ntot, cs);
   PackedEdges pk = pack_edges(st, nbr_arena, re, g.Ntot, g.spec, cs, pinned, ad);
@@ -352,6 +359,67 @@ void Engine::compute_staged(bool forces) {
   if (g.Ntot > 0 && g.B > 0) run_model(pk, forces);
   else last_pk = pk;
   PETB_CUDA(cudaEventRecord(ev1, st.s));
+}
+
+// The staged batch's pairs from the Verlet cache (cached_edges, src/device_geometry.cpp:262-352): one readback
+// decides between the cached pairs and a new search to cutoff + skin; either way the pairs' vectors come from the
+// positions and cells as they are now, and the packing drops those past the cutoff as it does for an engine's list.
+RawEdges Engine::cached_edges() {
+  const Geom& g = geom;
+  VerletCache& c = verlet;
+  const int N = g.Ntot, B = g.B;
+  const double reach = ckpt.hypers.cutoff + VerletCache::kSkin;
+  bool again = !c.valid;
+  if (!again && N > 0) {
+    verlet_check(st, g, c.pos0, c.cinv0, reach, c.worst);
+    double* h = reinterpret_cast<double*>(pinned + 16);
+    PETB_CUDA(cudaMemcpyAsync(h, c.worst, sizeof(double), cudaMemcpyDeviceToHost, st.s));
+    PETB_CUDA(cudaStreamSynchronize(st.s));
+    again = !(*h < VerletCache::kSkin);
+  }
+  if (again) {
+    // the bins for the longer reach, chosen on the host from the staged cells as staging chooses the model's
+    std::vector<int> gi(7 * size_t(B) + 1);
+    int bins = 0;
+    for (int b = 0; b < B; ++b) {
+      grid_for_cell(h_cells.data() + 9 * size_t(b), h_per[b], h_natoms[b], reach, gi.data() + 3 * b, gi.data() + 3 * B + 3 * b);
+      gi[6 * size_t(B) + b] = bins;
+      bins += gi[3 * b] * gi[3 * b + 1] * gi[3 * b + 2];
+    }
+    gi[7 * size_t(B)] = bins;
+    Geom gr = g;
+    gr.gnc = nbr_arena.alloc<int>(7 * size_t(B) + 1);
+    gr.gnr = gr.gnc + 3 * B, gr.goff = gr.gnr + 3 * B, gr.nbins = bins;
+    PETB_CUDA(cudaMemcpyAsync(gr.gnc, gi.data(), sizeof(int) * gi.size(), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaStreamSynchronize(st.s));  // gi leaves scope
+    posw = nbr_arena.alloc<double>(3 * size_t(N > 0 ? N : 1));
+    wrap_positions(st, gr, posw);
+    const RawEdges found = cell_list_search(st, nbr_arena, gr, posw, reach);
+    find_reverse(st, found, N);
+    cache_arena.reset();
+    const size_t E = found.E, Ea = E > 0 ? E : 1, Na = N > 0 ? N : 1;
+    RawEdges r;
+    r.E = found.E;
+    r.i = cache_arena.alloc<int>(Ea), r.j = cache_arena.alloc<int>(Ea), r.shift = cache_arena.alloc<int>(3 * Ea);
+    r.vec = cache_arena.alloc<double>(3 * Ea), r.dist = cache_arena.alloc<double>(Ea);
+    r.off = cache_arena.alloc<int>(size_t(N) + 1), r.reverse = cache_arena.alloc<int>(Ea);
+    c.pos0 = cache_arena.alloc<double>(3 * Na), c.cinv0 = cache_arena.alloc<double>(9 * size_t(B > 0 ? B : 1));
+    c.worst = cache_arena.alloc<double>(1);
+    PETB_CUDA(cudaMemcpyAsync(r.off, found.off, 4 * (size_t(N) + 1), cudaMemcpyDeviceToDevice, st.s));
+    if (E) {
+      PETB_CUDA(cudaMemcpyAsync(r.i, found.i, 4 * E, cudaMemcpyDeviceToDevice, st.s));
+      PETB_CUDA(cudaMemcpyAsync(r.j, found.j, 4 * E, cudaMemcpyDeviceToDevice, st.s));
+      PETB_CUDA(cudaMemcpyAsync(r.reverse, found.reverse, 4 * E, cudaMemcpyDeviceToDevice, st.s));
+      unwrap_shifts(st, found, g, r.shift);
+    }
+    if (N) PETB_CUDA(cudaMemcpyAsync(c.pos0, g.pos, 24 * size_t(N), cudaMemcpyDeviceToDevice, st.s));
+    if (B) PETB_CUDA(cudaMemcpyAsync(c.cinv0, g.cinv, 72 * size_t(B), cudaMemcpyDeviceToDevice, st.s));
+    c.ref = r, c.valid = true, ++c.searches;
+  } else {
+    ++c.reuses;
+  }
+  edge_vectors_batch(st, c.ref, g);
+  return c.ref;
 }
 
 void Engine::fetch(pet_results* out) {

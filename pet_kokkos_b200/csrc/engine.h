@@ -47,6 +47,21 @@ struct Session {
   int* remote_raw = nullptr;  // [n_remote]
 };
 
+// The pairs of a staged batch within cutoff + skin, kept between evaluations while no atom has moved (and no cell
+// strained) far enough for a pair outside to have come inside the cutoff: the reference's NefCache
+// (include/pet/device_geometry.hpp:198-228, src/device_geometry.cpp:165-352). The shifts are in terms of the
+// unwrapped positions, so a pair survives an atom crossing a cell face. Staging drops it; a batch whose
+// composition changes is staged again and so searched again (the reference reassembles a shrinking batch's pairs).
+struct VerletCache {
+  static constexpr double kSkin = 1.0;  // Angstrom, as the reference's
+  bool valid = false;
+  RawEdges ref;              // i, j, unwrapped shift, off, reverse; vec and dist refreshed each evaluation
+  double* pos0 = nullptr;    // [N,3] the positions at the search
+  double* cinv0 = nullptr;   // [B,9] the inverse cells then
+  double* worst = nullptr;   // [1] the test's result
+  long long searches = 0, reuses = 0;
+};
+
 struct Engine {
   explicit Engine(const std::string& json, const std::string& weights, const pet_options* opts);
   ~Engine();
@@ -70,11 +85,13 @@ struct Engine {
   int gemm_mode = 0;
   bool graphs = true;
   bool md_fixed = false;  // Options::md_fixed_shapes / PET_MD_FIXED
+  bool cache_neighbors = false;  // Options::cache_neighbors / PET_CACHE_NEIGHBORS
   Stream st;
   Profiler prof;
   Checkpoint ckpt;
   std::unique_ptr<Model> model;
-  Arena geom_arena, nbr_arena, save_arena, tmp_arena, session_arena;
+  Arena geom_arena, nbr_arena, save_arena, tmp_arena, session_arena, cache_arena;
+  VerletCache verlet;
   Geom geom;                  // staged batch
   std::vector<double> h_cells;  // staged cells on the host (the grid is chosen there)
   std::vector<int> h_natoms, h_per;
@@ -108,6 +125,7 @@ struct Engine {
   uint64_t graph_clock = 0;
   long long graph_replays = 0;
   void run_model(const PackedEdges& pk, bool forces);
+  RawEdges cached_edges();
   void drop_graphs();
 
  private:

@@ -332,6 +332,76 @@ __global__ void k_edge_vectors(RawEdges re, const double* __restrict__ pos, cons
   re.dist[e] = d2 > 1e-24 ? sqrt(d2) : 1e30;  // a coincident pair weighs nothing
 }
 
+// The same for a batch whose structures each have their own cell (the Verlet cache's pairs).
+__global__ void k_edge_vectors_batch(RawEdges re, Geom g) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= re.E) return;
+  const int i = re.i[e], j = re.j[e], a = re.shift[3 * e], b = re.shift[3 * e + 1], c = re.shift[3 * e + 2];
+  const double* hc = g.scell + 9 * g.sid[i];
+  const double* pos = g.pos;
+  const double x = pos[3 * j] + (a * hc[0] + b * hc[3] + c * hc[6]) - pos[3 * i];
+  const double y = pos[3 * j + 1] + (a * hc[1] + b * hc[4] + c * hc[7]) - pos[3 * i + 1];
+  const double z = pos[3 * j + 2] + (a * hc[2] + b * hc[5] + c * hc[8]) - pos[3 * i + 2];
+  const double d2 = x * x + y * y + z * z;
+  re.vec[3 * e] = x, re.vec[3 * e + 1] = y, re.vec[3 * e + 2] = z;
+  re.dist[e] = d2 > 1e-24 ? sqrt(d2) : 1e30;
+}
+
+// How many cells k_wrap moved atom i by along each periodic axis: the same expression, so the same floor.
+__device__ inline void wrap_count(const Geom& g, int i, int n[3]) {
+  const int b = g.sid[i], per = g.sper[b];
+  n[0] = n[1] = n[2] = 0;
+  if (!per) return;
+  const double* ci = g.cinv + 9 * b;
+  const double x = g.pos[3 * i], y = g.pos[3 * i + 1], z = g.pos[3 * i + 2];
+  for (int d = 0; d < 3; ++d) {
+    const double f = x * ci[d] + y * ci[3 + d] + z * ci[6 + d];
+    n[d] = (per >> d & 1) ? (int) floor(f) : 0;
+  }
+}
+
+// A searched pair's image in terms of the unwrapped positions: posw = pos - n.cell, so
+// posw_j + s.cell - posw_i = pos_j + (s - n_j + n_i).cell - pos_i (src/device_geometry.cpp:176-181).
+__global__ void k_unwrap_shifts(RawEdges re, Geom g, int* __restrict__ out) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= re.E) return;
+  int ni[3], nj[3];
+  wrap_count(g, re.i[e], ni);
+  wrap_count(g, re.j[e], nj);
+  for (int d = 0; d < 3; ++d) out[3 * e + d] = re.shift[3 * e + d] - nj[d] + ni[d];
+}
+
+// The Verlet test (src/device_geometry.cpp:283-307): a pair outside the cached list was more than `reach` apart at
+// the search; it cannot be inside the cutoff now while 2 d + reach |D - I|_F < skin, d the largest move in the
+// strained frame and D = H0^-1 H the strain since. worst = the largest such sum over the atoms.
+__global__ void k_verlet_check(Geom g, const double* __restrict__ pos0, const double* __restrict__ cinv0, double reach,
+                               unsigned long long* __restrict__ worst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= g.Ntot) return;
+  const int b = g.sid[i];
+  const double* c0 = cinv0 + 9 * b;
+  const double* h = g.scell + 9 * b;
+  double e2 = 0.0;
+  for (int a = 0; a < 3; ++a)
+    for (int d = 0; d < 3; ++d) {
+      double x = a == d ? -1.0 : 0.0;
+      for (int k = 0; k < 3; ++k) x += c0[3 * a + k] * h[3 * k + d];
+      e2 += x * x;
+    }
+  double ds[3], d2 = 0.0;
+  for (int d = 0; d < 3; ++d) {
+    ds[d] = 0.0;
+    for (int k = 0; k < 3; ++k) ds[d] += (g.pos[3 * i + k] - pos0[3 * i + k]) * c0[3 * k + d];
+  }
+  for (int d = 0; d < 3; ++d) {
+    const double x = ds[0] * h[d] + ds[1] * h[3 + d] + ds[2] * h[6 + d];
+    d2 += x * x;
+  }
+  double m = 2.0 * sqrt(d2) + reach * sqrt(e2);
+  if (!(m == m)) m = 1e300;  // a NaN position or cell: search again, and let the search report it
+  atomicMax(worst, (unsigned long long) __double_as_longlong(m));  // non-negative doubles order as their bits
+}
+
 // The smooth cutoff factor, argument and transcendentals in float as the reference
 // evaluates them (include/pet/cutoff.hpp:17-26).
 __device__ inline double cutoff_value(double d, double rc, double width, int kind) {
@@ -494,6 +564,26 @@ void find_reverse(Stream& st, const RawEdges& re, int) {
 void edge_vectors(Stream& st, const RawEdges& re, const double* pos, const double* cell9) {
   if (re.E == 0) return;
   k_edge_vectors<<<cdiv(re.E, 256), 256, 0, st.s>>>(re, pos, cell9);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void edge_vectors_batch(Stream& st, const RawEdges& re, const Geom& g) {
+  if (re.E == 0) return;
+  const ProfScope ps(st, PC_GEOMETRY, 0.0, 52.0 * re.E);
+  k_edge_vectors_batch<<<cdiv(re.E, 256), 256, 0, st.s>>>(re, g);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void unwrap_shifts(Stream& st, const RawEdges& re, const Geom& g, int* out) {
+  if (re.E == 0) return;
+  k_unwrap_shifts<<<cdiv(re.E, 256), 256, 0, st.s>>>(re, g, out);
+  PETB_LAUNCH_CHECK(st);
+}
+
+void verlet_check(Stream& st, const Geom& g, const double* pos0, const double* cinv0, double reach, double* worst) {
+  PETB_CUDA(cudaMemsetAsync(worst, 0, sizeof(double), st.s));
+  if (g.Ntot == 0) return;
+  k_verlet_check<<<cdiv(g.Ntot, 256), 256, 0, st.s>>>(g, pos0, cinv0, reach, reinterpret_cast<unsigned long long*>(worst));
   PETB_LAUNCH_CHECK(st);
 }
 

@@ -101,6 +101,13 @@ void grid_for_cell(const double cell[9], int periodic_bits, int n_atoms, double 
 // Host-side inverse cell (rows = lattice vectors), the reference's pet_cellinv.
 void invert_cell(const double c[9], double inv[9]);
 
+// The Verlet cache's kernels (the reference's NefCache, src/device_geometry.cpp:165-352): vectors of cached pairs
+// from a batch's current positions and cells; a searched list's shifts in terms of the unwrapped positions;
+// the test whether a pair outside the cached list could have come inside the cutoff (worst [1], device).
+void edge_vectors_batch(Stream& st, const RawEdges& re, const Geom& g);
+void unwrap_shifts(Stream& st, const RawEdges& re, const Geom& g, int* out);
+void verlet_check(Stream& st, const Geom& g, const double* pos0, const double* cinv0, double reach, double* worst);
+
 // Wrapped positions for the search: posw [Ntot,3].
 void wrap_positions(Stream& st, const Geom& g, double* posw);
 // The cell-list search. Allocates from `arena`; reads back the edge count once.
