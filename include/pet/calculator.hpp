@@ -71,6 +71,24 @@ struct EdgeListView {
   Exchange* exchange = nullptr;  // must outlive the list
 };
 
+// pet::DevicePairListView (include/pet/device_geometry.hpp:137-154): device memory throughout.
+struct DevicePairListView {
+  int n_atoms = 0, n_local = -1, n_pairs = 0;
+  const int* pairs = nullptr;
+  long stride_pair = 5, stride_col = 1;
+  const int* atomic_numbers = nullptr;
+  const int* renumber = nullptr;
+};
+
+// pet::BatchResult for one structure: device pointers, valid until the calculator's next evaluation.
+struct DeviceResults {
+  int n_atoms = 0;
+  const double* energy = nullptr;
+  const double* per_atom_energy = nullptr;
+  const double* forces = nullptr;
+  const double* virial = nullptr;
+};
+
 class Calculator {
  public:
   struct DeviceArrays {
@@ -165,6 +183,16 @@ class Calculator {
     out.energy = t.energy;
     for (int k = 0; k < 6; ++k) out.virial[k] = t.virial[k];
     return out;
+  }
+
+  // An engine's flat pair list on the device, set and evaluated in one call (calculator.hpp:260-268).
+  DeviceResults compute_pairs(const DevicePairListView& v, const double* positions, const double* cell = nullptr,
+                              bool compute_forces = true) {
+    const pet_pair_list l{v.n_atoms, v.n_local, v.n_pairs, v.pairs, v.stride_pair, v.stride_col, v.atomic_numbers, v.renumber};
+    pet_device_results d{};
+    check(pet_compute_pairs(h_, &l, positions, cell, compute_forces ? 1 : 0, &d));
+    atoms_ = v.n_atoms, pairs_ = v.n_pairs;
+    return DeviceResults{d.n_atoms, d.energy, d.per_atom_energy, d.forces, d.virial};
   }
 
   double cutoff() const { return pet_cutoff(h_); }

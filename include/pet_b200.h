@@ -126,6 +126,30 @@ typedef struct pet_totals {
   double virial[6];
 } pet_totals;
 
+/* pet::DevicePairListView (include/pet/device_geometry.hpp:137-154): an engine's pairs as a flat list in DEVICE
+ * memory, in any order, as metatomic hands them over. Pair k is atom pairs[k * stride_pair] ->
+ * pairs[k * stride_pair + stride_col], shifted by the next three columns (lattice vectors, as pet_edge_list's
+ * shifts). A full list. With renumber (device, [n_atoms]) the engine's atom a is atom renumber[a] here, the positions
+ * of every step are permuted the same way, and the results come back in this numbering. Each atom's pairs keep
+ * their order in the list. */
+typedef struct pet_pair_list {
+  int n_atoms, n_local, n_pairs;
+  const int* pairs;             /* device */
+  long stride_pair, stride_col; /* 0, 0: 5 and 1 */
+  const int* atomic_numbers;    /* device [n_atoms], the engine's numbering */
+  const int* renumber;          /* device [n_atoms], optional */
+} pet_pair_list;
+
+/* pet::BatchResult of one structure (calculator.hpp:144-165): DEVICE pointers into the calculator's own buffers,
+ * valid until its next evaluation. forces and virial are null when forces were not asked for. */
+typedef struct pet_device_results {
+  int n_atoms;
+  const double* energy;          /* [1]           */
+  const double* per_atom_energy; /* [n_atoms]     */
+  const double* forces;          /* [n_atoms * 3] */
+  const double* virial;          /* [6]           */
+} pet_device_results;
+
 /* The raw neighbour list of a batch as the device search lists it
  * (pet::RawEdges, include/pet/device_cell_list.hpp:52-59). Caller-allocated with
  * capacity `capacity` edges; n_edges receives the count (the call fails with
@@ -170,6 +194,13 @@ int pet_compute_step(pet_calc* c, const double* positions, const double* cell, i
                      int edge_gradients, pet_results* out);
 /* Calculator::compute_step(const DeviceArrays&, cell) (calculator.hpp:259). */
 int pet_compute_step_device(pet_calc* c, const pet_device_arrays* arrays, const double* cell, pet_totals* totals);
+/* Calculator::compute_pairs (calculator.hpp:260-268): a flat pair list set and evaluated in one call. positions
+ * [n_atoms * 3] is device memory in the engine's order, cell [9] host memory (needed with shifts). The results stay
+ * on the device (pet_fetch_results copies them out), in the list's numbering. It replaces any list
+ * pet_set_neighbors holds; pet_compute_step / pet_compute_step_device then step the same list (a renumbered list
+ * takes device positions). */
+int pet_compute_pairs(pet_calc* c, const pet_pair_list* pairs, const double* positions, const double* cell,
+                      int compute_forces, pet_device_results* out);
 
 /* The device neighbour search alone: build_nef_device's raw list
  * (src/device_geometry.cpp:356-366, src/device_cell_list.cpp:108-292). */

@@ -60,6 +60,17 @@ class PetDeviceArrays(C.Structure):
                 ("per_atom_virial", C.c_void_p), ("virial_scale", C.c_double)]
 
 
+class PetPairList(C.Structure):
+    _fields_ = [("n_atoms", C.c_int), ("n_local", C.c_int), ("n_pairs", C.c_int), ("pairs", C.c_void_p),
+                ("stride_pair", C.c_long), ("stride_col", C.c_long), ("atomic_numbers", C.c_void_p),
+                ("renumber", C.c_void_p)]
+
+
+class PetDeviceResults(C.Structure):
+    _fields_ = [("n_atoms", C.c_int), ("energy", C.c_void_p), ("per_atom_energy", C.c_void_p), ("forces", C.c_void_p),
+                ("virial", C.c_void_p)]
+
+
 class PetTotals(C.Structure):
     _fields_ = [("energy", C.c_double), ("virial", C.c_double * 6)]
 
@@ -90,6 +101,8 @@ SIGNATURES = {
     "pet_set_neighbors": (C.c_int, [C.c_void_p, _P(PetEdgeList)]),
     "pet_compute_step": (C.c_int, [C.c_void_p, _P(C.c_double), _P(C.c_double), C.c_int, C.c_int, _P(PetResults)]),
     "pet_compute_step_device": (C.c_int, [C.c_void_p, _P(PetDeviceArrays), _P(C.c_double), _P(PetTotals)]),
+    "pet_compute_pairs": (C.c_int, [C.c_void_p, _P(PetPairList), C.c_void_p, _P(C.c_double), C.c_int,
+                                    _P(PetDeviceResults)]),
     "pet_neighbor_list": (C.c_int, [C.c_void_p, _P(PetSystem), C.c_int, _P(PetRawEdges)]),
     "pet_cutoff": (C.c_double, [C.c_void_p]),
     "pet_ghost_cutoff": (C.c_double, [C.c_void_p]),
@@ -409,6 +422,25 @@ class Calculator:
         t = PetTotals()
         self._check(self._lib.pet_compute_step_device(self._h, C.byref(a), None if c is None else _dptr(c), C.byref(t)))
         return t.energy, np.array(list(t.virial))
+
+    def compute_pairs(self, n_atoms, n_pairs, pairs_ptr, atomic_numbers_ptr, positions_ptr, cell=None, renumber_ptr=0,
+                      n_local=-1, stride_pair=5, stride_col=1, compute_forces=True, fetch=True):
+        """Calculator::compute_pairs(DevicePairListView, positions, cell) (calculator.hpp:260-268): an engine's flat
+        pair list in device memory, set and evaluated in one call. Pointers are device addresses as integers.
+        Returns the device pointers (dict) and, with fetch, the results copied to the host in the list's numbering."""
+        v = PetPairList(n_atoms, n_local, n_pairs, pairs_ptr or None, stride_pair, stride_col, atomic_numbers_ptr or None,
+                        renumber_ptr or None)
+        c = None if cell is None else np.ascontiguousarray(cell, dtype=np.float64).reshape(9)
+        d = PetDeviceResults()
+        self._check(self._lib.pet_compute_pairs(self._h, C.byref(v), positions_ptr or None, None if c is None else _dptr(c),
+                                                int(compute_forces), C.byref(d)))
+        self._session_pairs, self._session_atoms = n_pairs, n_atoms
+        dev = dict(energy=d.energy, per_atom_energy=d.per_atom_energy, forces=d.forces, virial=d.virial)
+        if not fetch:
+            return dev, None
+        r, pr = self._results(1, n_atoms, compute_forces, [n_atoms])
+        self._check(self._lib.pet_fetch_results(self._h, C.byref(pr)))
+        return dev, r
 
     # ---- the neighbour search alone ----
     def neighbor_list(self, systems, capacity=None):

@@ -54,6 +54,21 @@ __global__ void k_live_fill(int* __restrict__ live, int* __restrict__ live_packe
 }
 
 // eg(e) += gmag(e) v(e)
+// A flat pair list's columns into a dense [P,5] block, whatever its strides.
+__global__ void k_dense_pairs(int* __restrict__ out, const int* __restrict__ pairs, long sp, long sc, int P) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= 5 * P) return;
+  out[t] = pairs[(t / 5) * sp + (t % 5) * sc];
+}
+
+// The engine's positions into the list's numbering.
+__global__ void k_renumber_positions(double* __restrict__ out, const double* __restrict__ x, const int* __restrict__ ren, int N) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  const int to = ren[i];
+  for (int c = 0; c < 3; ++c) out[3 * to + c] = x[3 * i + c];
+}
+
 __global__ void k_add_radial(double* __restrict__ eg, const double* __restrict__ gmag, const double* __restrict__ vec, int E) {
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= E) return;
@@ -581,7 +596,7 @@ void Engine::set_neighbors(const pet_edge_list* v) {
   s.overflow = A.alloc<int>(1);
   PETB_CUDA(cudaMemsetAsync(s.overflow, 0, sizeof(int), st.s));
   s.has_exchange = v->exchange != nullptr;
-  s.n_remote = 0, s.remote_raw = nullptr;
+  s.n_remote = 0, s.remote_raw = nullptr, s.renumber = nullptr;
   if (s.has_exchange) {
     s.exchange = *v->exchange;
     std::vector<int> remote;
@@ -617,8 +632,13 @@ static StepOut session_step(Engine& I, const double* positions, bool on_device, 
   I.tmp_arena.reset();
   PETB_CUDA(cudaEventRecord(I.ev0, st.s));
   const int N = s.n_atoms;
-  if (N)
+  if (s.renumber && !on_device) throw Error(1, "pet: a renumbered list takes device positions");
+  if (N && s.renumber) {
+    k_renumber_positions<<<cdiv(N, 256), 256, 0, st.s>>>(s.pos, positions, s.renumber, N);
+    PETB_LAUNCH_CHECK(st);
+  } else if (N) {
     PETB_CUDA(cudaMemcpyAsync(s.pos, positions, 24 * size_t(N), on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st.s));
+  }
   if (cell) PETB_CUDA(cudaMemcpyAsync(s.cell, cell, 72, cudaMemcpyHostToDevice, st.s));
   edge_vectors(st, s.re, s.pos, s.cell);
   // With an exchange only the owned atoms are centres (token rows); ghosts are neighbours.
@@ -750,6 +770,90 @@ void Engine::compute_step_device(const pet_device_arrays* a, const double* cell,
     break;
   }
   if (totals) *totals = t;
+}
+
+// An engine's pairs as a flat device list (EdgeSession::set(DevicePairListView), src/device_geometry.cpp:547-669;
+// Calculator::compute_pairs). The list comes to the host once per set, where each centre's pairs are gathered in
+// list order (the reference's run and scattered cases give the same order); every step stays on the device.
+void Engine::compute_pairs(const pet_pair_list* v, const double* positions, const double* cell, bool forces,
+                           pet_device_results* out) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (!v || v->n_atoms < 0 || v->n_pairs < 0) throw Error(2, "pet: no pair list given");
+  const int N = v->n_atoms, P = v->n_pairs;
+  if ((P > 0 && !v->pairs) || (N > 0 && !v->atomic_numbers)) throw Error(2, "pet: a pair list needs pairs and atomic numbers");
+  if (N > 0 && !positions) throw Error(2, "pet: no device positions given");
+  if (N >= (1 << 24)) throw Error(1, "pet: too many atoms for the edge key");
+  const long sp = v->stride_pair ? v->stride_pair : 5, sc = v->stride_col ? v->stride_col : 1;
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  tmp_arena.reset();
+  std::vector<int> hp(5 * size_t(P)), z(N), ren(v->renumber ? N : 0);
+  if (P) {
+    int* dense = tmp_arena.alloc<int>(5 * size_t(P));
+    k_dense_pairs<<<cdiv(5 * size_t(P), 256), 256, 0, st.s>>>(dense, v->pairs, sp, sc, P);
+    PETB_LAUNCH_CHECK(st);
+    PETB_CUDA(cudaMemcpyAsync(hp.data(), dense, 20 * size_t(P), cudaMemcpyDeviceToHost, st.s));
+  }
+  if (N) PETB_CUDA(cudaMemcpyAsync(z.data(), v->atomic_numbers, 4 * size_t(N), cudaMemcpyDeviceToHost, st.s));
+  if (N && v->renumber) PETB_CUDA(cudaMemcpyAsync(ren.data(), v->renumber, 4 * size_t(N), cudaMemcpyDeviceToHost, st.s));
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+
+  const bool has_ren = v->renumber != nullptr;
+  if (has_ren) {  // it must be a permutation
+    std::vector<char> seen(N, 0);
+    for (int a = 0; a < N; ++a) {
+      if (ren[a] < 0 || ren[a] >= N || seen[ren[a]]) throw Error(1, "pet: the renumbering is not a permutation of the atoms");
+      seen[ren[a]] = 1;
+    }
+  }
+  auto ours = [&](int a) { return has_ren ? ren[a] : a; };
+  std::vector<int> zz(N);
+  int uncovered = 0;
+  for (int a = 0; a < N; ++a) {
+    zz[ours(a)] = z[a];
+    uncovered += ckpt.species_to_index.empty() || z[a] < 0 || z[a] >= int(ckpt.species_to_index.size()) ||
+                 ckpt.species_to_index[z[a]] < 0;
+  }
+  if (uncovered) throw Error(1, "pet: " + std::to_string(uncovered) + " atoms have elements the model does not cover");
+  std::vector<int> off(size_t(N) + 1, 0);
+  int bad = 0;
+  for (int k = 0; k < P; ++k) {
+    const int i = hp[5 * size_t(k)], j = hp[5 * size_t(k) + 1];
+    if (i < 0 || i >= N || j < 0 || j >= N) ++bad;
+    else ++off[ours(i) + 1];
+  }
+  if (bad) throw Error(1, "pet: " + std::to_string(bad) + " pairs name atoms that do not exist");
+  for (int a = 0; a < N; ++a) off[a + 1] += off[a];
+  std::vector<int> cur(off.begin(), off.end() - 1), nb(P), sh(3 * size_t(P));
+  bool shifted = false;
+  for (int k = 0; k < P; ++k) {
+    const int e = cur[ours(hp[5 * size_t(k)])]++;
+    nb[e] = ours(hp[5 * size_t(k) + 1]);
+    for (int d = 0; d < 3; ++d) {
+      sh[3 * size_t(e) + d] = hp[5 * size_t(k) + 2 + d];
+      shifted = shifted || sh[3 * size_t(e) + d] != 0;
+    }
+  }
+  pet_edge_list list{};
+  list.n_atoms = N, list.n_local = v->n_local;
+  list.atomic_numbers = zz.data(), list.offsets = off.data(), list.neighbors = nb.data();
+  list.shifts = shifted ? sh.data() : nullptr;
+  list.cell = cell, list.half = 0, list.exchange = nullptr;
+  set_neighbors(&list);
+  if (has_ren && N) {
+    md.renumber = session_arena.alloc<int>(N);
+    PETB_CUDA(cudaMemcpyAsync(md.renumber, ren.data(), 4 * size_t(N), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaStreamSynchronize(st.s));
+  }
+  session_step(*this, positions, true, cell, forces);
+  if (fixed_step_overflowed(*this)) session_step(*this, positions, true, cell, forces);
+  if (out) {
+    *out = pet_device_results{};
+    out->n_atoms = N;
+    if (have_out) {
+      out->energy = last_out.f.energy, out->per_atom_energy = last_out.per_atom;
+      if (last_out.has_forces) out->forces = last_out.f.forces, out->virial = last_out.f.vir6;
+    }
+  }
 }
 
 // ---- testing aids ---------------------------------------------------------------------

@@ -45,6 +45,7 @@ struct Session {
   pet_exchange exchange{};
   int n_remote = 0;
   int* remote_raw = nullptr;  // [n_remote]
+  int* renumber = nullptr;    // [n_atoms] a flat pair list's renumbering (device); null: none
 };
 
 // The pairs of a staged batch within cutoff + skin, kept between evaluations while no atom has moved (and no cell
@@ -76,6 +77,8 @@ struct Engine {
   void set_neighbors(const pet_edge_list* list);
   void compute_step(const double* positions, const double* cell, bool forces, bool edge_gradients, pet_results* out);
   void compute_step_device(const pet_device_arrays* arrays, const double* cell, pet_totals* totals);
+  void compute_pairs(const pet_pair_list* pairs, const double* positions, const double* cell, bool forces,
+                     pet_device_results* out);
   void debug_fetch(const char* name, float* out, size_t capacity, size_t* n);
   void gemm_host(int mode, bool w_transposed, int m, int n, int k, const float* A, const float* W, float* C);
 

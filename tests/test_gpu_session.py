@@ -213,3 +213,89 @@ def test_device_arrays_step_adds_into_the_engines_arrays(lib_path, models, fixed
                                    atol=1e-9 * max(1.0, np.abs(ref.virial).max()))
     host.close()
     dev.close()
+
+
+@pytest.mark.parametrize("renumbered", [False, True])
+@pytest.mark.parametrize("order", ["listed", "interleaved", "strided"])
+def test_flat_pair_list_on_the_device_gets_what_the_host_list_does(calc, renumbered, order):
+    """tests/test_edges.cpp:709-779: the engine numbers the atoms backwards and hands the pairs over flat, in list
+    order or each atom's pairs interleaved with the others'; with the renumbering the answer comes back in ours."""
+    import torch
+    s = st.diamond(2, jitter=0.05, seed=21)
+    n = s["n_atoms"]
+    v = full_list(s, calc.cutoff, skin=0.5)
+    ref = calc.compute_edges(v)
+    off = np.asarray(v.offsets)
+    P = int(off[-1])
+    theirs = np.arange(n)[::-1].copy() if renumbered else np.arange(n)
+    i = np.repeat(np.arange(n), np.diff(off))
+    flat = np.column_stack([theirs[i], theirs[np.asarray(v.neighbors)], np.asarray(v.shifts)]).astype(np.int32)
+    if order == "interleaved":  # round-robin over the atoms: a scattered list, each atom's pairs still in their order
+        rank = np.arange(P) - off[i]
+        flat = flat[np.lexsort((i, rank))]
+    ren = np.empty(n, np.int32)
+    ren[theirs] = np.arange(n)
+    z = np.empty(n, np.int32)
+    z[theirs] = s["atomic_numbers"]
+    x = np.empty((n, 3))
+    x[theirs] = s["positions"]
+    dev = "cuda:0"
+    if order == "strided":  # column-major storage: stride_pair 1, stride_col P
+        t_pairs = torch.tensor(np.ascontiguousarray(flat.T), device=dev)
+        strides = dict(stride_pair=1, stride_col=P)
+    else:
+        t_pairs = torch.tensor(flat, device=dev)
+        strides = {}
+    t_z, t_ren, t_x = torch.tensor(z, device=dev), torch.tensor(ren, device=dev), torch.tensor(x, device=dev)
+    torch.cuda.synchronize()
+    ptrs, r = calc.compute_pairs(n, P, t_pairs.data_ptr(), t_z.data_ptr(), t_x.data_ptr(), cell=s["cell"],
+                                 renumber_ptr=t_ren.data_ptr() if renumbered else 0, **strides)
+    assert r.energy[0] == ref.energy[0]
+    assert np.array_equal(r.forces, ref.forces) and np.array_equal(r.virial, ref.virial)
+    assert np.array_equal(r.per_atom_energy, ref.per_atom_energy)
+    assert ptrs["energy"] and ptrs["forces"] and ptrs["virial"] and ptrs["per_atom_energy"]
+    # the list stays set: a step over moved positions, on the device, in the engine's order
+    moved = s["positions"] + np.random.default_rng(3).normal(0, 0.02, (n, 3))
+    want = calc.compute_edges(EdgeListView(moved, v.atomic_numbers, v.offsets, v.neighbors, v.shifts, v.cell))
+    xm = np.empty((n, 3))
+    xm[theirs] = moved
+    t_xm = torch.tensor(xm, device=dev)
+    forces = torch.zeros((n, 3), dtype=torch.float64, device=dev)
+    torch.cuda.synchronize()
+    ptrs, r = calc.compute_pairs(n, P, t_pairs.data_ptr(), t_z.data_ptr(), t_xm.data_ptr(), cell=s["cell"],
+                                 renumber_ptr=t_ren.data_ptr() if renumbered else 0, **strides)
+    e, w = calc.compute_step_device(t_xm.data_ptr(), forces.data_ptr(), cell=s["cell"])
+    torch.cuda.synchronize()
+    assert e == want.energy[0] and np.array_equal(w, want.virial[0])
+    assert np.array_equal(forces.cpu().numpy(), want.forces)
+
+
+def test_flat_pair_list_errors(calc):
+    """src/device_geometry.cpp:560-607: a renumbering that is no permutation, pairs naming atoms that do not exist,
+    elements the model does not cover; a renumbered list takes device positions."""
+    import torch
+    s = st.diamond(1, jitter=0.02, seed=2)
+    n = s["n_atoms"]
+    v = full_list(s, calc.cutoff)
+    P = int(np.asarray(v.offsets)[-1])
+    i = np.repeat(np.arange(n), np.diff(v.offsets))
+    flat = np.column_stack([i, np.asarray(v.neighbors), np.asarray(v.shifts)]).astype(np.int32)
+    dev = "cuda:0"
+    t_x = torch.tensor(s["positions"], device=dev)
+    t_z = torch.tensor(np.asarray(s["atomic_numbers"], np.int32), device=dev)
+    t_pairs = torch.tensor(flat, device=dev)
+    bad_ren = torch.tensor(np.zeros(n, np.int32), device=dev)
+    with pytest.raises(RuntimeError, match="not a permutation"):
+        calc.compute_pairs(n, P, t_pairs.data_ptr(), t_z.data_ptr(), t_x.data_ptr(), cell=s["cell"], renumber_ptr=bad_ren.data_ptr())
+    bad = flat.copy()
+    bad[3, 1] = n + 5
+    t_bad = torch.tensor(bad, device=dev)
+    with pytest.raises(RuntimeError, match="1 pairs name atoms that do not exist"):
+        calc.compute_pairs(n, P, t_bad.data_ptr(), t_z.data_ptr(), t_x.data_ptr(), cell=s["cell"])
+    t_zbad = torch.tensor(np.full(n, 117, np.int32), device=dev)
+    with pytest.raises(RuntimeError, match="elements the model does not cover"):
+        calc.compute_pairs(n, P, t_pairs.data_ptr(), t_zbad.data_ptr(), t_x.data_ptr(), cell=s["cell"])
+    ident = torch.tensor(np.arange(n, dtype=np.int32), device=dev)
+    calc.compute_pairs(n, P, t_pairs.data_ptr(), t_z.data_ptr(), t_x.data_ptr(), cell=s["cell"], renumber_ptr=ident.data_ptr())
+    with pytest.raises(RuntimeError, match="takes device positions"):
+        calc.compute_step(s["positions"], s["cell"])
