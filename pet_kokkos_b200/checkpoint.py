@@ -141,11 +141,13 @@ def random_tensors(h, n_species, seed=0, init="n002"):
     return out
 
 
-def write_safetensors(path, tensors):
+def write_safetensors(path, tensors, keep_f64=False):
+    """F32 throughout; with keep_f64, float64 arrays stay F64 (a converted model's statistics are stored so)."""
     header, off = {}, 0
+    wide = lambda v: keep_f64 and np.asarray(v).dtype == np.float64
     for k, v in tensors.items():
-        n = v.size * 4
-        header[k] = {"dtype": "F32", "shape": list(v.shape), "data_offsets": [off, off + n]}
+        n = v.size * (8 if wide(v) else 4)
+        header[k] = {"dtype": "F64" if wide(v) else "F32", "shape": list(v.shape), "data_offsets": [off, off + n]}
         off += n
     hj = json.dumps(header, separators=(",", ":")).encode()
     hj += b" " * ((8 - len(hj) % 8) % 8)
@@ -153,7 +155,7 @@ def write_safetensors(path, tensors):
         f.write(struct.pack("<Q", len(hj)))
         f.write(hj)
         for v in tensors.values():
-            f.write(np.ascontiguousarray(v, dtype="<f4").tobytes())
+            f.write(np.ascontiguousarray(v, dtype="<f8" if wide(v) else "<f4").tobytes())
 
 
 def read_safetensors(path):

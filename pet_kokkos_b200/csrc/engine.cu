@@ -172,7 +172,7 @@ int Engine::species_index(int Z) const {
 
 // ---- staging (stage_systems, src/device_geometry.cpp:368-401) -------------------
 
-void Engine::stage(const pet_system* systems, int B) {
+void Engine::stage(const pet_system* systems, int B, bool keep_cache) {
   PETB_CUDA(cudaSetDevice(device));
   if (B < 0 || (B > 0 && !systems)) throw Error(2, "pet: no systems given");
   long long Nll = 0;
@@ -195,6 +195,7 @@ void Engine::stage(const pet_system* systems, int B) {
   int* h_gnc = h_sper + B;
   int* h_gnr = h_gnc + 3 * B;
   int* h_goff = h_gnr + 3 * B;
+  const std::vector<int> was_natoms = h_natoms, was_per = h_per, was_species = h_species;
   h_cells.assign(size_t(B) * 9, 0.0);
   h_natoms.assign(B, 0);
   h_per.assign(B, 0);
@@ -234,7 +235,10 @@ void Engine::stage(const pet_system* systems, int B) {
   g.gnr = g.gnc + 3 * B;
   g.goff = g.gnr + 3 * B;
   geom = g;
-  verlet.valid = false;  // staging resets the neighbour cache (include/pet/calculator.hpp:210-212)
+  h_species.assign(h_spec, h_spec + N);
+  // Calculator::stage resets the neighbour cache (include/pet/calculator.hpp:210-212); an evaluation that stages
+  // the same atoms again keeps it
+  verlet.valid = verlet.valid && keep_cache && was_natoms == h_natoms && was_per == h_per && was_species == h_species;
   // the copy must finish before the staging block is reused by another stage()
   PETB_CUDA(cudaStreamSynchronize(st.s));
 }
@@ -461,7 +465,7 @@ void Engine::fetch(pet_results* out) {
 }
 
 void Engine::compute(const pet_system* systems, int B, bool forces, pet_results* out) {
-  stage(systems, B);
+  stage(systems, B, true);
   compute_staged(forces);
   fetch(out);
 }

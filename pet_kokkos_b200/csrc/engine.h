@@ -69,7 +69,9 @@ struct Engine {
 
   // Calculator::compute(vector<System>) on the device path.
   void compute(const pet_system* systems, int B, bool forces, pet_results* out);
-  void stage(const pet_system* systems, int B);
+  // keep_cache: the Verlet cache survives when the batch is the same atoms as the last one staged (compute() with
+  // Options::cache_neighbors steps a structure this way, src/calculator.cpp:638-644); Calculator::stage drops it.
+  void stage(const pet_system* systems, int B, bool keep_cache = false);
   void update_staged(const double* positions, const double* cells);
   void compute_staged(bool forces);
   void fetch(pet_results* out);
@@ -97,7 +99,7 @@ struct Engine {
   VerletCache verlet;
   Geom geom;                  // staged batch
   std::vector<double> h_cells;  // staged cells on the host (the grid is chosen there)
-  std::vector<int> h_natoms, h_per;
+  std::vector<int> h_natoms, h_per, h_species;
   double* posw = nullptr;
   PackedEdges last_pk;
   PassOut last_out;

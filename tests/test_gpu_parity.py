@@ -172,3 +172,32 @@ def test_errors_are_reported(models, lib_path):
     r = c.compute(st.diamond(1))  # still usable afterwards
     assert np.isfinite(r.energy).all()
     c.close()
+
+
+def test_a_converted_model_with_extra_heads_loads_and_the_extras_are_ignored(models, tmp_path):
+    """A converted published model carries last-layer uncertainty and non-conservative heads next to the energy
+    model (tools/convert_pet.py:342-420; src/checkpoint.cpp:122-135). This path evaluates the energy model: the
+    extra json sections and tensors (float64 ones among them) do not change it."""
+    import json
+    from pet_kokkos_b200 import Calculator, checkpoint as ck
+    jp, sp = models("tiny", "feedforward", "scaled", 4)
+    meta = json.loads(open(jp).read())
+    tens = ck.read_safetensors(sp)
+    h = meta["hypers"]
+    F = 2 * h.get("num_readout_layers", 1) * h["d_head"]
+    rng = np.random.default_rng(0)
+    tens = dict(tens)
+    tens["llpr.energy.inv_cholesky"] = rng.normal(size=(F, F))  # float64, as the converter writes it
+    tens["llpr.energy.ensemble"] = rng.normal(size=(4, F)).astype(np.float32)
+    tens["non_conservative.forces.node_heads.0.0.weight"] = rng.normal(size=(h["d_head"], h["d_pet"])).astype(np.float32)
+    meta["uncertainty"] = {"energy": {"features": F, "multiplier": 1.5, "ensemble": 4}}
+    meta["non_conservative"] = {"force": {"scale": [0.25]}, "stress": {"scale": [2.0]}}
+    jp2, sp2 = tmp_path / "extras.json", tmp_path / "extras.safetensors"
+    jp2.write_text(json.dumps(meta))
+    ck.write_safetensors(sp2, tens, keep_f64=True)
+    assert ck.read_safetensors(sp2)["llpr.energy.inv_cholesky"].dtype == np.float64
+    s = st.diamond(2, jitter=0.05, seed=3)
+    a, b = Calculator(jp, sp), Calculator(jp2, sp2)
+    ra, rb = a.compute(s), b.compute(s)
+    assert ra.energy[0] == rb.energy[0] and np.array_equal(ra.forces, rb.forces) and np.array_equal(ra.virial, rb.virial)
+    a.close(), b.close()

@@ -118,9 +118,24 @@ def test_staging_resets_the_cache(models):
     staged(cached, [s], first=True)
     staged(cached, [s], first=True)
     assert cached.neighbor_searches == 2 and cached.neighbor_reuses == 0
-    r = cached.compute(s)  # compute() stages: a search each time
-    assert cached.neighbor_searches == 3 and np.isfinite(r.energy).all()
     cached.close()
+
+
+def test_compute_on_the_same_atoms_keeps_the_cache(models):
+    """An ASE-style loop: compute() on a structure whose atoms move a little each call (src/calculator.cpp:638-644)."""
+    plain, cached = make(models, False), make(models, True)
+    s = st.diamond(2, jitter=0.05, seed=7)
+    rng = np.random.default_rng(2)
+    for step in range(4):
+        close(cached.compute(s), plain.compute(s))
+        s = st.make_system(s["atomic_numbers"], s["positions"] + rng.normal(0, 0.02, s["positions"].shape), s["cell"])
+    assert cached.neighbor_searches == 1 and cached.neighbor_reuses == 3
+    other = st.make_system(np.where(np.arange(64) == 3, 14, s["atomic_numbers"]), s["positions"], s["cell"])
+    close(cached.compute(other), plain.compute(other))  # another element somewhere: other atoms, a new search
+    assert cached.neighbor_searches == 2
+    close(cached.compute(st.diamond(1, jitter=0.02, seed=1)), plain.compute(st.diamond(1, jitter=0.02, seed=1)))
+    assert cached.neighbor_searches == 3
+    plain.close(), cached.close()
 
 
 def test_adaptive_cutoff_over_cached_pairs(models, tmp_path):
