@@ -229,6 +229,14 @@ long long pet_kernel_launches(const pet_calc* c);
 long long pet_graph_replays(const pet_calc* c);
 /* Neighbour searches run for staged batches under Options::cache_neighbors, and the evaluations the cached
  * pairs served instead (the reference's NefCache, include/pet/device_geometry.hpp:198-228). */
+/* Batches that pet_compute ran as several consecutive pieces to fit Options::memory_budget_bytes /
+ * Options::max_batch_atoms (src/calculator.cpp:326-345). */
+long long pet_batch_splits(const pet_calc* c);
+/* Evaluations that ran out of device memory and were retried with the pools released and the batch cut smaller
+ * (the reference's recovery, src/model.cpp:952-971). pet_debug_fail_alloc(k) is the test hook for it: the k-th
+ * device allocation of the scratch pools from now (0 = the next) reports out of memory once; k < 0 disarms. */
+long long pet_oom_recoveries(const pet_calc* c);
+void pet_debug_fail_alloc(long k);
 long long pet_neighbor_searches(const pet_calc* c);
 long long pet_neighbor_reuses(const pet_calc* c);
 double pet_last_device_ms(const pet_calc* c);

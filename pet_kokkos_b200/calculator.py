@@ -114,6 +114,9 @@ SIGNATURES = {
     "pet_kernel_launches": (C.c_longlong, [C.c_void_p]),
     "pet_last_device_ms": (C.c_double, [C.c_void_p]),
     "pet_graph_replays": (C.c_longlong, [C.c_void_p]),
+    "pet_batch_splits": (C.c_longlong, [C.c_void_p]),
+    "pet_oom_recoveries": (C.c_longlong, [C.c_void_p]),
+    "pet_debug_fail_alloc": (None, [C.c_long]),
     "pet_neighbor_searches": (C.c_longlong, [C.c_void_p]),
     "pet_neighbor_reuses": (C.c_longlong, [C.c_void_p]),
     "pet_profile": (C.c_int, [C.c_void_p, C.c_int]),
@@ -214,7 +217,7 @@ class Calculator:
     """A loaded model on one GPU.  Reuse one across calls: it holds the scratch pools."""
 
     def __init__(self, model_json, model_weights=None, gemm=None, device=-1, graphs=None, md_fixed_shapes=None,
-                 cache_neighbors=None):
+                 cache_neighbors=None, memory_budget_bytes=0, max_batch_atoms=0):
         self._h = None
         self._lib = load_library()
         if model_weights is None:  # a path prefix, as the reference's resolve_model accepts
@@ -227,6 +230,7 @@ class Calculator:
             o.graphs = int(bool(graphs))
         if md_fixed_shapes is not None:  # Options::md_fixed_shapes (calculator.hpp:111-116)
             o.md_fixed_shapes = int(bool(md_fixed_shapes))
+        o.memory_budget_bytes, o.max_batch_atoms = int(memory_budget_bytes), int(max_batch_atoms)
         if cache_neighbors:  # Options::cache_neighbors (calculator.hpp:36-40): a Verlet cache for staged batches
             o.cache_neighbors = 1
         h = C.c_void_p()
@@ -283,6 +287,20 @@ class Calculator:
     @property
     def graph_replays(self):
         return self._lib.pet_graph_replays(self._h)
+
+    @property
+    def batch_splits(self):
+        """Batches compute() ran as several pieces to fit memory_budget_bytes / max_batch_atoms."""
+        return self._lib.pet_batch_splits(self._h)
+
+    @property
+    def oom_recoveries(self):
+        """Evaluations retried after the device ran out of memory (pools released, the batch cut smaller)."""
+        return self._lib.pet_oom_recoveries(self._h)
+
+    def fail_alloc(self, k):
+        """Test hook: the k-th device allocation of the scratch pools from now reports out of memory, once."""
+        self._lib.pet_debug_fail_alloc(int(k))
 
     @property
     def neighbor_searches(self):

@@ -140,6 +140,9 @@ int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neig
 }
 long long pet_kernel_launches(const pet_calc* c) { return c && c->e ? c->e->st.launches : 0; }
 long long pet_graph_replays(const pet_calc* c) { return c && c->e ? c->e->graph_replays : 0; }
+long long pet_oom_recoveries(const pet_calc* c) { return c && c->e ? c->e->oom_recoveries : 0; }
+void pet_debug_fail_alloc(long k) { petb::g_fail_alloc_in = k; }
+long long pet_batch_splits(const pet_calc* c) { return c && c->e ? c->e->batch_splits : 0; }
 long long pet_neighbor_searches(const pet_calc* c) { return c && c->e ? c->e->verlet.searches : 0; }
 long long pet_neighbor_reuses(const pet_calc* c) { return c && c->e ? c->e->verlet.reuses : 0; }
 double pet_last_device_ms(const pet_calc* c) { return c && c->e ? c->e->last_ms : 0.0; }

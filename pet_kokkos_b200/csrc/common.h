@@ -29,6 +29,10 @@ struct Error : std::runtime_error {
 
 inline int cdiv(long long a, long long b) { return int((a + b - 1) / b); }
 
+// Failure injection for tests, on the host: when >= 0, the pools' cudaMalloc number g_fail_alloc_in from now reports
+// out of memory instead of allocating (once). No GPU fault is involved.
+inline long g_fail_alloc_in = -1;
+
 // Device scratch for one evaluation: a bump allocator over a few large blocks.
 // The first evaluations grow it (cudaMalloc); later ones of the same shapes
 // allocate nothing, so the pointers repeat and a captured graph stays valid.
@@ -58,6 +62,8 @@ class Arena {
     size_t size = next_block_;
     while (size < bytes) size *= 2;
     Block b;
+    if (g_fail_alloc_in >= 0 && g_fail_alloc_in-- == 0)
+      throw Error(4, "cudaMalloc: out of memory (injected for a test)");
     PETB_CUDA(cudaMalloc(&b.ptr, size));
     b.size = size;
     b.used = bytes;

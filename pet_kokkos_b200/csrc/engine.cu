@@ -133,6 +133,8 @@ Engine::Engine(const std::string& json, const std::string& weights, const pet_op
   graphs = (opts && opts->graphs >= 0 ? opts->graphs : env_int("PET_GRAPHS", 1)) != 0;
   md_fixed = (opts && opts->md_fixed_shapes >= 0 ? opts->md_fixed_shapes : env_int("PET_MD_FIXED", 0)) != 0;
   cache_neighbors = (opts && opts->cache_neighbors > 0) || env_int("PET_CACHE_NEIGHBORS", 0) != 0;
+  memory_budget = opts ? opts->memory_budget_bytes : 0;
+  max_batch_atoms = opts && opts->max_batch_atoms > 0 ? opts->max_batch_atoms : 0;
   PETB_CUDA(cudaStreamCreateWithFlags(&st.s, cudaStreamNonBlocking));
   PETB_CUDA(cudaEventCreate(&ev0));
   PETB_CUDA(cudaEventCreate(&ev1));
@@ -375,6 +377,7 @@ void Engine::compute_staged(bool forces) {
   PackedEdges pk = pack_edges(st, nbr_arena, re, g.Ntot, g.spec, cs, pinned, ad);
   pk.n_atoms = g.Ntot, pk.n_local = g.Ntot, pk.B = g.B, pk.sid = g.sid, pk.soff = g.soff;
   last_B = g.B, last_N = g.Ntot;
+  peak_slots = std::max(peak_slots, double(g.Ntot) * double(pk.M + 1));
   if (g.Ntot > 0 && g.B > 0) run_model(pk, forces);
   else last_pk = pk;
   PETB_CUDA(cudaEventRecord(ev1, st.s));
@@ -464,10 +467,127 @@ void Engine::fetch(pet_results* out) {
     throw Error(5, "pet: a tensor-core GEMM gave up waiting on its pipeline; the results of this evaluation are invalid");
 }
 
+// How many neighbours an atom of this structure has, roughly: the density times the cutoff sphere for a periodic
+// structure, every other atom for a small one (the reference's neighbors_estimate).
+static double neighbors_estimate(const pet_system& s, double cutoff) {
+  const double all = s.n_atoms > 1 ? double(s.n_atoms - 1) : 1.0;
+  if (!(s.pbc[0] || s.pbc[1] || s.pbc[2])) return all;
+  const double* c = s.cell;
+  const double vol = std::fabs(c[0] * (c[4] * c[8] - c[5] * c[7]) - c[1] * (c[3] * c[8] - c[5] * c[6]) +
+                               c[2] * (c[3] * c[7] - c[4] * c[6]));
+  if (!(vol > 1e-9)) return all;
+  const double est = 4.18879020478639 * cutoff * cutoff * cutoff * double(s.n_atoms) / vol;
+  return est > 1.0 ? est : 1.0;
+}
+
+std::vector<std::pair<int, int>> Engine::memory_runs(const pet_system* systems, int B) const {
+  const Hypers& h = ckpt.hypers;
+  const double pool = double(save_arena.capacity() + tmp_arena.capacity() + nbr_arena.capacity());
+  // bytes per edge slot: measured once an evaluation of some size has run, else from the widths of what a pass saves
+  // (about 64 floats of d_pet per token row of a 2 x 2 model), a quarter more for what else the pools hold
+  const double blocks = double(h.num_gnn_layers) * double(h.num_attention_layers);
+  const double estimate = 1.25 * 4.0 * double(h.d_pet) * (12.0 * blocks + 8.0 * h.num_gnn_layers);
+  const double per_slot = (pool > 0.0 && peak_slots >= 4096.0) ? pool / peak_slots : estimate;
+  double budget = double(memory_budget);
+  if (memory_budget == 0) {
+    size_t free_b = 0, total_b = 0;
+    if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) free_b = total_b = size_t(64) << 30;
+    budget = std::min(double(free_b) + pool, double(total_b)) * 0.9;
+  }
+  const double cap = budget / per_slot;
+  const long max_atoms = max_batch_atoms > 0 ? max_batch_atoms : (1L << 40);
+  std::vector<std::pair<int, int>> runs;
+  int b0 = 0;
+  long atoms = 0;
+  double m = 0.0;
+  for (int i = 0; i < B; ++i) {
+    const long a = systems[i].n_atoms;
+    const double mi = std::max(m, neighbors_estimate(systems[i], h.cutoff));
+    if (i > b0 && (double(atoms + a) * (mi + 1.0) > cap || atoms + a > max_atoms)) {
+      runs.emplace_back(b0, i);
+      b0 = i, atoms = 0, m = 0.0;
+    }
+    atoms += a;
+    m = std::max(m, neighbors_estimate(systems[i], h.cutoff));
+  }
+  runs.emplace_back(b0, B);
+  return runs;
+}
+
+void Engine::compute_runs(const pet_system* systems, int B, const std::vector<std::pair<int, int>>& runs, bool forces,
+                          pet_results* out) {
+  if (runs.size() == 1) {
+    stage(systems, B, true);
+    compute_staged(forces);
+    fetch(out);
+    return;
+  }
+  // A batch too large for the device: consecutive pieces, the results in order, struct_id counted over the whole
+  // batch (Calculator::compute, src/calculator.cpp:589-624).
+  if (!out) throw Error(2, "pet: no results struct given");
+  ++batch_splits;
+  size_t a0 = 0;
+  for (const auto& run : runs) {
+    const int b0 = run.first, nb = run.second - run.first;
+    size_t na = 0;
+    for (int b = b0; b < run.second; ++b) na += size_t(systems[b].n_atoms);
+    stage(systems + b0, nb, false);
+    compute_staged(forces);
+    pet_results piece{};
+    piece.energy = out->energy ? out->energy + b0 : nullptr;
+    piece.per_atom_energy = out->per_atom_energy ? out->per_atom_energy + a0 : nullptr;
+    piece.forces = out->forces ? out->forces + 3 * a0 : nullptr;
+    piece.virial = out->virial ? out->virial + 6 * size_t(b0) : nullptr;
+    piece.struct_id = out->struct_id ? out->struct_id + a0 : nullptr;
+    fetch(&piece);
+    if (piece.struct_id && have_out)
+      for (size_t i = 0; i < na; ++i) piece.struct_id[i] += b0;
+    a0 += na;
+  }
+  last_B = B, last_N = int(a0);
+}
+
+// Out of device memory is recovered from where that can help (the reference drops a recompute tier, releases its
+// pool and retries, src/model.cpp:952-971): the pools are released, so that the next pass allocates one block of
+// the size it needs instead of growing in steps, and a batch is cut into pieces half the size; three rounds of
+// that, then the error goes to the caller with what the pools held.
 void Engine::compute(const pet_system* systems, int B, bool forces, pet_results* out) {
-  stage(systems, B, true);
-  compute_staged(forces);
-  fetch(out);
+  if (B < 0 || (B > 0 && !systems)) throw Error(2, "pet: no systems given");
+  for (int b = 0; b < B; ++b)
+    if (systems[b].n_atoms < 0) throw Error(2, "pet: negative atom count");
+  auto runs = B > 1 ? memory_runs(systems, B) : std::vector<std::pair<int, int>>{{0, B}};
+  for (int round = 0;; ++round) {
+    try {
+      compute_runs(systems, B, runs, forces, out);
+      return;
+    } catch (const Error& e) {
+      if (e.code != 4 || round == 3) {
+        if (e.code != 4) throw;
+        throw Error(4, std::string(e.what()) + " (pet: out of device memory after " + std::to_string(round) +
+                           " retries; the pools held " + std::to_string((save_arena.capacity() + tmp_arena.capacity() +
+                           nbr_arena.capacity()) >> 20) + " MiB, the batch was cut into " + std::to_string(runs.size()) +
+                           " pieces)");
+      }
+      cudaGetLastError();  // the failed allocation leaves its error behind
+      PETB_CUDA(cudaDeviceSynchronize());
+      drop_graphs();       // they replay into pool addresses
+      graph_seen.clear();
+      have_out = false, verlet.valid = false;
+      save_arena.release(), tmp_arena.release(), nbr_arena.release(), cache_arena.release();
+      ++oom_recoveries;
+      std::vector<std::pair<int, int>> halved;
+      for (const auto& r : runs) {
+        const int n = r.second - r.first;
+        if (n <= 1) {
+          halved.push_back(r);
+        } else {
+          halved.emplace_back(r.first, r.first + n / 2);
+          halved.emplace_back(r.first + n / 2, r.second);
+        }
+      }
+      runs = halved;
+    }
+  }
 }
 
 void Engine::neighbor_list(const pet_system* systems, int B, pet_raw_edges* out) {

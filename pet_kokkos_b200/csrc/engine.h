@@ -91,6 +91,16 @@ struct Engine {
   bool graphs = true;
   bool md_fixed = false;  // Options::md_fixed_shapes / PET_MD_FIXED
   bool cache_neighbors = false;  // Options::cache_neighbors / PET_CACHE_NEIGHBORS
+  size_t memory_budget = 0;      // Options::memory_budget_bytes; 0: what the device has
+  int max_batch_atoms = 0;       // Options::max_batch_atoms; 0: no limit
+  double peak_slots = 0.0;       // the most atoms x (neighbours + 1) one evaluation has held: samples bytes per slot
+  long long batch_splits = 0;    // batches evaluated as more than one piece
+  long long oom_recoveries = 0;  // evaluations retried after the device ran out of memory
+  void compute_runs(const pet_system* systems, int B, const std::vector<std::pair<int, int>>& runs, bool forces,
+                    pet_results* out);
+  // Consecutive runs of a batch, each at least one structure, whose estimated edge slots fit the memory budget and
+  // whose atoms fit max_batch_atoms (memory_runs, src/calculator.cpp:326-345).
+  std::vector<std::pair<int, int>> memory_runs(const pet_system* systems, int B) const;
   Stream st;
   Profiler prof;
   Checkpoint ckpt;

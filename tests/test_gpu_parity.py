@@ -201,3 +201,58 @@ def test_a_converted_model_with_extra_heads_loads_and_the_extras_are_ignored(mod
     ra, rb = a.compute(s), b.compute(s)
     assert ra.energy[0] == rb.energy[0] and np.array_equal(ra.forces, rb.forces) and np.array_equal(ra.virial, rb.virial)
     a.close(), b.close()
+
+
+def test_a_batch_split_to_fit_memory_gives_the_answer_of_the_whole_batch(models, lib_path):
+    """tests/test_determinism.cpp:116-162: compute() runs a batch too big for the device as consecutive pieces, by
+    max_batch_atoms and by a memory budget so small that every structure goes alone; the pieces come back in order,
+    struct_id counted over the whole batch, each structure as the whole batch had it (the native GEMMs are
+    batch-invariant and attention is per atom, so here to the bit)."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("tiny", "feedforward", "scaled", 2)
+    systems = [st.diamond(2, jitter=0.05, seed=1), st.water_box(9, 7.0, seed=2), st.diamond(1, jitter=0.02, seed=3),
+               st.random_mixture(30, 7.5, seed=4), st.diamond(2, jitter=0.04, seed=5), st.water_box(5, 6.0, seed=6)]
+    most = max(s["n_atoms"] for s in systems)
+    whole_calc = Calculator(jp, sp)
+    whole = whole_calc.compute(systems)
+    assert whole_calc.batch_splits == 0
+    for opts, pieces in ((dict(max_batch_atoms=2 * most), None), (dict(memory_budget_bytes=1), len(systems))):
+        c = Calculator(jp, sp, **opts)
+        split = c.compute(systems)
+        assert c.batch_splits == 1
+        assert split.n_atoms == whole.n_atoms and np.array_equal(split.struct_id, whole.struct_id)
+        assert np.array_equal(split.energy, whole.energy) and np.array_equal(split.per_atom_energy, whole.per_atom_energy)
+        assert np.array_equal(split.forces, whole.forces) and np.array_equal(split.virial, whole.virial)
+        energy_only = c.compute(systems, compute_forces=False)
+        assert np.array_equal(energy_only.energy, whole.energy)
+        assert c.compute(systems[:1]).energy[0] == whole.energy[0] and c.batch_splits == 2  # one structure is never split
+        c.close()
+    whole_calc.close()
+
+
+def test_out_of_memory_is_recovered_by_smaller_pieces(models, lib_path):
+    """The failure is made on the host (an allocation of the scratch pools reports out of memory once): the pools
+    are released, the batch cut in half and evaluated again, and the calculator stays usable."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("tiny", "feedforward", "scaled", 2)
+    systems = [st.diamond(2, jitter=0.05, seed=s) for s in range(4)]
+    c = Calculator(jp, sp)
+    whole = c.compute(systems)
+    big = [st.diamond(3, jitter=0.05, seed=s) for s in range(4)]  # larger: the pools have to grow
+    want = c.compute(big)
+    c.close()
+    c = Calculator(jp, sp)
+    c.fail_alloc(2)
+    got = c.compute(big)
+    assert c.oom_recoveries == 1 and c.batch_splits == 1
+    assert np.array_equal(got.energy, want.energy) and np.array_equal(got.forces, want.forces)
+    assert np.array_equal(got.struct_id, want.struct_id)
+    again = c.compute(systems)  # the calculator stays usable, graphs and pools rebuilt
+    assert np.array_equal(again.energy, whole.energy) and np.array_equal(again.forces, whole.forces)
+    one = Calculator(jp, sp)
+    one.fail_alloc(1)
+    r = one.compute(big[0])  # one structure cannot be cut: released pools, the same pass again
+    assert one.oom_recoveries == 1 and r.energy[0] == want.energy[0]
+    one.close()
+    c.fail_alloc(-1)
+    c.close()
