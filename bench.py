@@ -41,9 +41,10 @@ os.environ.setdefault("OMP_WAIT_POLICY", "passive")
 METRIC = "atom_evals_per_s"
 UNIT = "atom-evals/s"
 # DRAM traffic of one weight-GEMM launch per token row (atoms + kept edges), from one ncu capture:
-# dram__bytes_read.sum + dram__bytes_write.sum averaged over six consecutive k_gemm_tc launches of the water648
-# workload (35.5 MB at 25 320 rows). A GEMM reads A once and writes C once, so it grows with the rows.
-GEMM_DRAM_BYTES_PER_TOKEN_ROW = 35.5e6 / 25320
+# dram__bytes_read.sum + dram__bytes_write.sum averaged over seven consecutive k_gemm_tc launches of the water648
+# workload, token-row and atom-row GEMMs as they come (50.2 MB at 25 320 rows; profiles/k_gemm_tc_water648_s_3xtf32.md).
+# A GEMM reads A once and writes C once, so it grows with the rows.
+GEMM_DRAM_BYTES_PER_TOKEN_ROW = 50.2e6 / 25320
 MODEL_OF = {"diamond64": "xs", "water648": "s", "diamond1728": "s", "batch512x64": "s", "diamond13824": "l"}
 
 
