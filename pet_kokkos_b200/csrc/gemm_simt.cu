@@ -16,8 +16,22 @@ namespace {
 
 constexpr int BM = 128, BN = 128, BK = 16, PAD = 4;
 
+// Two fp32 values in one 64-bit register, and the packed fused multiply-add of sm_100: d.x = a.x * b.x + d.x and
+// d.y = a.y * b.y + d.y, each rounded once (round to nearest even), as fmaf does.
+__device__ __forceinline__ unsigned long long pack2(float x, float y) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& x, float& y) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
+}
+__device__ __forceinline__ void fma2(unsigned long long& d, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+
 template <int EPI>
-__global__ void __launch_bounds__(256) k_gemm_native(GemmArgs p) {
+__global__ void __launch_bounds__(256, 2) k_gemm_native(GemmArgs p) {
   __shared__ __align__(16) float As[2][BK][BM + PAD];
   __shared__ __align__(16) float Bs[2][BK][BN + PAD];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -44,11 +58,13 @@ __global__ void __launch_bounds__(256) k_gemm_native(GemmArgs p) {
     }
   };
 
-  float acc[8][8];
+  // The accumulators as pairs of neighbouring columns: one fma.rn.f32x2 advances two of them with the IEEE fp32
+  // fused multiply-add of the scalar instruction (same bits), for half the issue slots.
+  unsigned long long acc2[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+    for (int j = 0; j < 4; ++j) acc2[i][j] = 0ull;
 
   fetch(0);
   stash(0);
@@ -62,11 +78,13 @@ __global__ void __launch_bounds__(256) k_gemm_native(GemmArgs p) {
       const float4 a0 = ld4(&As[buf][k][ty * 4]), a1 = ld4(&As[buf][k][64 + ty * 4]);
       const float4 b0 = ld4(&Bs[buf][k][tx * 4]), b1 = ld4(&Bs[buf][k][64 + tx * 4]);
       const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      const unsigned long long b2[4] = {pack2(b0.x, b0.y), pack2(b0.z, b0.w), pack2(b1.x, b1.y), pack2(b1.z, b1.w)};
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < 8; ++i) {
+        const unsigned long long aa = pack2(a[i], a[i]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) fma2(acc2[i][j], aa, b2[j]);
+      }
     }
     if (more) {
       stash(buf ^ 1);
@@ -75,6 +93,11 @@ __global__ void __launch_bounds__(256) k_gemm_native(GemmArgs p) {
     }
   }
 
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) unpack2(acc2[i][j], acc[i][2 * j], acc[i][2 * j + 1]);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int row = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
