@@ -4,22 +4,26 @@
 // A persistent kernel, one CTA per SM, each walking 128 x BN tiles of C = A . B^T (A [M,K],
 // B [N,K], both K-major fp32) in an N-fastest order so that CTAs running side by side share
 // their A rows in L2. Roles, by warp:
-//   warp 0      producer: one thread issues cp.async.bulk.tensor (TMA) loads of a 128 x 32 slab
-//               of A and a BN x 32 slab of B per stage, 128-byte swizzled, landing on an mbarrier;
-//   warp 1      issuer: one thread issues tcgen05.mma kind::tf32 (M = 128, N = BN, K = 8) four
-//               times per stage into one of TWO accumulators in tensor memory, releases the stage
-//               with tcgen05.commit and hands the finished accumulator to the epilogue;
+//   warp 0      producer: one thread issues cp.async.bulk.tensor (TMA) loads of a 128 x BK slab
+//               of A and a BN x BK slab of B per stage, landing on an mbarrier. BK = 32 columns of K
+//               (128-byte swizzle), or 16 (64-byte swizzle) with twice the stages where that hides
+//               more of a TMA round trip (the 3xTF32 mode's 256-wide tiles);
+//   warp 1      issuer: one thread issues tcgen05.mma kind::tf32 (M = 128, N = BN, K = 8) for every
+//               8 columns of a stage into one of TWO accumulators in tensor memory, releases the
+//               stage with tcgen05.commit and hands the finished accumulator to the epilogue;
 //   warps 4-11  epilogue: tcgen05.ld the accumulator (a thread owns a row, a warp pair splits the
 //               columns), turn each 32 x 32 chunk through a per-warp shared-memory pad so that
 //               lanes run along columns, issue the epilogue's global loads for four row groups
 //               before consuming them, and write 16 bytes per lane. The accumulator is handed
 //               back as soon as it has been read, so the next tile's products overlap this
 //               tile's stores;
-//   warps 12-15 (3xTF32 mode) splitter: for every landed stage write lo = x - hi(x) beside the
-//               tiles, hi(x) being x with its 13 low mantissa bits cleared, which is what the
-//               tensor core reads of an fp32 operand. The issuer then accumulates
-//               hi.hi + hi.lo + lo.hi in fp32: fp32-class accuracy without reading the operands
-//               from L2 a second time.
+//   warps 12-15 (3xTF32 mode) splitter: for every landed stage write A's lo = x - hi(x) beside the
+//               tile, hi(x) being x with its 13 low mantissa bits cleared, which is what the
+//               tensor core reads of an fp32 operand (lo is rounded to tf32 by adding half of its
+//               last kept bit, since the tensor core would truncate it too). The weights' lo parts
+//               are computed once when the model is loaded and arrive by a third TMA map. The
+//               issuer accumulates hi.lo + lo.hi + hi.hi in fp32, small terms first: fp32-class
+//               accuracy without reading the activations from L2 a second time.
 // No TMA load here uses cluster multicast. Every wait is bounded: a wait that runs out sets an
 // error word the host checks, every role then leaves its loop, and the CTA still reaches its
 // tensor-memory release.
