@@ -71,6 +71,20 @@ struct EdgeListView {
   Exchange* exchange = nullptr;  // must outlive the list
 };
 
+// pet::DeviceEdgeListView (include/pet/device_geometry.hpp:113-135): device memory throughout, except cell.
+struct DeviceEdgeListView {
+  int n_atoms = 0, n_local = -1, n_centres = 0;
+  const int* ilist = nullptr;
+  const int* numneigh = nullptr;
+  const int* neighbors = nullptr;
+  long stride_i = 0, stride_k = 1;
+  int mask = ~0;
+  const int* atomic_numbers = nullptr;
+  const int* image_of = nullptr;
+  const double* positions = nullptr;
+  const double* cell = nullptr;
+};
+
 // pet::DevicePairListView (include/pet/device_geometry.hpp:137-154): device memory throughout.
 struct DevicePairListView {
   int n_atoms = 0, n_local = -1, n_pairs = 0;
@@ -185,6 +199,12 @@ class Calculator {
     return out;
   }
 
+  void set_neighbors(const DeviceEdgeListView& v) {
+    const pet_device_edge_list l{v.n_atoms, v.n_local,  v.n_centres, v.ilist,     v.numneigh, v.neighbors, v.stride_i,
+                                 v.stride_k, v.mask,    v.atomic_numbers, v.image_of, v.positions, v.cell, nullptr};
+    check(pet_set_neighbors_device(h_, &l));
+    atoms_ = v.n_atoms, pairs_ = 0;
+  }
   // An engine's flat pair list on the device, set and evaluated in one call (calculator.hpp:260-268).
   DeviceResults compute_pairs(const DevicePairListView& v, const double* positions, const double* cell = nullptr,
                               bool compute_forces = true) {

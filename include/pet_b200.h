@@ -126,6 +126,26 @@ typedef struct pet_totals {
   double virial[6];
 } pet_totals;
 
+/* pet::DeviceEdgeListView (include/pet/device_geometry.hpp:113-135): an engine's full list already in DEVICE
+ * memory (LAMMPS's KOKKOS package). Centre ilist[ii], ii < n_centres, has numneigh[i] neighbours
+ * neighbors[i * stride_i + k * stride_k] & mask (either layout of the engine's 2-D array; the mask drops the bits the
+ * engine keeps above the index). The pairs are taken in atom order, each atom's in list order. With image_of
+ * (periodic images instead of ghosts) a neighbour j becomes the owned atom image_of[j] and the lattice shift between
+ * them, worked out from positions and cell as they are at the call. Every pointer is device memory except cell. */
+typedef struct pet_device_edge_list {
+  int n_atoms, n_local, n_centres;
+  const int* ilist;
+  const int* numneigh;          /* indexed by atom */
+  const int* neighbors;
+  long stride_i, stride_k;      /* stride_k 0: 1 */
+  int mask;                     /* 0: all bits */
+  const int* atomic_numbers;    /* [n_atoms] */
+  const int* image_of;          /* [n_atoms], optional */
+  const double* positions;      /* [n_atoms * 3], with image_of */
+  const double* cell;           /* HOST [9], with image_of */
+  const pet_exchange* exchange; /* as pet_edge_list's */
+} pet_device_edge_list;
+
 /* pet::DevicePairListView (include/pet/device_geometry.hpp:137-154): an engine's pairs as a flat list in DEVICE
  * memory, in any order, as metatomic hands them over. Pair k is atom pairs[k * stride_pair] ->
  * pairs[k * stride_pair + stride_col], shifted by the next three columns (lattice vectors, as pet_edge_list's
@@ -194,6 +214,9 @@ int pet_compute_step(pet_calc* c, const double* positions, const double* cell, i
                      int edge_gradients, pet_results* out);
 /* Calculator::compute_step(const DeviceArrays&, cell) (calculator.hpp:259). */
 int pet_compute_step_device(pet_calc* c, const pet_device_arrays* arrays, const double* cell, pet_totals* totals);
+/* Calculator::set_neighbors(const DeviceEdgeListView&) (calculator.hpp:236): the list is set once, then stepped
+ * with pet_compute_step / pet_compute_step_device. */
+int pet_set_neighbors_device(pet_calc* c, const pet_device_edge_list* list);
 /* Calculator::compute_pairs (calculator.hpp:260-268): a flat pair list set and evaluated in one call. positions
  * [n_atoms * 3] is device memory in the engine's order, cell [9] host memory (needed with shifts). The results stay
  * on the device (pet_fetch_results copies them out), in the list's numbering. It replaces any list

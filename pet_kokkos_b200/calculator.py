@@ -60,6 +60,13 @@ class PetDeviceArrays(C.Structure):
                 ("per_atom_virial", C.c_void_p), ("virial_scale", C.c_double)]
 
 
+class PetDeviceEdgeList(C.Structure):
+    _fields_ = [("n_atoms", C.c_int), ("n_local", C.c_int), ("n_centres", C.c_int), ("ilist", C.c_void_p),
+                ("numneigh", C.c_void_p), ("neighbors", C.c_void_p), ("stride_i", C.c_long), ("stride_k", C.c_long),
+                ("mask", C.c_int), ("atomic_numbers", C.c_void_p), ("image_of", C.c_void_p), ("positions", C.c_void_p),
+                ("cell", C.POINTER(C.c_double)), ("exchange", C.c_void_p)]
+
+
 class PetPairList(C.Structure):
     _fields_ = [("n_atoms", C.c_int), ("n_local", C.c_int), ("n_pairs", C.c_int), ("pairs", C.c_void_p),
                 ("stride_pair", C.c_long), ("stride_col", C.c_long), ("atomic_numbers", C.c_void_p),
@@ -101,6 +108,7 @@ SIGNATURES = {
     "pet_set_neighbors": (C.c_int, [C.c_void_p, _P(PetEdgeList)]),
     "pet_compute_step": (C.c_int, [C.c_void_p, _P(C.c_double), _P(C.c_double), C.c_int, C.c_int, _P(PetResults)]),
     "pet_compute_step_device": (C.c_int, [C.c_void_p, _P(PetDeviceArrays), _P(C.c_double), _P(PetTotals)]),
+    "pet_set_neighbors_device": (C.c_int, [C.c_void_p, _P(PetDeviceEdgeList)]),
     "pet_compute_pairs": (C.c_int, [C.c_void_p, _P(PetPairList), C.c_void_p, _P(C.c_double), C.c_int,
                                     _P(PetDeviceResults)]),
     "pet_neighbor_list": (C.c_int, [C.c_void_p, _P(PetSystem), C.c_int, _P(PetRawEdges)]),
@@ -440,6 +448,17 @@ class Calculator:
         t = PetTotals()
         self._check(self._lib.pet_compute_step_device(self._h, C.byref(a), None if c is None else _dptr(c), C.byref(t)))
         return t.energy, np.array(list(t.virial))
+
+    def set_neighbors_device(self, n_atoms, n_centres, ilist_ptr, numneigh_ptr, neighbors_ptr, stride_i, atomic_numbers_ptr,
+                             stride_k=1, mask=0, n_local=-1, image_of_ptr=0, positions_ptr=0, cell=None):
+        """Calculator::set_neighbors(const DeviceEdgeListView&) (calculator.hpp:236): an engine's full list in device
+        memory (LAMMPS's KOKKOS layout). Pointers are device addresses as integers; cell is host memory."""
+        c = None if cell is None else np.ascontiguousarray(cell, dtype=np.float64).reshape(9)
+        v = PetDeviceEdgeList(n_atoms, n_local, n_centres, ilist_ptr or None, numneigh_ptr or None, neighbors_ptr or None,
+                              stride_i, stride_k, mask, atomic_numbers_ptr or None, image_of_ptr or None, positions_ptr or None,
+                              None if c is None else _dptr(c), None)
+        self._check(self._lib.pet_set_neighbors_device(self._h, C.byref(v)))
+        self._session_atoms, self._session_pairs = n_atoms, 0
 
     def compute_pairs(self, n_atoms, n_pairs, pairs_ptr, atomic_numbers_ptr, positions_ptr, cell=None, renumber_ptr=0,
                       n_local=-1, stride_pair=5, stride_col=1, compute_forces=True, fetch=True):

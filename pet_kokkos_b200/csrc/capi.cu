@@ -102,6 +102,9 @@ int pet_compute_step(pet_calc* c, const double* positions, const double* cell, i
 int pet_compute_step_device(pet_calc* c, const pet_device_arrays* arrays, const double* cell, pet_totals* totals) {
   return guarded(c, [&](Engine& e) { e.compute_step_device(arrays, cell, totals); });
 }
+int pet_set_neighbors_device(pet_calc* c, const pet_device_edge_list* list) {
+  return guarded(c, [&](Engine& e) { e.set_neighbors_device(list); });
+}
 int pet_compute_pairs(pet_calc* c, const pet_pair_list* pairs, const double* positions, const double* cell, int forces,
                       pet_device_results* out) {
   return guarded(c, [&](Engine& e) { e.compute_pairs(pairs, positions, cell, forces != 0, out); });

@@ -61,6 +61,15 @@ __global__ void k_dense_pairs(int* __restrict__ out, const int* __restrict__ pai
   out[t] = pairs[(t / 5) * sp + (t % 5) * sc];
 }
 
+// An engine's 2-D neighbour array into a dense list: centre ii's neighbours at out[off[ii] ...], index bits only.
+__global__ void k_dense_neighbors(int* __restrict__ out, const int* __restrict__ ilist, const int* __restrict__ off,
+                                  const int* __restrict__ nbr, long si, long sk, int mask, int NC) {
+  const int ii = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (ii >= NC) return;
+  const int i = ilist[ii], e0 = off[ii], n = off[ii + 1] - e0;
+  for (int k = lane; k < n; k += 32) out[e0 + k] = nbr[i * si + k * sk] & mask;
+}
+
 // The engine's positions into the list's numbering.
 __global__ void k_renumber_positions(double* __restrict__ out, const double* __restrict__ x, const int* __restrict__ ren, int N) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -894,6 +903,82 @@ void Engine::compute_step_device(const pet_device_arrays* a, const double* cell,
     break;
   }
   if (totals) *totals = t;
+}
+
+// An engine's full list in device memory (EdgeSession::set(DeviceEdgeListView), src/device_geometry.cpp:456-545).
+// As for the flat pair list, the list comes to the host once per set (the counts first, then the neighbours
+// gathered dense by a kernel) and goes through the host list's path; every step stays on the device.
+void Engine::set_neighbors_device(const pet_device_edge_list* v) {
+  PETB_CUDA(cudaSetDevice(device));
+  if (!v || v->n_atoms < 0 || v->n_centres < 0) throw Error(2, "pet: no edge list given");
+  const int N = v->n_atoms, NC = v->n_centres;
+  if (N > 0 && !v->atomic_numbers) throw Error(2, "pet: an edge list needs atomic numbers");
+  if (NC > 0 && (!v->ilist || !v->numneigh || !v->neighbors)) throw Error(2, "pet: an edge list needs ilist, numneigh and neighbors");
+  if (N >= (1 << 24)) throw Error(1, "pet: too many atoms for the edge key");
+  if (v->image_of && (!v->cell || !v->positions)) throw Error(1, "pet: images need the positions and the cell");
+  const long si = v->stride_i, sk = v->stride_k ? v->stride_k : 1;
+  const int mask = v->mask ? v->mask : ~0;
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  tmp_arena.reset();
+  std::vector<int> ilist(NC), numneigh(N), z(N), image(v->image_of ? N : 0);
+  std::vector<double> x(v->image_of ? 3 * size_t(N) : 0);
+  if (NC) PETB_CUDA(cudaMemcpyAsync(ilist.data(), v->ilist, 4 * size_t(NC), cudaMemcpyDeviceToHost, st.s));
+  if (N) {
+    PETB_CUDA(cudaMemcpyAsync(numneigh.data(), v->numneigh, 4 * size_t(N), cudaMemcpyDeviceToHost, st.s));
+    PETB_CUDA(cudaMemcpyAsync(z.data(), v->atomic_numbers, 4 * size_t(N), cudaMemcpyDeviceToHost, st.s));
+    if (v->image_of) {
+      PETB_CUDA(cudaMemcpyAsync(image.data(), v->image_of, 4 * size_t(N), cudaMemcpyDeviceToHost, st.s));
+      PETB_CUDA(cudaMemcpyAsync(x.data(), v->positions, 24 * size_t(N), cudaMemcpyDeviceToHost, st.s));
+    }
+  }
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  // the centres' counts, in ilist order for the gather and in atom order for the list
+  std::vector<int> coff(size_t(NC) + 1, 0), off(size_t(N) + 1, 0);
+  for (int ii = 0; ii < NC; ++ii) {
+    const int i = ilist[ii];
+    if (i < 0 || i >= N || numneigh[i] < 0) throw Error(2, "pet: a centre of the list is not one of its atoms");
+    coff[ii + 1] = coff[ii] + numneigh[i];
+    off[i + 1] = numneigh[i];
+  }
+  for (int i = 0; i < N; ++i) off[i + 1] += off[i];
+  const int E = off[N];
+  if (E != coff[NC]) throw Error(2, "pet: a centre is listed twice");
+  std::vector<int> dense(E), nb(E), sh;
+  if (E) {
+    int* d_off = tmp_arena.alloc<int>(size_t(NC) + 1);
+    int* d_dense = tmp_arena.alloc<int>(E);
+    PETB_CUDA(cudaMemcpyAsync(d_off, coff.data(), 4 * (size_t(NC) + 1), cudaMemcpyHostToDevice, st.s));
+    k_dense_neighbors<<<cdiv(size_t(NC) * 32, 256), 256, 0, st.s>>>(d_dense, v->ilist, d_off, v->neighbors, si, sk, mask, NC);
+    PETB_LAUNCH_CHECK(st);
+    PETB_CUDA(cudaMemcpyAsync(dense.data(), d_dense, 4 * size_t(E), cudaMemcpyDeviceToHost, st.s));
+    PETB_CUDA(cudaStreamSynchronize(st.s));
+  }
+  for (int ii = 0; ii < NC; ++ii)  // ilist order -> atom order
+    std::copy(dense.begin() + coff[ii], dense.begin() + coff[ii + 1], nb.begin() + off[ilist[ii]]);
+  for (int e = 0; e < E; ++e)
+    if (nb[e] < 0 || nb[e] >= N) throw Error(2, "pet: a neighbour index is out of range");
+  if (v->image_of) {  // each neighbour becomes the owned atom it is an image of, with the shift between them
+    double inv[9];
+    invert_cell(v->cell, inv);
+    const double* c = v->cell;
+    const double det = c[0] * (c[4] * c[8] - c[5] * c[7]) - c[1] * (c[3] * c[8] - c[5] * c[6]) + c[2] * (c[3] * c[7] - c[4] * c[6]);
+    if (std::fabs(det) < 1e-12) throw Error(1, "pet: images need a cell with volume");
+    sh.assign(3 * size_t(E), 0);
+    for (int e = 0; e < E; ++e) {
+      const int j = nb[e], o = image[j];
+      if (o < 0 || o >= N) throw Error(1, "pet: a neighbour is not an image of an owned atom");
+      const double d0 = x[3 * size_t(j)] - x[3 * size_t(o)], d1 = x[3 * size_t(j) + 1] - x[3 * size_t(o) + 1],
+                   d2 = x[3 * size_t(j) + 2] - x[3 * size_t(o) + 2];
+      for (int d = 0; d < 3; ++d) sh[3 * size_t(e) + d] = int(std::lround(d0 * inv[d] + d1 * inv[3 + d] + d2 * inv[6 + d]));
+      nb[e] = o;
+    }
+  }
+  pet_edge_list list{};
+  list.n_atoms = N, list.n_local = v->n_local;
+  list.atomic_numbers = z.data(), list.offsets = off.data(), list.neighbors = nb.data();
+  list.shifts = v->image_of ? sh.data() : nullptr;
+  list.cell = v->cell, list.half = 0, list.exchange = v->exchange;
+  set_neighbors(&list);
 }
 
 // An engine's pairs as a flat device list (EdgeSession::set(DevicePairListView), src/device_geometry.cpp:547-669;

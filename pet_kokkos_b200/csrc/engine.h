@@ -79,6 +79,7 @@ struct Engine {
   void set_neighbors(const pet_edge_list* list);
   void compute_step(const double* positions, const double* cell, bool forces, bool edge_gradients, pet_results* out);
   void compute_step_device(const pet_device_arrays* arrays, const double* cell, pet_totals* totals);
+  void set_neighbors_device(const pet_device_edge_list* list);
   void compute_pairs(const pet_pair_list* pairs, const double* positions, const double* cell, bool forces,
                      pet_device_results* out);
   void debug_fetch(const char* name, float* out, size_t capacity, size_t* n);

@@ -299,3 +299,83 @@ def test_flat_pair_list_errors(calc):
     calc.compute_pairs(n, P, t_pairs.data_ptr(), t_z.data_ptr(), t_x.data_ptr(), cell=s["cell"], renumber_ptr=ident.data_ptr())
     with pytest.raises(RuntimeError, match="takes device positions"):
         calc.compute_step(s["positions"], s["cell"])
+
+
+@pytest.mark.parametrize("layout", ["rows", "columns"])
+def test_device_list_gets_the_bits_of_the_host_list(calc, layout):
+    """tests/test_edges.cpp:528-587: the engine's 2-D neighbour array in device memory (either layout, the engine's
+    flag bits above the index masked off, centres listed out of order) gives what the same list gives from the host."""
+    import torch
+    s = st.diamond(2, jitter=0.05, seed=31)
+    n = s["n_atoms"]
+    # a cluster's list: no shifts, so ghosts are not needed
+    c = st.make_system(s["atomic_numbers"], s["positions"], np.eye(3) * 60.0, pbc=(False, False, False))
+    v = full_list(c, calc.cutoff, skin=0.4)
+    calc.set_neighbors(v)
+    ref = calc.compute_step(c["positions"], c["cell"])  # the host list carries (zero) shifts
+    off = np.asarray(v.offsets)
+    counts = np.diff(off)
+    M = int(counts.max())
+    table = np.zeros((n, M), np.int32)
+    for i in range(n):
+        table[i, :counts[i]] = np.asarray(v.neighbors)[off[i]:off[i + 1]] | (1 << 30)  # a flag bit above the index
+    dev = "cuda:0"
+    ilist = np.random.default_rng(0).permutation(n).astype(np.int32)
+    if layout == "rows":
+        t_tab, si, sk = torch.tensor(table, device=dev), M, 1
+    else:
+        t_tab, si, sk = torch.tensor(np.ascontiguousarray(table.T), device=dev), 1, n
+    t_il, t_nn = torch.tensor(ilist, device=dev), torch.tensor(counts.astype(np.int32), device=dev)
+    t_z = torch.tensor(np.asarray(c["atomic_numbers"], np.int32), device=dev)
+    torch.cuda.synchronize()
+    calc.set_neighbors_device(n, n, t_il.data_ptr(), t_nn.data_ptr(), t_tab.data_ptr(), si, t_z.data_ptr(), stride_k=sk,
+                              mask=(1 << 30) - 1)
+    got = calc.compute_step(c["positions"])
+    assert got.energy[0] == ref.energy[0] and np.array_equal(got.forces, ref.forces) and np.array_equal(got.virial, ref.virial)
+
+
+def test_device_list_with_images_equals_the_periodic_list(calc):
+    """Periodic images instead of ghosts (include/pet/device_geometry.hpp:109-111): every neighbour is replaced by the
+    owned atom it is an image of and the lattice shift between them, which is the periodic list with shifts."""
+    import torch
+    s = st.diamond(2, jitter=0.05, seed=32)
+    n = s["n_atoms"]
+    v = full_list(s, calc.cutoff, skin=0.3)
+    ref = calc.compute_edges(v, True, False)
+    off, nbr, sh = np.asarray(v.offsets), np.asarray(v.neighbors), np.asarray(v.shifts)
+    # one image atom per distinct (atom, shift != 0)
+    keys = {}
+    image_of, pos = list(range(n)), [p for p in s["positions"]]
+    nb2 = np.empty_like(nbr)
+    for e in range(len(nbr)):
+        k = (int(nbr[e]), *map(int, sh[e]))
+        if not any(k[1:]):
+            nb2[e] = nbr[e]
+            continue
+        if k not in keys:
+            keys[k] = len(image_of)
+            image_of.append(k[0])
+            pos.append(s["positions"][k[0]] + sh[e] @ s["cell"])
+        nb2[e] = keys[k]
+    na = len(image_of)
+    counts = np.concatenate([np.diff(off), np.zeros(na - n, np.int64)]).astype(np.int32)
+    M = int(counts.max())
+    table = np.zeros((na, M), np.int32)
+    for i in range(n):
+        table[i, :counts[i]] = nb2[off[i]:off[i + 1]]
+    z = np.asarray(s["atomic_numbers"], np.int32)[np.array(image_of)]
+    dev = "cuda:0"
+    t = {k: torch.tensor(a, device=dev) for k, a in dict(il=np.arange(n, dtype=np.int32), nn=counts, tab=table, z=z,
+                                                           im=np.array(image_of, np.int32), x=np.array(pos)).items()}
+    torch.cuda.synchronize()
+    calc.set_neighbors_device(na, n, t["il"].data_ptr(), t["nn"].data_ptr(), t["tab"].data_ptr(), M, t["z"].data_ptr(),
+                              n_local=n, image_of_ptr=t["im"].data_ptr(), positions_ptr=t["x"].data_ptr(), cell=s["cell"])
+    got = calc.compute_step(np.array(pos), s["cell"])
+    assert abs(got.energy[0] - ref.energy[0]) <= 1e-9 * abs(ref.energy[0])
+    assert np.abs(got.forces[:n] - ref.forces).max() <= 1e-9 * max(1.0, np.abs(ref.forces).max())
+    assert np.abs(got.forces[n:]).max() == 0.0  # the images carry no pairs and no force
+    assert np.abs(got.virial - ref.virial).max() <= 1e-9 * max(1.0, np.abs(ref.virial).max())
+    bad = torch.tensor(np.full(na, -1, np.int32), device=dev)
+    with pytest.raises(RuntimeError, match="not an image of an owned atom"):
+        calc.set_neighbors_device(na, n, t["il"].data_ptr(), t["nn"].data_ptr(), t["tab"].data_ptr(), M, t["z"].data_ptr(),
+                                  n_local=n, image_of_ptr=bad.data_ptr(), positions_ptr=t["x"].data_ptr(), cell=s["cell"])
