@@ -306,7 +306,15 @@ void Engine::run_model(const PackedEdges& pk, bool forces) {
                                      ptr(pk.off),          ptr(pk.center),     ptr(pk.species),      ptr(pk.reverse),
                                      ptr(pk.vec),          ptr(pk.dist),       ptr(pk.cut),          ptr(pk.atom_species),
                                      ptr(pk.soff),         save_arena.generation(), tmp_arena.generation(),
-                                     ptr(save_arena.alloc_bytes(0))};
+                                     ptr(save_arena.alloc_bytes(0)),
+                                     // the rest of what the recorded kernels read: the neighbour atoms, the maps between
+                                     // packed and raw edges, and an adaptive cutoff's per-atom data and raw list
+                                     ptr(pk.nbr),          ptr(pk.rc),         ptr(pk.raw_of),       ptr(pk.packed_of_raw),
+                                     ptr(pk.sid),          ptr(pk.adaptive.acut), ptr(pk.adaptive.root), ptr(pk.adaptive.slope),
+                                     ptr(pk.adaptive.eff), ptr(pk.adaptive.probes), uint64_t(pk.adaptive.P),
+                                     uint64_t(pk.adaptive.n_atoms), uint64_t(pk.adaptive.raw.E), ptr(pk.adaptive.raw.i),
+                                     ptr(pk.adaptive.raw.j), ptr(pk.adaptive.raw.vec), ptr(pk.adaptive.raw.dist),
+                                     ptr(pk.adaptive.raw.off), ptr(pk.adaptive.raw.reverse)};
   for (auto& g : graph_cache)
     if (g.key == key) {
       PETB_CUDA(cudaGraphLaunch(g.exec, st.s));

@@ -379,3 +379,27 @@ def test_device_list_with_images_equals_the_periodic_list(calc):
     with pytest.raises(RuntimeError, match="not an image of an owned atom"):
         calc.set_neighbors_device(na, n, t["il"].data_ptr(), t["nn"].data_ptr(), t["tab"].data_ptr(), M, t["z"].data_ptr(),
                                   n_local=n, image_of_ptr=bad.data_ptr(), positions_ptr=t["x"].data_ptr(), cell=s["cell"])
+
+
+def test_recorded_passes_follow_the_list_they_were_recorded_for(tmp_path):
+    """An adaptive cutoff's backward reads the raw list as well as the packed edges. Two lists of the same atoms
+    with different skins keep the same edges (same packed shapes) from raw lists of different sizes: a pass
+    recorded for one must not be replayed for the other."""
+    from pet_kokkos_b200 import Calculator, checkpoint as ck
+    jp, sp = ck.write_random_checkpoint(tmp_path / "ad", "tiny", "feedforward", seed=5, init="scaled",
+                                        num_neighbors_adaptive=16.0, adaptive_cutoff_method="solver", cutoff=5.5)
+    c = Calculator(jp, sp)
+    s = st.diamond(2, jitter=0.08, seed=1)
+    want = {}
+    for skin in (0.2, 0.9):
+        fresh = Calculator(jp, sp, graphs=False)
+        want[skin] = fresh.compute_edges(full_list(s, fresh.cutoff, skin=skin), True, False)
+        fresh.close()
+    for skin in (0.2, 0.9, 0.2, 0.9):
+        c.set_neighbors(full_list(s, c.cutoff, skin=skin))
+        for _ in range(3):  # eager, recorded, replayed
+            r = c.compute_step(s["positions"], s["cell"])
+            assert r.energy[0] == want[skin].energy[0] and np.array_equal(r.forces, want[skin].forces)
+            assert np.array_equal(r.virial, want[skin].virial)
+    assert c.graph_replays >= 4
+    c.close()
