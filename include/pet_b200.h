@@ -43,8 +43,8 @@ enum {
 enum { PET_GEMM_NATIVE = 0, PET_GEMM_TF32 = 1, PET_GEMM_BF16 = 2, PET_GEMM_TF32X3 = 3 };
 
 /* pet::Options (calculator.hpp:32-117), the subset this path uses. A negative
- * value means "unset": environment (PET_GEMM, PET_GRAPHS, PET_DEVICE_SEARCH)
- * then the default. */
+ * value means "unset": environment (PET_GEMM, PET_GRAPHS, PET_MD_FIXED) then the
+ * default. */
 typedef struct pet_options {
   int device;               /* CUDA device ordinal; -1: the current device          */
   int gemm_mode;            /* PET_GEMM_*; -1 unset (default native fp32)             */
@@ -86,7 +86,8 @@ typedef struct pet_results {
  * calculator's cudaStream_t. A callback either enqueues its transfers on that stream (NCCL send/recv, peer
  * copies) or synchronizes it, does the transfer its own way and returns once `in` is filled. Every rank makes the
  * same sequence of calls, also with n_live = 0. Return 0, or non-zero to fail the evaluation.
- * (atoms_forward / atoms_reverse of the reference serve the adaptive cutoff, which this path does not have.) */
+ * (atoms_forward / atoms_reverse of the reference move per-atom values for the adaptive cutoff and D3; they are not
+ * part of these callbacks, and an adaptive-cutoff model over an exchange is refused.) */
 typedef struct pet_exchange {
   void* user;
   /* Exchange::set_live: once per evaluation, the kept edges to ghosts: live[n_live], ascending indices into the
@@ -250,8 +251,6 @@ long long pet_kernel_launches(const pet_calc* c);
 /* Evaluations served by replaying a recorded CUDA graph (Options::graphs; the reference's GraphCache,
  * include/pet/graph.hpp:68-146: eager first, capture second, replay after). */
 long long pet_graph_replays(const pet_calc* c);
-/* Neighbour searches run for staged batches under Options::cache_neighbors, and the evaluations the cached
- * pairs served instead (the reference's NefCache, include/pet/device_geometry.hpp:198-228). */
 /* Batches that pet_compute ran as several consecutive pieces to fit Options::memory_budget_bytes /
  * Options::max_batch_atoms (src/calculator.cpp:326-345). */
 long long pet_batch_splits(const pet_calc* c);
@@ -260,6 +259,8 @@ long long pet_batch_splits(const pet_calc* c);
  * device allocation of the scratch pools from now (0 = the next) reports out of memory once; k < 0 disarms. */
 long long pet_oom_recoveries(const pet_calc* c);
 void pet_debug_fail_alloc(long k);
+/* Neighbour searches run for staged batches under Options::cache_neighbors, and the evaluations the cached
+ * pairs served instead (the reference's NefCache, include/pet/device_geometry.hpp:198-228). */
 long long pet_neighbor_searches(const pet_calc* c);
 long long pet_neighbor_reuses(const pet_calc* c);
 double pet_last_device_ms(const pet_calc* c);
@@ -291,16 +292,19 @@ int pet_gemm_host(pet_calc* c, int mode, int w_transposed, int m, int n, int k, 
 /* C[m,n] = A[m,k] . W^T, W [n,k], fp32 on the CUDA cores, on host arrays, WITHOUT allocating
  * device memory. It has no counterpart in the reference. It exists for callers that cannot
  * call cudaMalloc: plug-ins of a host program that owns all device memory through its own
- * pool, code that runs while a stream of the process is being captured, loops that may not
- * take the driver's allocation lock. Operands are staged in a fixed 12 MiB array inside the
- * library image (resident on every GPU that loads the library until the process exits), on
- * the current device and its default stream. Limits and rules:
+ * pool, code that runs while another thread of the process has a stream capture open (where
+ * cudaMalloc is an error), loops that may not take the driver's allocation lock. Operands are
+ * staged in a fixed 12 MiB array inside the library image (resident on every GPU that loads the
+ * library until the process exits), on the current device; the copies and the kernel run on the
+ * calling thread's own stream (cudaStreamPerThread), which the call waits for before it returns.
+ * Limits and rules:
  *   - round64(m*k) + round64(n*k) + round64(m*n) floats must fit 3 Mi floats, n % 4 == 0 and
  *     k % 4 == 0; a larger problem is refused with PET_ERR_INVALID and a message in errbuf;
  *   - the first call on each device resolves the array's device address (cudaGetSymbolAddress):
  *     make that first call before any stream capture starts;
  *   - every call uses the same array, which keeps the previous call's contents (the kernel
- *     overwrites all of C, so nothing needs clearing); calls that overlap on one GPU race.
+ *     overwrites all of C, so nothing needs clearing); calls that overlap on one GPU (two host
+ *     threads) race.
  * errbuf (optional) receives the message of a failure. */
 int pet_gemm_host_static(int m, int n, int k, const float* A, const float* W, float* C, char* errbuf, size_t errbuf_len);
 

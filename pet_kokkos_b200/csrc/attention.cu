@@ -197,14 +197,11 @@ __global__ void __launch_bounds__(256) k_attn_bwd(AttnArgs p) {
 }
 
 template <class K>
-void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, int* opted) {
+void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, SmemOptIn& opted) {
   if (int(bytes) > 227 * 1024)
     throw Error(1, "attention: an atom with " + std::to_string(p.S - 1) + " neighbours needs " + std::to_string(bytes) +
                        " bytes of shared memory per block, above the device's 227 KiB");
-  if (int(bytes) > *opted) {
-    PETB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
-    *opted = int(bytes);
-  }
+  opt_in_shared_memory(kernel, bytes, opted);
   int threads = (p.S + 31) / 32 * 32;
   if (threads > 256) threads = 256;
   kernel<<<p.N * p.H, threads, bytes, st.s>>>(p);
@@ -213,13 +210,13 @@ void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, int* opted) {
 
 template <int HD>
 void fwd_hd(Stream& st, const AttnArgs& p) {
-  static int opted = 48 * 1024;
-  launch(st, k_attn_fwd<HD>, p, sizeof(float) * (2 * size_t(p.S) * HD + p.S), &opted);
+  static SmemOptIn opted;
+  launch(st, k_attn_fwd<HD>, p, sizeof(float) * (2 * size_t(p.S) * HD + p.S), opted);
 }
 template <int HD>
 void bwd_hd(Stream& st, const AttnArgs& p) {
-  static int opted = 48 * 1024;
-  launch(st, k_attn_bwd<HD>, p, sizeof(float) * (4 * size_t(p.S) * HD + 4 * size_t(p.S)), &opted);
+  static SmemOptIn opted;
+  launch(st, k_attn_bwd<HD>, p, sizeof(float) * (4 * size_t(p.S) * HD + 4 * size_t(p.S)), opted);
 }
 
 }  // namespace

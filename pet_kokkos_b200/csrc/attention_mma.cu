@@ -394,11 +394,8 @@ size_t bwd_bytes(int S, int HD) {
 }
 
 template <class K>
-void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, int threads, int* opted) {
-  if (int(bytes) > *opted) {
-    PETB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
-    *opted = int(bytes);
-  }
+void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, int threads, SmemOptIn& opted) {
+  opt_in_shared_memory(kernel, bytes, opted);
   kernel<<<p.N * p.H, threads, bytes, st.s>>>(p);
   PETB_LAUNCH_CHECK(st);
 }
@@ -407,10 +404,10 @@ template <int HD>
 bool fwd_hd(Stream& st, const AttnArgs& p) {
   const int S16 = round16(p.S), threads = 32 * (S16 / 16);
   if (S16 > 176 || fwd_bytes(22, HD) > 200 * 1024) return false;
-  static int o10 = 48 * 1024, o16 = 48 * 1024, o22 = 48 * 1024;
-  if (S16 <= 80) launch(st, k_attn_fwd_mma<HD, 10>, p, fwd_bytes(10, HD), threads, &o10);
-  else if (S16 <= 128) launch(st, k_attn_fwd_mma<HD, 16>, p, fwd_bytes(16, HD), threads, &o16);
-  else launch(st, k_attn_fwd_mma<HD, 22>, p, fwd_bytes(22, HD), threads, &o22);
+  static SmemOptIn o10, o16, o22;
+  if (S16 <= 80) launch(st, k_attn_fwd_mma<HD, 10>, p, fwd_bytes(10, HD), threads, o10);
+  else if (S16 <= 128) launch(st, k_attn_fwd_mma<HD, 16>, p, fwd_bytes(16, HD), threads, o16);
+  else launch(st, k_attn_fwd_mma<HD, 22>, p, fwd_bytes(22, HD), threads, o22);
   return true;
 }
 template <int HD>
@@ -420,9 +417,9 @@ bool bwd_hd(Stream& st, const AttnArgs& p) {
   if (threads > 512) threads = 512;
   const size_t bytes = bwd_bytes(p.S, HD);
   if (bytes > 200 * 1024) return false;
-  static int o320 = 48 * 1024, o512 = 48 * 1024;
-  if (threads <= 320) launch(st, k_attn_bwd_mma<HD, 320>, p, bytes, threads, &o320);
-  else launch(st, k_attn_bwd_mma<HD, 512>, p, bytes, threads, &o512);
+  static SmemOptIn o320, o512;
+  if (threads <= 320) launch(st, k_attn_bwd_mma<HD, 320>, p, bytes, threads, o320);
+  else launch(st, k_attn_bwd_mma<HD, 512>, p, bytes, threads, o512);
   return true;
 }
 

@@ -329,24 +329,21 @@ size_t bwd_bytes(int S, int HD) {
 }
 
 template <class K>
-void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, int* opted) {
-  if (int(bytes) > *opted) {
-    PETB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
-    *opted = int(bytes);
-  }
+void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, SmemOptIn& opted) {
+  opt_in_shared_memory(kernel, bytes, opted);
   kernel<<<p.N * p.H, 192, bytes, st.s>>>(p);
   PETB_LAUNCH_CHECK(st);
 }
 
 template <int HD>
 void fwd_hd(Stream& st, const AttnArgs& p) {
-  static int opted = 48 * 1024;
-  launch(st, k_attn_fwd_tile<HD>, p, fwd_bytes(p.S, HD), &opted);
+  static SmemOptIn opted;
+  launch(st, k_attn_fwd_tile<HD>, p, fwd_bytes(p.S, HD), opted);
 }
 template <int HD>
 void bwd_hd(Stream& st, const AttnArgs& p) {
-  static int opted = 48 * 1024;
-  launch(st, k_attn_bwd_tile<HD>, p, bwd_bytes(p.S, HD), &opted);
+  static SmemOptIn opted;
+  launch(st, k_attn_bwd_tile<HD>, p, bwd_bytes(p.S, HD), opted);
 }
 
 }  // namespace

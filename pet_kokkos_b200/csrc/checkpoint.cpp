@@ -189,8 +189,9 @@ Checkpoint::Checkpoint(const std::string& json_path, const std::string& safetens
     if (h.bool_or("system_conditioning", false))
       throw Error(1, "checkpoint: system_conditioning models are outside this evaluator's scope");
     if (p.adaptive()) {
-      p.adaptive_solver = !choose("adaptive_cutoff_method", h.at("adaptive_cutoff_method").string(), "grid", "solver");
-      p.cutoff_width_adaptive = h.number_or("cutoff_width_adaptive", 0.5);
+      // older adaptive checkpoints carry neither key: the grid scheme and the plain taper width (src/checkpoint.cpp:91-95)
+      p.adaptive_solver = !choose("adaptive_cutoff_method", h.string_or("adaptive_cutoff_method", "grid"), "grid", "solver");
+      p.cutoff_width_adaptive = h.number_or("cutoff_width_adaptive", p.cutoff_width);
       // as the reference (src/model.cpp): the adaptive cutoff is implemented for the feedforward featurizer
       if (!p.feedforward) throw Error(1, "checkpoint: the residual featurizer with an adaptive cutoff is not implemented");
     }

@@ -11,6 +11,8 @@
 #include <string>
 #include <vector>
 
+#include "per_device.h"
+
 namespace petb {
 
 // An error that crosses the C ABI as a status code plus a message.
@@ -200,5 +202,19 @@ struct ProfScope {
       throw ::petb::Error(5, std::string("kernel launch failed at ") + __FILE__ + ":" + \
                                  std::to_string(__LINE__) + ": " + cudaGetErrorString(err__)); \
   } while (0)
+
+// Raises a kernel's dynamic shared-memory limit on the CURRENT device when `bytes` is more than this device has been
+// granted for it so far (the attribute is per device; `memo` is the kernel's own table).
+template <class K>
+void opt_in_shared_memory(K kernel, size_t bytes, SmemOptIn& memo) {
+  int dev = 0;
+  PETB_CUDA(cudaGetDevice(&dev));
+  cudaError_t e = cudaSuccess;
+  memo.ensure(dev, int(bytes), [&](int b) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
+    return e == cudaSuccess ? 0 : 1;
+  });
+  PETB_CUDA(e);
+}
 
 }  // namespace petb

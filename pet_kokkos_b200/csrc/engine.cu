@@ -901,6 +901,9 @@ void Engine::compute_step_device(const pet_device_arrays* a, const double* cell,
     if (forces) PETB_CUDA(cudaMemcpyAsync(h + 1, last_out.f.vir6, 48, cudaMemcpyDeviceToHost, st.s));
     if (skip) PETB_CUDA(cudaMemcpyAsync(pinned + 8, md.overflow, sizeof(int), cudaMemcpyDeviceToHost, st.s));
     PETB_CUDA(cudaStreamSynchronize(st.s));
+    // a tensor-core GEMM that gave up on a wait left garbage behind, and the adds above have put it into the caller's arrays
+    if (gemm_mode != GEMM_NATIVE && gemm_tensor_error(st))
+      throw Error(5, "pet: a tensor-core GEMM gave up waiting on its pipeline; the arrays this step added into are invalid");
     if (skip && pinned[8] != 0) {  // outgrown: drop the capacities and run the step again, read back and resized
       md.caps_valid = false;
       continue;
@@ -1063,6 +1066,8 @@ void Engine::compute_pairs(const pet_pair_list* v, const double* positions, cons
   }
   session_step(*this, positions, true, cell, forces);
   if (fixed_step_overflowed(*this)) session_step(*this, positions, true, cell, forces);
+  if (gemm_mode != GEMM_NATIVE && gemm_tensor_error(st))  // synchronizes the stream
+    throw Error(5, "pet: a tensor-core GEMM gave up waiting on its pipeline; the results of this evaluation are invalid");
   if (out) {
     *out = pet_device_results{};
     out->n_atoms = N;

@@ -334,6 +334,9 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// What the tensor-core path needs of one device: its SM count and an error word in its memory (with a pinned
+// mirror), plus the driver's tensor-map encoder (the same function for every device). One per device ordinal,
+// built on first use with that device current.
 struct TensorState {
   EncodeFn encode = nullptr;
   int* err = nullptr;       // device error word
@@ -343,14 +346,14 @@ struct TensorState {
 };
 
 TensorState& state() {
-  static TensorState s;
-  static std::once_flag once;
-  std::call_once(once, [] {
+  static PerDevice<TensorState> table;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return table.get(dev, [dev](TensorState& s) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return;
-    int dev = 0, major = 0;
-    cudaGetDevice(&dev);
+    int major = 0;
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev);
     if (major != 10 || s.sms <= 0) return;
@@ -361,7 +364,6 @@ TensorState& state() {
     s.encode = reinterpret_cast<EncodeFn>(fn);
     s.ok = true;
   });
-  return s;
 }
 
 // A [rows, K] fp32 row-major matrix as a 2-D tensor map with a 32 x box_rows box, 128-byte swizzle,
@@ -384,12 +386,9 @@ template <int EPI, int BN, int STAGES, bool X3>
 void launch_tc(Stream& st, const GemmArgs& a) {
   using L = Smem<BN, STAGES, X3>;
   static_assert(L::kTotal <= 227 * 1024, "the tile pipeline does not fit shared memory");
-  static bool opted = false;
+  static SmemOptIn opted;
   auto kernel = k_gemm_tc<EPI, BN, STAGES, X3>;
-  if (!opted) {
-    PETB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    opted = true;
-  }
+  opt_in_shared_memory(kernel, L::kTotal, opted);
   const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM, L::BK), mb = make_map(a.B, a.N, a.K, a.ldb, BN, L::BK);
   const CUtensorMap mblo = a.b_lo_offset ? make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, BN, L::BK) : mb;
   const long long tiles = (long long) cdiv(a.M, TBM) * cdiv(a.N, BN);

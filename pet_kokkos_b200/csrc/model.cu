@@ -14,43 +14,160 @@ namespace petb {
 using Taps = std::map<std::string, std::pair<const float*, size_t>>;
 
 // ---- weights -----------------------------------------------------------------
+//
+// A checkpoint tensor is uploaded once as it is stored (doubles) and every layout the kernels read is made from it
+// on the device: both orientations in fp32, the low parts of their 3xTF32 split, and bf16 copies of both. The
+// SwiGLU row pairing and the fold of compress.0 are index maps and short fp64 sums over the uploaded tensors, so
+// the host never loops over a weight.
 
-void Model::put_mat(const std::string& name, int rows, int cols, const double* d) {
-  // Both orientations, then the low parts of their 3xTF32 split (x minus its leading 11 significant bits, with half
-  // of the last bit the tensor core keeps added so that its truncation rounds): [w | wt | w_lo | wt_lo].
-  const size_t n = size_t(rows) * cols;
-  std::vector<float> w(4 * n);
-  for (int a = 0; a < rows; ++a)
-    for (int b = 0; b < cols; ++b) {
-      const float v = float(d[size_t(a) * cols + b]);
-      w[size_t(a) * cols + b] = v;
-      w[n + size_t(b) * rows + a] = v;
-    }
-  for (size_t i = 0; i < 2 * n; ++i) {
-    uint32_t bits, lo;
-    std::memcpy(&bits, &w[i], 4);
-    bits &= 0xFFFFE000u;
-    float hi;
-    std::memcpy(&hi, &bits, 4);
-    const float r = w[i] - hi;
-    std::memcpy(&lo, &r, 4);
-    lo += 0x1000u;
-    std::memcpy(&w[2 * n + i], &lo, 4);
-  }
-  float* dev = nullptr;
-  PETB_CUDA(cudaMalloc(&dev, w.size() * sizeof(float)));
-  owned_.push_back(dev);
-  PETB_CUDA(cudaMemcpy(dev, w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice));
-  mat_[name] = Mat{dev, dev + n, rows, cols, 2 * n};
+namespace {
+
+// Row a of the prepared matrix comes from this row of the stored one. A SwiGLU input layer is stored as [v ; g]
+// (F value rows, then F gate rows) and read as (v_0, g_0, v_1, g_1, ...) so that a gate pair meets in one GEMM
+// thread's run of columns (the reference does the same at load, src/model.cpp:211-222).
+__device__ __forceinline__ int stored_row(int a, int rows, int paired) { return paired ? (a & 1) * (rows / 2) + (a >> 1) : a; }
+
+__device__ __forceinline__ uint16_t bf16_bits(float x) {  // round to nearest even; weights are finite
+  const uint32_t u = __float_as_uint(x);
+  return uint16_t((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+// x minus its leading 11 significant bits, with half of the last bit the tensor core keeps added so that its
+// truncation of this part rounds.
+__device__ __forceinline__ float tf32_low_part(float x) {
+  return __uint_as_float(__float_as_uint(x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u)) + 0x1000u);
 }
 
-void Model::put_vec(const std::string& name, int len, const double* d) {
-  std::vector<float> v(len);
-  for (int a = 0; a < len; ++a) v[a] = float(d[a]);
+// src [rows, ld] doubles (the first `cols` columns of each row) -> [w | wt | w_lo | wt_lo] floats, then bf16 w, wt.
+__global__ void k_weight_layouts(const double* src, int ld, int rows, int cols, int paired, float* out, uint16_t* out16) {
+  const size_t n = size_t(rows) * cols, i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int a = int(i / cols), b = int(i % cols);
+  const float v = float(src[size_t(stored_row(a, rows, paired)) * ld + b]);
+  const size_t t = size_t(b) * rows + a;
+  out[i] = v, out[n + t] = v;
+  out[2 * n + i] = out[3 * n + t] = tf32_low_part(v);
+  out16[i] = out16[n + t] = bf16_bits(v);
+}
+__global__ void k_weight_vector(const double* src, int len, int paired, float* out) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a < len) out[a] = float(src[stored_row(a, len, paired)]);
+}
+
+// compress.0 acts on [edge embedding of (v, |v|) | species embedding | input_edge]; the first two blocks are linear
+// in four numbers and in a table row, so their products with compress.0 are formed once, in fp64 with every product
+// and sum rounded on its own, in column order (the reference's fold, src/model.cpp:233-254, gives the same bits):
+//   wx[d, c]  = sum_j W[d, j] We[j, c]        b[d] = b0[d] + sum_j W[d, j] be[j]
+//   tab[s, d] = sum_j T[s, j] W[d, D + j]
+__global__ void k_fold_geometry(const double* W, int K, const double* We, const double* be, const double* b0, int D, double* wx,
+                                double* b) {
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  double x[4] = {0.0, 0.0, 0.0, 0.0}, bias = b0[d];
+  for (int j = 0; j < D; ++j) {
+    const double w = W[size_t(d) * K + j];
+    for (int c = 0; c < 4; ++c) x[c] = __dadd_rn(x[c], __dmul_rn(w, We[j * 4 + c]));
+    bias = __dadd_rn(bias, __dmul_rn(w, be[j]));
+  }
+  for (int c = 0; c < 4; ++c) wx[d * 4 + c] = x[c];
+  b[d] = bias;
+}
+__global__ void k_fold_species(const double* W, int K, const double* T, int ns, int D, double* tab) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= ns * D) return;
+  const int s = i / D, d = i % D;
+  double acc = 0.0;
+  for (int j = 0; j < D; ++j) acc = __dadd_rn(acc, __dmul_rn(T[size_t(s) * D + j], W[size_t(d) * K + D + j]));
+  tab[i] = acc;
+}
+
+// A tensor's doubles on the device for the duration of the load.
+struct Staged {
+  double* p = nullptr;
+  int rows = 0, cols = 0;
+  explicit Staged(const Tensor& t) {
+    rows = t.shape.empty() ? 1 : int(t.dim(0));
+    cols = t.shape.size() > 1 ? int(t.dim(1)) : 1;
+    alloc(t.data.size());
+    PETB_CUDA(cudaMemcpy(p, t.data.data(), t.data.size() * sizeof(double), cudaMemcpyHostToDevice));
+  }
+  explicit Staged(size_t n) { alloc(n); }
+  ~Staged() { cudaFree(p); }
+  Staged(const Staged&) = delete;
+  void alloc(size_t n) { PETB_CUDA(cudaMalloc(&p, (n ? n : 1) * sizeof(double))); }
+};
+
+// What the network reads from a checkpoint, as (tensor name, how it is prepared).
+enum class Prep { Matrix, Vector, PairedMatrix, PairedVector, CompressFold };
+struct PlanItem {
+  std::string name;
+  Prep prep;
+  int layer = 0;
+};
+
+std::vector<PlanItem> weight_plan(const Hypers& h) {
+  std::vector<PlanItem> plan;
+  const bool ff = h.feedforward, paired = h.swiglu;
+  auto dense = [&](const std::string& stem, bool pair_rows = false) {
+    plan.push_back({stem + ".weight", pair_rows ? Prep::PairedMatrix : Prep::Matrix});
+    plan.push_back({stem + ".bias", pair_rows ? Prep::PairedVector : Prep::Vector});
+  };
+  auto norm = [&](const std::string& stem) {
+    plan.push_back({stem + ".weight", Prep::Vector});
+    if (h.layernorm) plan.push_back({stem + ".bias", Prep::Vector});
+  };
+  plan.push_back({"edge_embedder.weight", Prep::Matrix});
+  for (int L = 0; L < h.num_gnn_layers; ++L) {
+    const std::string layer = "gnn_layers." + std::to_string(L);
+    plan.push_back({layer + ".compress.0", Prep::CompressFold, L});
+    dense(layer + ".compress.2");
+    for (int a = 0; a < h.num_attention_layers; ++a) {
+      const std::string block = layer + ".trans.layers." + std::to_string(a);
+      for (const char* part : {".attention.input_linear", ".attention.output_linear", ".mlp.w_out"}) dense(block + part);
+      dense(block + ".mlp.w_in", paired);
+      norm(block + ".norm_attention"), norm(block + ".norm_mlp");
+      if (!h.expanded_node()) continue;
+      for (const char* part : {".center_contraction", ".center_expansion", ".center_mlp.w_out"}) dense(block + part);
+      dense(block + ".center_mlp.w_in", paired);
+      norm(block + ".norm_center_features");
+    }
+    if (ff) {
+      const std::string n = "combination_norms." + std::to_string(L), m = "combination_mlps." + std::to_string(L);
+      plan.push_back({n + ".weight", Prep::Vector}), plan.push_back({n + ".bias", Prep::Vector});
+      dense(m + ".0"), dense(m + ".2");
+    }
+  }
+  for (int i = 0; i < h.num_readout_layers; ++i) {
+    const std::string r = std::to_string(i);
+    plan.push_back({"node_embedders." + r + ".weight", Prep::Matrix});
+    for (const char* side : {"node", "edge"}) {
+      dense(std::string(side) + "_heads.energy." + r + ".0"), dense(std::string(side) + "_heads.energy." + r + ".2");
+      dense(std::string(side) + "_last_layers.energy." + r + ".energy___0");
+    }
+  }
+  return plan;
+}
+
+}  // namespace
+
+void Model::put_mat(const std::string& name, const double* src, int ld, int rows, int cols, bool paired) {
+  const size_t n = size_t(rows) * cols;
+  float* dev = nullptr;
+  PETB_CUDA(cudaMalloc(&dev, (4 * n + n + 8) * sizeof(float)));  // four fp32 layouts, then two bf16 ones (2n halves)
+  owned_.push_back(dev);
+  uint16_t* dev16 = reinterpret_cast<uint16_t*>(dev + 4 * n);
+  if (n) k_weight_layouts<<<cdiv((long long) n, 256), 256>>>(src, ld, rows, cols, paired ? 1 : 0, dev, dev16);
+  PETB_CUDA(cudaGetLastError());
+  Mat m;
+  m.w = dev, m.wt = dev + n, m.rows = rows, m.cols = cols, m.lo_off = 2 * n, m.w16 = dev16, m.wt16 = dev16 + n;
+  mat_[name] = m;
+}
+
+void Model::put_vec(const std::string& name, const double* src, int len, bool paired) {
   float* dev = nullptr;
   PETB_CUDA(cudaMalloc(&dev, (len > 0 ? len : 1) * sizeof(float)));
   owned_.push_back(dev);
-  PETB_CUDA(cudaMemcpy(dev, v.data(), len * sizeof(float), cudaMemcpyHostToDevice));
+  if (len) k_weight_vector<<<cdiv(len, 256), 256>>>(src, len, paired ? 1 : 0, dev);
+  PETB_CUDA(cudaGetLastError());
   vec_[name] = dev;
 }
 
@@ -65,8 +182,29 @@ const float* Model::vec(const std::string& name) const {
   return it->second;
 }
 
+// compress.0 of layer L -> "@x4" [D,4], "@b" [D], "@tab" [n_species, D] and, past the first layer, "@in" [D,D] (the
+// block that still multiplies input_edge). At layer 0 the species block is the edge embedder's table itself.
+void Model::fold_compress(const Checkpoint& ck, const std::string& c0, int L) {
+  const std::string layer = "gnn_layers." + std::to_string(L);
+  const Staged W(ck.at(c0 + ".weight")), b0(ck.at(c0 + ".bias"));
+  const Staged We(ck.at(layer + ".edge_embedder.weight")), be(ck.at(layer + ".edge_embedder.bias"));
+  const Staged T(ck.at(L == 0 ? "edge_embedder.weight" : layer + ".neighbor_embedder.weight"));
+  const int D = W.rows, K = W.cols, ns = T.rows;
+  if (K != (L == 0 ? 2 : 3) * D || T.cols != D || We.rows != D || We.cols != 4)
+    throw Error(1, "model: '" + c0 + "' does not have the shape of a compress layer");
+  const size_t nx = size_t(D) * 4, nb = size_t(D), nt = size_t(ns) * D;
+  const Staged wx(nx), b(nb), tab(nt);
+  k_fold_geometry<<<cdiv(D, 128), 128>>>(W.p, K, We.p, be.p, b0.p, D, wx.p, b.p);
+  k_fold_species<<<cdiv((long long) ns * D, 128), 128>>>(W.p, K, T.p, ns, D, tab.p);
+  PETB_CUDA(cudaGetLastError());
+  put_mat(c0 + "@x4", wx.p, 4, D, 4, false);
+  put_vec(c0 + "@b", b.p, D, false);
+  put_mat(c0 + "@tab", tab.p, D, ns, D, false);
+  if (L > 0) put_mat(c0 + "@in", W.p + 2 * D, K, D, D, false);
+  PETB_CUDA(cudaDeviceSynchronize());  // the staged tensors are freed on return
+}
+
 Model::Model(const Checkpoint& ck) : h_(ck.hypers), scale_(ck.energy_scale) {
-  const int G = h_.num_gnn_layers, A = h_.num_attention_layers, R = h_.num_readout_layers;
   const bool ff = h_.feedforward, ln = h_.layernorm, expanded = h_.expanded_node(), swiglu = h_.swiglu;
 
   // The two families the reference implements (src/model.cpp:314-334); anything else is refused by name.
@@ -74,99 +212,24 @@ Model::Model(const Checkpoint& ck) : h_(ck.hypers), scale_(ck.energy_scale) {
     throw Error(1, "model: the feedforward featurizer needs PreLN + RMSNorm + SwiGLU with d_node != d_pet");
   if (!ff && (h_.preln || !ln || swiglu || expanded))
     throw Error(1, "model: the residual featurizer needs PostLN + LayerNorm + SiLU with d_node == d_pet");
-  if (A < 1) throw Error(1, "model: num_attention_layers must be >= 1");
+  if (h_.num_attention_layers < 1) throw Error(1, "model: num_attention_layers must be >= 1");
   if (h_.head_dim * h_.num_heads != h_.d_pet) throw Error(1, "model: num_heads * head_dim must equal d_pet");
   if (h_.d_pet % 4 || h_.d_node % 4 || h_.d_head % 4 || h_.d_feedforward % 4)
     throw Error(1, "model: layer widths must be multiples of 4");
 
-  auto load_mat = [&](const std::string& n) {
-    const Tensor& t = ck.at(n);
-    if (t.shape.size() != 2) throw Error(1, "model: expected a 2-D tensor '" + n + "'");
-    put_mat(n, int(t.dim(0)), int(t.dim(1)), t.data.data());
-  };
-  auto load_vec = [&](const std::string& n) { put_vec(n, int(ck.at(n).numel()), ck.at(n).data.data()); };
-  auto load_linear = [&](const std::string& p) { load_mat(p + ".weight"), load_vec(p + ".bias"); };
-  // A SwiGLU w_in's [v ; g] output rows interleaved to (v_j, g_j), so a pair meets in one
-  // GEMM thread's run of columns (src/model.cpp:211-222).
-  auto load_swiglu_in = [&](const std::string& p) {
-    const Tensor &W = ck.at(p + ".weight"), &b = ck.at(p + ".bias");
-    const int F = int(W.dim(0)) / 2, K = int(W.dim(1));
-    std::vector<double> w(W.data.size()), bi(b.data.size());
-    for (int j = 0; j < 2 * F; ++j) {
-      const int src = j % 2 ? F + j / 2 : j / 2;
-      std::copy_n(&W.data[size_t(src) * K], K, &w[size_t(j) * K]);
-      bi[j] = b.data[src];
+  for (const PlanItem& it : weight_plan(h_)) {
+    if (it.prep == Prep::CompressFold) {
+      fold_compress(ck, it.name, it.layer);
+      continue;
     }
-    put_mat(p + ".weight", 2 * F, K, w.data());
-    put_vec(p + ".bias", 2 * F, bi.data());
-  };
-  auto load_mlp_in = [&](const std::string& p) { swiglu ? load_swiglu_in(p) : load_linear(p); };
-  auto load_norm = [&](const std::string& p) {
-    load_vec(p + ".weight");
-    if (ln) load_vec(p + ".bias");
-  };
-  // compress.0 folded in double (src/model.cpp:233-254): its input columns are
-  // [edge embedding of (v,|v|) | species block | input_edge].
-  auto fold_compress = [&](int L) {
-    const std::string g = "gnn_layers." + std::to_string(L), c0 = g + ".compress.0";
-    const Tensor &W = ck.at(c0 + ".weight"), &b0 = ck.at(c0 + ".bias");
-    const Tensor &We = ck.at(g + ".edge_embedder.weight"), &be = ck.at(g + ".edge_embedder.bias");
-    const Tensor& T = ck.at(L == 0 ? "edge_embedder.weight" : g + ".neighbor_embedder.weight");
-    const int D = int(W.dim(0)), K = int(W.dim(1)), ns = int(T.dim(0));
-    auto w = [&](int d, int j) { return W.data[size_t(d) * K + j]; };
-    std::vector<double> wx(size_t(D) * 4, 0.0), b(b0.data), tab(size_t(ns) * D, 0.0), wi;
-    for (int d = 0; d < D; ++d)
-      for (int j = 0; j < D; ++j) {
-        for (int c = 0; c < 4; ++c) wx[d * 4 + c] += w(d, j) * We.data[j * 4 + c];
-        b[d] += w(d, j) * be.data[j];
-        for (int s = 0; s < ns; ++s) tab[size_t(s) * D + d] += T.data[size_t(s) * D + j] * w(d, D + j);
-      }
-    put_mat(c0 + "@x4", D, 4, wx.data());
-    put_vec(c0 + "@b", D, b.data());
-    put_mat(c0 + "@tab", ns, D, tab.data());
-    if (L == 0) return;
-    for (int d = 0; d < D; ++d)
-      for (int j = 0; j < D; ++j) wi.push_back(w(d, 2 * D + j));
-    put_mat(c0 + "@in", D, D, wi.data());
-  };
-
-  for (int L = 0; L < G; ++L) {
-    const std::string g = "gnn_layers." + std::to_string(L), ls = std::to_string(L);
-    fold_compress(L);
-    load_linear(g + ".compress.2");
-    for (int a = 0; a < A; ++a) {
-      const std::string tl = g + ".trans.layers." + std::to_string(a);
-      load_linear(tl + ".attention.input_linear");
-      load_linear(tl + ".attention.output_linear");
-      load_norm(tl + ".norm_attention");
-      load_norm(tl + ".norm_mlp");
-      load_mlp_in(tl + ".mlp.w_in");
-      load_linear(tl + ".mlp.w_out");
-      if (expanded) {
-        load_linear(tl + ".center_contraction");
-        load_linear(tl + ".center_expansion");
-        load_norm(tl + ".norm_center_features");
-        load_mlp_in(tl + ".center_mlp.w_in");
-        load_linear(tl + ".center_mlp.w_out");
-      }
-    }
-    if (ff) {
-      load_vec("combination_norms." + ls + ".weight");
-      load_vec("combination_norms." + ls + ".bias");
-      load_linear("combination_mlps." + ls + ".0");
-      load_linear("combination_mlps." + ls + ".2");
-    }
-  }
-  load_mat("edge_embedder.weight");
-  for (int i = 0; i < R; ++i) {
-    const std::string si = std::to_string(i);
-    load_mat("node_embedders." + si + ".weight");
-    load_linear("node_heads.energy." + si + ".0");
-    load_linear("node_heads.energy." + si + ".2");
-    load_linear("edge_heads.energy." + si + ".0");
-    load_linear("edge_heads.energy." + si + ".2");
-    load_linear("node_last_layers.energy." + si + ".energy___0");
-    load_linear("edge_last_layers.energy." + si + ".energy___0");
+    const Tensor& t = ck.at(it.name);
+    const bool matrix = it.prep == Prep::Matrix || it.prep == Prep::PairedMatrix;
+    const bool paired = it.prep == Prep::PairedMatrix || it.prep == Prep::PairedVector;
+    if (matrix && t.shape.size() != 2) throw Error(1, "model: expected a 2-D tensor '" + it.name + "'");
+    const Staged dev(t);
+    if (matrix) put_mat(it.name, dev.p, dev.cols, dev.rows, dev.cols, paired);
+    else put_vec(it.name, dev.p, int(t.numel()), paired);
+    PETB_CUDA(cudaDeviceSynchronize());
   }
   const size_t ns = ck.composition_energies.size();
   PETB_CUDA(cudaMalloc(&comp_, (ns ? ns : 1) * sizeof(double)));

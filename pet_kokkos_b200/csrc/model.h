@@ -23,6 +23,8 @@ struct Mat {
   const float* wt = nullptr;
   int rows = 0, cols = 0;
   size_t lo_off = 0;  // w + lo_off and wt + lo_off: the low parts of the 3xTF32 split of w and wt
+  const uint16_t* w16 = nullptr;   // w and wt again as bf16 (round to nearest even), for the bf16 GEMM mode
+  const uint16_t* wt16 = nullptr;
 };
 
 struct PassOut {
@@ -66,8 +68,10 @@ class Model {
 
   const Mat& mat(const std::string& name) const;
   const float* vec(const std::string& name) const;
-  void put_mat(const std::string& name, int rows, int cols, const double* d);
-  void put_vec(const std::string& name, int len, const double* d);
+  // `src` are doubles in DEVICE memory; the layouts the kernels read are made from them by kernels.
+  void put_mat(const std::string& name, const double* src, int ld, int rows, int cols, bool paired);
+  void put_vec(const std::string& name, const double* src, int len, bool paired);
+  void fold_compress(const Checkpoint& ck, const std::string& c0, int layer);
 
   Hypers h_;
   double scale_ = 1.0;

@@ -11,9 +11,11 @@
 // The price: the array (kStaticFloats floats, 12 MiB) is resident on every GPU that loads the
 // library, from load to process exit, whether or not this entry point is called; problems that
 // do not fit are refused; and all calls share the one array, so two calls that overlap on a GPU
-// (different host threads, or different streams) race on it. Calls are serialised by the
-// function itself only in the sense that each one synchronizes the device's default stream
-// before it returns.
+// (different host threads) race on it. The copies and the kernel run on the calling thread's
+// own stream (cudaStreamPerThread: it exists without being created, does not wait on the
+// process-wide default stream and is not implicitly joined to other streams), and each call
+// waits for that stream before it returns.
+#include <atomic>
 #include <cstdio>
 
 #include "../../include/pet_b200.h"
@@ -22,13 +24,15 @@
 namespace {
 
 constexpr size_t kStaticFloats = size_t(3) << 20;  // 3 Mi floats = 12 MiB per GPU
-constexpr int kMaxDevices = 64;
+using petb::kMaxDevices;
 
 // The staging array. In host code this name is only a handle: its device address is obtained
 // with cudaGetSymbolAddress below and that pointer is what kernels receive.
 static __device__ __align__(256) float g_static_scratch[kStaticFloats];
 
-float* g_scratch_ptr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+// Device address of g_static_scratch, per device ordinal. Two threads that race on a device's first call both
+// resolve the same address, so a relaxed atomic store is all the cache needs.
+std::atomic<float*> g_scratch_ptr[kMaxDevices];
 
 size_t round64(size_t n) { return (n + 63) & ~size_t(63); }
 
@@ -57,7 +61,8 @@ extern "C" int pet_gemm_host_static(int m, int n, int k, const float* A, const f
   if (dev < 0 || dev >= kMaxDevices) return fail(errbuf, errbuf_len, PET_ERR_INVALID, "pet_gemm_host_static: device ordinal out of range");
   // Set-up, once per device, with that device current: the first call on a device resolves the
   // array's address there. Make that first call before any stream capture begins.
-  if (!g_scratch_ptr[dev]) {
+  float* dA = g_scratch_ptr[dev].load(std::memory_order_relaxed);
+  if (!dA) {
     float* ptr = nullptr;
     const cudaError_t e = cudaGetSymbolAddress((void**) &ptr, g_static_scratch);
     if (e != cudaSuccess || !ptr) {
@@ -65,13 +70,14 @@ extern "C" int pet_gemm_host_static(int m, int n, int k, const float* A, const f
       snprintf(msg, sizeof(msg), "pet_gemm_host_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
       return fail(errbuf, errbuf_len, PET_ERR_CUDA, msg);
     }
-    g_scratch_ptr[dev] = ptr;
+    g_scratch_ptr[dev].store(ptr, std::memory_order_relaxed);
+    dA = ptr;
   }
-  float* dA = g_scratch_ptr[dev];
   float* dW = dA + na;
   float* dC = dW + nw;
   try {
-    petb::Stream st;  // the device's default stream; nothing here allocates
+    petb::Stream st;  // this thread's own stream; nothing here allocates
+    st.s = cudaStreamPerThread;
     petb::Arena unused;
     PETB_CUDA(cudaMemcpyAsync(dA, A, sizeof(float) * size_t(m) * k, cudaMemcpyHostToDevice, st.s));
     PETB_CUDA(cudaMemcpyAsync(dW, W, sizeof(float) * size_t(n) * k, cudaMemcpyHostToDevice, st.s));

@@ -35,20 +35,8 @@ def test_muting_the_exchange_changes_the_answer(lib_path, models):
     whole = Calculator(jp, sp)
     ref = whole.compute(s)
     calcs = [Calculator(jp, sp) for _ in range(2)]
-    domains = [exchange.exchange_domain(s, r, 2, whole.cutoff) for r in range(2)]
-    hub = exchange.ThreadHub(exchange.route(domains))
-    hub.mute = True
-    import threading
-    out = [None, None]
-
-    def run(r):
-        fields, owner, _, _ = domains[r]
-        res = calcs[r].compute_edges(exchange.view_of(fields, exchange.ThreadExchange(hub, r)), True, False)
-        out[r] = exchange.fold_to_owners(res, owner, s["n_atoms"])
-    ts = [threading.Thread(target=run, args=(r,)) for r in range(2)]
-    [t.start() for t in ts]
-    [t.join() for t in ts]
-    E = out[0][0] + out[1][0]
+    # through compute_threads, so that a rank that raises aborts the barrier instead of leaving the other one waiting
+    E, _, _, _ = exchange.compute_threads(calcs, s, whole.cutoff, mute=True)
     assert abs(E - ref.energy[0]) > 1e-4 * np.abs(ref.per_atom_energy).sum()
     for c in calcs + [whole]:
         c.close()

@@ -227,3 +227,22 @@ def test_adaptive_cutoff_with_an_engine_list_matches_the_reference(reference, li
             assert np.abs(rk.virial[0] - steps["virial"][k]).max() <= 1e-5 * max(1.0, np.abs(steps["virial"][k]).max())
     c.close()
     fixed.close()
+
+
+def test_an_older_adaptive_checkpoint_without_the_newer_keys(reference, lib_path, tmp_path):
+    """Checkpoints written before `adaptive_cutoff_method` and `cutoff_width_adaptive` existed: both readers must fall
+    back to the grid scheme and to the plain taper width (src/checkpoint.cpp:91-95), here 0.8 A so that a wrong
+    constant would show in the energies."""
+    import json
+    from pathlib import Path
+    from pet_kokkos_b200 import Calculator, checkpoint as ck
+    jp, sp = ck.write_random_checkpoint(tmp_path / "old_adaptive", "tiny", "feedforward", seed=6, init="scaled",
+                                        num_neighbors_adaptive=16.0, cutoff=5.5, cutoff_width=0.8)
+    meta = json.loads(Path(jp).read_text())
+    del meta["hypers"]["adaptive_cutoff_method"], meta["hypers"]["cutoff_width_adaptive"]
+    Path(jp).write_text(json.dumps(meta))
+    systems = [st.diamond(2, jitter=0.08, seed=2), st.random_mixture(30, 8.0, seed=5)]
+    ref = reference.ReferenceCalculator(str(jp), str(sp)).compute(systems)
+    c = Calculator(jp, sp)
+    bands(c.compute(systems), ref)
+    c.close()
