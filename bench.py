@@ -12,12 +12,23 @@ work is fixed (weak scaling).  `value` is measured with the structures already
 staged in device memory (CUDA events, max over ranks); `e2e` goes through the
 public Calculator.compute call with host arrays in and host results out.
 
+Beside the headline the same JSON line carries `splits`: the two ways the path shards over
+the GPUs of a box, both strong scaling (total work fixed as N grows).  `batch512x64`: the
+512-structure batch, whole structures dealt to ranks by sharding.partition, no data-path
+collective.  `diamond13824`: one 13824-atom cell (pet-omat-l shape); at N = 1 the whole cell
+on one GPU (the backward re-runs each layer's forward to fit memory), at N >= 2 bricks by
+centre atom with ghosts one cutoff deep, edge rows swapped at every layer and the ghost
+forces reduced over NCCL.  --no-splits skips them.
+
 --impl reference times the reference's own CPU implementation of the path on the
 host cores: its unmodified sources compiled for the host (oracle/build_ref.sh, the
 build with its GEMMs through a CBLAS, OpenMP threads for its kernels), through its
-Calculator::compute, on a bounded sample of the workload.  Where that library is not
-built, the CPU restatement (oracle/pet_oracle.py) is timed instead and the line says
-"port".
+Calculator::compute, on the same workload, with every host core this process may use
+(an inherited OMP_NUM_THREADS is overridden; the count in force is reported).  A
+workload whose full size would take more than about ten minutes of CPU for the asked
+steps is timed on a smaller sample of it and the line says so.  Where that library is
+not built, the CPU restatement (oracle/pet_oracle.py) is timed instead and the line
+says "port".
 """
 from __future__ import annotations
 
@@ -45,6 +56,7 @@ UNIT = "atom-evals/s"
 # workload, token-row and atom-row GEMMs as they come (50.2 MB at 25 320 rows; profiles/k_gemm_tc_water648_s_3xtf32.md).
 # A GEMM reads A once and writes C once, so it grows with the rows.
 GEMM_DRAM_BYTES_PER_TOKEN_ROW = 50.2e6 / 25320
+DTYPE_OF = {"native": "f32", "tf32": "tf32", "bf16": "bf16", "3xtf32": "f32 (3xTF32)"}
 MODEL_OF = {"diamond64": "xs", "water648": "s", "diamond1728": "s", "batch512x64": "s", "diamond13824": "l"}
 
 
@@ -134,39 +146,52 @@ def rank_systems(workload, rank, world):
     return st.workload(workload, seed=rank)
 
 
-def cpu_sample(workload):
-    """A bounded sample of the workload for the CPU arm: the same model, fewer atoms where the full case is too slow."""
+def cpu_sample(workload, full):
+    """The CPU arm's structures: the workload itself, or a smaller sample of it with the same model and the same
+    per-atom neighbour count where the full case is too slow for the steps asked."""
     from pet_kokkos_b200 import structures as st
+    if full and workload != "diamond13824":
+        return st.workload(workload), "the full workload", True
     if workload in ("diamond1728", "diamond13824"):
-        return [st.diamond(3, jitter=0.05, seed=0)], "216-atom jittered diamond (3x3x3 cells), same model, same per-atom neighbour count"
+        return ([st.diamond(3, jitter=0.05, seed=0)],
+                "216-atom jittered diamond (3x3x3 cells), same model, same per-atom neighbour count", False)
     if workload == "batch512x64":
-        return st.mixture_batch(8, 64, 9.0), "8 of the 512 structures"
-    return st.workload(workload), "the full workload"
+        return st.mixture_batch(8, 64, 9.0), "8 of the 512 structures", False
+    return st.workload(workload), "the full workload", True
 
 
-def time_cpu(jp, sp, systems, steps, warmup, threads):
-    """Times the CPU arm: (atoms per step, seconds of each step, kind). "reference" is the reference's own code
-    (oracle/_ref, its CBLAS build); "port" the restatement, where that library is not there."""
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_runner(jp, sp, threads):
+    """(run(systems), kind, threads in force). "reference" is the reference's own code (oracle/_ref, its CBLAS build);
+    "port" the restatement, where that library is not there."""
     from oracle import reference_lib
-    n_atoms = sum(s["n_atoms"] for s in systems)
     if os.path.exists(reference_lib.BLAS_LIB_PATH):
         calc = reference_lib.ReferenceCalculator(str(jp), str(sp), blas=True)
-        run, kind = (lambda: calc.compute(systems)), "reference"
-    else:
-        import torch
-        from oracle import pet_oracle as po
-        from pet_kokkos_b200 import checkpoint as ck
-        meta, tens = ck.load_checkpoint(jp, sp)
-        torch.set_num_threads(threads)
-        run, kind = (lambda: po.evaluate(meta, tens, systems, dtype=torch.float32)), "port"
+        used = reference_lib.set_threads(threads)
+        return (lambda systems: calc.compute(systems)), "reference", used
+    import torch
+    from oracle import pet_oracle as po
+    from pet_kokkos_b200 import checkpoint as ck
+    meta, tens = ck.load_checkpoint(jp, sp)
+    torch.set_num_threads(threads)
+    return (lambda systems: po.evaluate(meta, tens, systems, dtype=torch.float32)), "port", torch.get_num_threads()
+
+
+def time_cpu(run, systems, steps, warmup):
     for _ in range(warmup):
-        run()
+        run(systems)
     t = []
     for _ in range(steps):
         t0 = time.perf_counter()
-        run()
+        run(systems)
         t.append(time.perf_counter() - t0)
-    return n_atoms, t, kind
+    return t
 
 
 def run_reference(args):
@@ -174,50 +199,89 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
     with tempfile.TemporaryDirectory() as tmp:
         jp, sp = make_model(tmp, MODEL_OF[args.workload])
-        systems, what = cpu_sample(args.workload)
-        n_atoms, t, kind = time_cpu(jp, sp, systems, args.steps, min(args.warmup, 1), threads)
+        run, kind, threads = cpu_runner(jp, sp, host_cores())
+        # One evaluation of the small sample tells how long the full workload would take (the path's cost is
+        # linear in atoms at a fixed neighbour count): the full one is timed when steps + warm-up fit ten minutes.
+        small, small_what, _ = cpu_sample(args.workload, False)
+        t0 = time.perf_counter()
+        run(small)
+        per_atom = (time.perf_counter() - t0) / sum(s["n_atoms"] for s in small)
+        from pet_kokkos_b200 import structures as st
+        full_atoms = sum(s["n_atoms"] for s in st.workload(args.workload)) if args.workload != "diamond13824" else 13824
+        fits = per_atom * full_atoms * (args.steps + args.warmup) <= 600.0
+        systems, what, same = cpu_sample(args.workload, fits)
+        t = time_cpu(run, systems, args.steps, args.warmup)
+        n_atoms = sum(s["n_atoms"] for s in systems)
     sec = float(np.mean(t))
     value = n_atoms / sec
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "model": f"random-init pet-mad-{MODEL_OF[args.workload]}-like", "sample": what},
+        "config": {"workload": args.workload, "model": f"random-init pet-mad-{MODEL_OF[args.workload]}-like", "sample": what,
+                   "same_config": same, "atoms_per_step": n_atoms},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": what},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0}))
+        "gpu_launches": 0}), flush=True)
 
 
-def run_one_cell(args):
-    """The 13824-atom cell decomposed by centre atom over all ranks (strong scaling): ghosts one cutoff deep, edge rows
-    swapped over NCCL at every layer (the reference's exchange mode), each step set once by set_neighbors and evaluated
-    by compute_step with host positions in and host results out; ghost forces, energy and virial are reduced with one
-    NCCL all-reduce per step."""
+CHECKS = ROOT / "tests" / "golden" / "bench_checks.npz"
+
+
+def check_against_fixture(tag, model_paths, energy, forces, virial, loose=1.0):
+    """Holds a sub-sample's energy, forces and virial to the reference's stored answer (tests/golden/bench_checks.npz,
+    made by tests/golden/make_bench_checks.py) within the parity bands before anything is timed. Returns a short
+    record for the JSON line; raises when the bands are missed."""
+    if not CHECKS.exists():
+        return {"checked": False, "why": "tests/golden/bench_checks.npz is missing"}
+    import hashlib
+    from pet_kokkos_b200 import checkpoint as ck
+    g = np.load(CHECKS)
+    _, tens = ck.load_checkpoint(*model_paths)
+    h = hashlib.sha256()
+    for k in sorted(tens):
+        h.update(k.encode()), h.update(np.ascontiguousarray(tens[k], "<f4").tobytes())
+    if h.hexdigest() != str(g[f"{tag}_digest"]):
+        return {"checked": False, "why": "the seeded model differs from the fixture's"}
+    re, rf, rw = g[f"{tag}_energy"], g[f"{tag}_forces"], g[f"{tag}_virial"]
+    e_scale = max(np.abs(re).max(), np.abs(g[f"{tag}_per_atom_energy"]).sum() / len(re))
+    de = float(np.abs(np.asarray(energy) - re).max() / e_scale)
+    df = float(np.abs(np.asarray(forces) - rf).max() / max(1.0, np.abs(rf).max()))
+    dw = float(np.abs(np.asarray(virial).reshape(rw.shape) - rw).max() / max(1.0, np.abs(rw).max()))
+    rec = {"checked": True, "against": "the reference's CPU build on the same inputs", "rel_dE": de, "dF": df, "rel_dW": dw}
+    if not (de <= loose * 1e-6 and df <= loose * 1e-5 and dw <= loose * 1e-5):
+        raise RuntimeError(f"bench: the {tag} sub-sample misses the parity bands: {rec}")
+    return rec
+
+
+# The bands of bench.py's own checks by GEMM mode, as multiples of the fp32 bands (1e-6 / 1e-5 / 1e-5): the speed modes
+# are held to the reference's bands for them (about three decimal digits), never passed off as fp32.
+CHECK_LOOSE = {"native": 1.0, "3xtf32": 1.0, "tf32": 2000.0, "bf16": 20000.0}
+
+
+def cell_step_fn(calc, system, rank, world, dist):
+    """One evaluation of a periodic cell over `world` ranks, returning a device tensor [1 + 6 + 3 n] (energy, virial,
+    forces of the WHOLE cell on every rank). One rank: the staged cell, evaluated in place. Several: bricks by centre
+    atom, ghosts one cutoff deep, rows swapped at every layer (the reference's exchange mode), set once by
+    set_neighbors and stepped by compute_step; ghost forces folded onto their owners and everything reduced with one
+    all-reduce."""
     import torch
-    import torch.distributed as dist
-    from pet_kokkos_b200 import Calculator, exchange, structures as st
+    from pet_kokkos_b200 import exchange
+    n_total = system["n_atoms"]
+    if world == 1:
+        calc.stage([system])
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29555")
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local), rank=rank, world_size=world)
-    shape = MODEL_OF[args.workload]
-    tmp = tempfile.TemporaryDirectory()
-    jp, sp = make_model(tmp.name, shape)
-    calc = Calculator(jp, sp, gemm=args.gemm, device=local)
-    s = st.workload(args.workload)
-    s = s[0] if isinstance(s, list) else s
-    domains = [exchange.exchange_domain(s, r, world, calc.cutoff) for r in range(world)]
+        def step():
+            calc.compute_staged(True)
+            r = calc.fetch()
+            return torch.from_numpy(np.concatenate([r.energy, r.virial[0], r.forces.ravel()]))
+        return step, {"atoms_owned_rank0": n_total}
+    domains = [exchange.exchange_domain(system, r, world, calc.cutoff) for r in range(world)]
     fields, owner, _, remote = domains[rank]
-    ex = exchange.NcclExchange(exchange.route(domains)[rank])
+    ex = exchange.make_exchange(calc, exchange.route(domains)[rank], dist)
     calc.set_neighbors(exchange.view_of(fields, ex))
-    n_total = s["n_atoms"]
 
     def step():
         res = calc.compute_step(fields["positions"], None, True, False)
@@ -225,57 +289,147 @@ def run_one_cell(args):
         buf = torch.from_numpy(np.concatenate([[e], W, F.ravel()])).cuda()
         dist.all_reduce(buf)
         return buf
+    return step, {"atoms_owned_rank0": int(fields["n_local"]), "atoms_listed_rank0": int(len(fields["positions"])),
+                  "edges_to_ghosts_rank0": int(len(remote)), "exchange": type(ex).__name__}
+
+
+def measure_cell(args, workload, rank, world, local, dist, steps, warmup, tmpdir):
+    """Times the one-cell split; returns the record for the JSON line (rank 0) after checking a 512-atom cell of the
+    same model through the same code path against the reference's stored answer."""
+    import torch
+    from pet_kokkos_b200 import Calculator, structures as st
+    shape = MODEL_OF[workload]
+    jp, sp = make_model(tmpdir, shape)
+    calc = Calculator(jp, sp, gemm=args.gemm, device=local)
 
     def barrier():
-        dist.barrier()
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    small = st.diamond(4, jitter=0.05, seed=0)
+    step, _ = cell_step_fn(calc, small, rank, world, dist)
+    out = step().cpu().numpy()
+    check = check_against_fixture("cell", (jp, sp), out[:1], out[7:].reshape(-1, 3), out[1:7], CHECK_LOOSE[args.gemm])
+    s = st.workload(workload)[0]
+    n_total = s["n_atoms"]
+    step, info = cell_step_fn(calc, s, rank, world, dist)
+    for _ in range(warmup):
         step()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     launches0 = calc.kernel_launches
     dev_ms = []
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         out = step()
         dev_ms.append(calc.last_device_ms)
     barrier()
     wall = time.perf_counter() - t0
     launches = calc.kernel_launches - launches0
-    clocks = sampler.stop() if rank == 0 else None
     n_act, n_edges, max_nb = calc.last_shapes()
+    plan = calc.memory_plan()
     calc.profile(True)  # one more step with CUDA events around each kernel class (rank 0's are reported)
     step()
     calc.profile(False)
     prof = calc.profile_read()
-    classes = {k: {"ms_per_step": v["ms"], "tflops": v["flops"] / max(v["ms"], 1e-9) / 1e9, "gbs": v["bytes"] / max(v["ms"], 1e-9) / 1e6}
-               for k, v in prof.items()}
-    t = torch.tensor([wall, float(np.sum(dev_ms))], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    wall, step_ms = [float(x) for x in t.tolist()]
-    if rank == 0:
-        value = n_total * args.steps / wall
-        listed = len(fields["positions"])
-        emit(json.dumps({
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": step_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None,
-            "dtype": {"native": "f32", "tf32": "tf32", "bf16": "bf16", "3xtf32": "f32 (3xTF32)"}[args.gemm], "data": "synthetic",
-            "config": {"workload": args.workload, "model": f"random-init pet-omat-{shape}-like", "atoms_total": n_total,
-                       "atoms_owned_rank0": fields["n_local"], "atoms_listed_rank0": listed, "kept_edges_rank0": n_edges,
-                       "edges_to_ghosts_rank0": int(len(remote)), "max_neighbors": max_nb, "gemm_mode": args.gemm,
-                       "decomposition": "bricks by centre atom, ghosts one cutoff deep, edge rows exchanged per layer (NCCL all-to-all)",
-                       "l2": "working set far exceeds the 126 MB L2; no flush needed"},
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": listed * 24, "d2h_bytes_per_step": listed * 24 + 8 + 48 + 8 * fields["n_local"],
-                    "ms_per_step": wall / args.steps * 1e3},
-            "gpu_launches": int(launches), "clocks": clocks, "roofline": None, "classes": classes, "cpu_baseline": None,
-            "energy": float(out[0].item())}))
+    exch_ms = getattr(calc, "exchange_ms", lambda: None)()
+    classes = {k: {"ms_per_step": v["ms"], "tflops": v["flops"] / max(v["ms"], 1e-9) / 1e9} for k, v in prof.items()}
+    if world > 1:
+        t = torch.tensor([wall, float(np.sum(dev_ms))], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        wall, step_ms = [float(x) for x in t.tolist()]
+    else:
+        step_ms = float(np.sum(dev_ms))
+    rec = {"workload": workload, "model": f"random-init pet-omat-{shape}-like", "scaling": "strong", "n_gpus": world,
+           "value": n_total * steps / wall, "unit": UNIT, "steps": steps, "warmup": warmup,
+           "ms_per_step": wall / steps * 1e3, "device_ms_per_step": step_ms / steps, "atoms_total": n_total,
+           "kept_edges_rank0": n_edges, "max_neighbors": max_nb, "recompute": plan["tier"],
+           "pool_gib_rank0": plan["pool_bytes"] / 2 ** 30, "gpu_launches": int(launches), "classes_rank0": classes,
+           "non_kernel_ms_per_step": wall / steps * 1e3 - sum(v["ms"] for v in prof.values()),
+           "check": check, "energy": float(out[0].item()), **info}
+    if exch_ms is not None:
+        rec["exchange_ms_per_step_rank0"] = exch_ms
     calc.close()
-    dist.destroy_process_group()
+    return rec
+
+
+def measure_batch(args, rank, world, local, dist, steps, warmup, tmpdir):
+    """Times the 512-structure batch dealt to the ranks as contiguous runs of near-equal cost (sharding.partition): no
+    data-path collective, host structures in and host results out every step; checks its first four structures
+    against the reference's stored answer first."""
+    import torch
+    from pet_kokkos_b200 import Calculator, sharding, structures as st
+    jp, sp = make_model(tmpdir, MODEL_OF["batch512x64"])
+    calc = Calculator(jp, sp, gemm=args.gemm, device=local)
+    systems = st.workload("batch512x64")
+    r4 = calc.compute(systems[:4])
+    check = check_against_fixture("batch", (jp, sp), r4.energy, r4.forces, r4.virial, CHECK_LOOSE[args.gemm])
+    runs = sharding.partition([sharding.structure_cost(s, calc.cutoff) for s in systems], world)
+    b, e = runs[rank]
+    mine = systems[b:e]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        calc.compute(mine)
+    barrier()
+    t0 = time.perf_counter()
+    dev_ms = 0.0
+    for _ in range(steps):
+        calc.compute(mine)
+        dev_ms += calc.last_device_ms
+    barrier()
+    wall = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([wall, dev_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        wall, dev_ms = [float(x) for x in t.tolist()]
+    n_total = sum(s["n_atoms"] for s in systems)
+    rec = {"workload": "batch512x64", "model": "random-init pet-mad-s-like", "scaling": "strong", "n_gpus": world,
+           "value": n_total * steps / wall, "unit": UNIT, "steps": steps, "warmup": warmup,
+           "ms_per_step": wall / steps * 1e3, "device_ms_per_step": dev_ms / steps, "atoms_total": n_total,
+           "structures_rank0": e - b if rank == 0 else None, "batch_pieces_rank0": int(calc.batch_splits),
+           "sharding": "contiguous runs of near-equal atoms x neighbours per rank, no data-path collective; host in, host out",
+           "check": check}
+    calc.close()
+    return rec
+
+
+def run_one_cell(args):
+    """--workload diamond13824: the one-cell split alone, as the headline line."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29555")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), rank=rank, world_size=world)
+    tmp = tempfile.TemporaryDirectory()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    rec = measure_cell(args, args.workload, rank, world, local, dist, args.steps, args.warmup, tmp.name)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        emit(json.dumps({
+            "metric": METRIC, "value": rec["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": rec["ms_per_step"], "device_ms_per_step": rec["device_ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE_OF[args.gemm], "data": "synthetic",
+            "config": {k: rec[k] for k in rec if k not in ("value", "unit", "classes_rank0")} | {"gemm_mode": args.gemm,
+                       "l2": "working set far exceeds the 126 MB L2; no flush needed"},
+            "e2e": {"value": rec["value"], "unit": UNIT, "h2d_bytes_per_step": rec["atoms_total"] * 24,
+                    "d2h_bytes_per_step": rec["atoms_total"] * 24 + 56, "ms_per_step": rec["ms_per_step"]},
+            "gpu_launches": rec["gpu_launches"], "clocks": clocks, "roofline": None, "classes": rec["classes_rank0"],
+            "cpu_baseline": None}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_ours(args):
@@ -361,6 +515,9 @@ def run_ours(args):
     else:
         total_atoms = n_atoms
 
+    # ---- the two multi-GPU splits (every rank takes part), each checked on a sub-sample before it is timed ----
+    splits = None
+    line = None
     if rank == 0:
         peaks = measured_peaks()
         value = total_atoms * args.steps / wall  # barrier + synchronize on both sides, max over ranks
@@ -393,11 +550,12 @@ def run_ours(args):
                        "tflops": v["flops"] / max(v["ms"], 1e-9) / 1e9, "gbs": v["bytes"] / max(v["ms"], 1e-9) / 1e6}
                    for k, v in prof.items()}
         # the other GEMM/attention modes on the same staged structures (N = 1 only), three steps each after two:
-        # native = fp32 on the CUDA cores (the default correctness mode), tf32 = one tensor-core pass (a speed mode)
+        # native = fp32 on the CUDA cores (the default correctness mode); tf32 and bf16 = the speed modes (one
+        # tensor-core pass per product, single-pass tf32 attention), each with its measured distance from native
         modes = None
         if world == 1 and not args.no_cpu:
-            modes = {}
-            for other in ("native", "tf32"):
+            modes, results = {}, {args.gemm: r}
+            for other in ("native", "3xtf32", "tf32", "bf16"):
                 if other == args.gemm:
                     continue
                 c2 = Calculator(jp, sp, gemm=other, device=local)
@@ -408,21 +566,27 @@ def run_ours(args):
                 ms = []
                 for _ in range(3):
                     c2.compute_staged(True)
-                    c2.fetch()
+                    results[other] = c2.fetch()
                     ms.append(c2.last_device_ms)
-                modes[other] = {"device_ms_per_step": float(np.mean(ms))}
+                modes[other] = {"device_ms_per_step": float(np.mean(ms)), "dtype": DTYPE_OF[other]}
                 c2.close()
+            exact = results["native"]
+            for name, res in results.items():
+                d = modes.setdefault(name, {"device_ms_per_step": step_ms / args.steps, "dtype": DTYPE_OF[name]})
+                d["vs_native_dE_meV_per_atom"] = float(np.abs(res.energy - exact.energy).max() / n_atoms * 1e3)
+                d["vs_native_max_dF_meV_per_A"] = float(np.abs(res.forces - exact.forces).max() * 1e3)
         # the CPU arm beside it (N = 1 only): the reference's path on the host cores, on a bounded sample
         cpu = None
         if world == 1 and not args.no_cpu:
-            cs, what = cpu_sample(args.workload)
-            threads = os.cpu_count() or 1
-            na, t, kind = time_cpu(jp, sp, cs, 2, 1, threads)
+            cs, what, _ = cpu_sample(args.workload, False)  # bounded: 10-30 s of CPU work
+            run, kind, threads = cpu_runner(jp, sp, host_cores())
+            t = time_cpu(run, cs, 2, 1)
+            na = sum(x["n_atoms"] for x in cs)
             cpu = {"value": na / float(np.mean(t)), "unit": UNIT, "cores": threads, "kind": kind, "sample": what}
-        emit(json.dumps({
+        line = ({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": step_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"native": "f32", "tf32": "tf32", "bf16": "bf16", "3xtf32": "f32 (3xTF32)"}[args.gemm],
+            "dtype": DTYPE_OF[args.gemm],
             "data": "synthetic",
             "config": {"workload": args.workload, "model": f"random-init pet-mad-{shape}-like", "atoms_per_gpu": n_atoms,
                        "kept_edges_per_gpu": n_edges, "max_neighbors": max_nb, "gemm_mode": args.gemm,
@@ -431,8 +595,21 @@ def run_ours(args):
             "e2e": {"value": total_atoms * args.steps / e2e_wall, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_wall / args.steps * 1e3},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "classes": classes, "other_modes": modes,
-            "cpu_baseline": cpu}))
+            "cpu_baseline": cpu})
     calc.close()
+    if not args.no_splits and args.workload == "diamond1728":
+        splits = {}
+        for name, fn in (("batch512x64", lambda: measure_batch(args, rank, world, local, dist, 3, 1, tmp.name)),
+                         ("diamond13824", lambda: measure_cell(args, "diamond13824", rank, world, local, dist, 2, 1, tmp.name))):
+            try:
+                splits[name] = fn()
+            except Exception as e:  # a split that fails must not take the headline number with it
+                if world > 1:
+                    raise
+                splits[name] = {"failed": f"{type(e).__name__}: {e}"[:500]}
+    if rank == 0:
+        line["splits"] = splits
+        emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
@@ -446,6 +623,7 @@ def main():
     ap.add_argument("--gemm", default=os.environ.get("PET_GEMM", "3xtf32"), choices=["native", "tf32", "bf16", "3xtf32"])
     ap.add_argument("--workload", default="diamond1728", choices=sorted(MODEL_OF))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU arm beside the GPU number")
+    ap.add_argument("--no-splits", action="store_true", help="skip the batch and one-cell splits beside the headline")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -54,7 +54,9 @@ typedef struct pet_options {
   int max_batch_atoms;      /* 0: none                                                */
   int cache_neighbors;      /* Options::cache_neighbors (calculator.hpp:39-40): 1 keeps a staged batch's pairs within
                                cutoff + 1 A between evaluations; 0: PET_CACHE_NEIGHBORS, then off */
-  int reserved[7];
+  int recompute;            /* Options::recompute (include/pet/config.hpp:19-24): 0 auto (PET_RECOMPUTE, then the first
+                               tier that fits the memory budget), 1 never, 2 wide, 3 layers */
+  int reserved[6];
 } pet_options;
 
 /* pet::System (include/pet/neighbors.hpp:15-25). */
@@ -243,6 +245,23 @@ size_t pet_workspace_bytes(const pet_calc* c);
 /* Shapes of the latest evaluation: atoms, kept edges, max neighbours
  * (Calculator::memory_plan, calculator.hpp:307). */
 int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neighbors);
+
+/* The latest evaluation's memory decision (Calculator::memory_plan / MemoryPlan, include/pet/model.hpp:23-28,
+ * calculator.hpp:305-308): shapes, the recompute tier it ran under (1 never, 2 wide, 3 layers), the bytes estimated
+ * for that tier, the budget given (0: what the device has) and what the scratch pools hold now.
+ * pet_memory_report writes the same as text with the device's free and total memory (Calculator::memory_report).
+ * pet_recommended_batch_atoms: atoms per batch the device can afford, the smaller of what memory allows and where
+ * throughput stops improving, known once something has been evaluated (Calculator::recommended_batch_atoms,
+ * src/calculator.cpp:921-938). */
+typedef struct pet_memory_plan_info {
+  int atoms, max_neighbors;
+  long edges;
+  int tier;
+  size_t estimate_bytes, budget_bytes, pool_bytes;
+} pet_memory_plan_info;
+int pet_memory_plan(const pet_calc* c, pet_memory_plan_info* out);
+int pet_memory_report(const pet_calc* c, char* buf, size_t len);
+int pet_recommended_batch_atoms(const pet_calc* c);
 
 /* Kernels launched by this library on this calculator since creation, and the
  * device time in milliseconds of the latest evaluation (CUDA events on the

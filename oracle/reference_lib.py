@@ -88,6 +88,19 @@ def _load(blas=False):
     return _libs[blas]
 
 
+def set_threads(n: int, blas: bool = True) -> int:
+    """Gives the reference's OpenMP kernels and its BLAS `n` host threads, whatever OMP_NUM_THREADS the process
+    inherited (torchrun exports OMP_NUM_THREADS=1 to its ranks), and returns the OpenMP thread count in force."""
+    _load(blas)
+    omp = ctypes.CDLL("libgomp.so.1")
+    omp.omp_set_num_threads(int(n))
+    if blas:
+        path, prefix = find_blas()
+        ob = ctypes.CDLL(path)
+        getattr(ob, prefix + "openblas_set_num_threads")(int(n))
+    return int(omp.omp_get_max_threads())
+
+
 def _ptr(a):
     return None if a is None else a.ctypes.data
 

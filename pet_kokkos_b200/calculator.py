@@ -20,6 +20,7 @@ _LIB_PATH = Path(__file__).resolve().parent / "libpet_b200.so"
 _lib = None
 
 GEMM_MODES = {"native": 0, "tf32": 1, "bf16": 2, "3xtf32": 3}
+RECOMPUTE_TIERS = {"auto": 0, "never": 1, "wide": 2, "layers": 3}
 
 
 class PetSystem(C.Structure):
@@ -30,7 +31,12 @@ class PetSystem(C.Structure):
 class PetOptions(C.Structure):
     _fields_ = [("device", C.c_int), ("gemm_mode", C.c_int), ("graphs", C.c_int), ("md_fixed_shapes", C.c_int),
                 ("memory_budget_bytes", C.c_size_t), ("max_batch_atoms", C.c_int), ("cache_neighbors", C.c_int),
-                ("reserved", C.c_int * 7)]
+                ("recompute", C.c_int), ("reserved", C.c_int * 6)]
+
+
+class PetMemoryPlan(C.Structure):
+    _fields_ = [("atoms", C.c_int), ("max_neighbors", C.c_int), ("edges", C.c_long), ("tier", C.c_int),
+                ("estimate_bytes", C.c_size_t), ("budget_bytes", C.c_size_t), ("pool_bytes", C.c_size_t)]
 
 
 class PetResults(C.Structure):
@@ -119,6 +125,9 @@ SIGNATURES = {
     "pet_supports": (C.c_int, [C.c_void_p, C.c_int]),
     "pet_workspace_bytes": (C.c_size_t, [C.c_void_p]),
     "pet_last_shapes": (C.c_int, [C.c_void_p, _P(C.c_int), _P(C.c_int), _P(C.c_int)]),
+    "pet_memory_plan": (C.c_int, [C.c_void_p, _P(PetMemoryPlan)]),
+    "pet_memory_report": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
+    "pet_recommended_batch_atoms": (C.c_int, [C.c_void_p]),
     "pet_kernel_launches": (C.c_longlong, [C.c_void_p]),
     "pet_last_device_ms": (C.c_double, [C.c_void_p]),
     "pet_graph_replays": (C.c_longlong, [C.c_void_p]),
@@ -225,7 +234,7 @@ class Calculator:
     """A loaded model on one GPU.  Reuse one across calls: it holds the scratch pools."""
 
     def __init__(self, model_json, model_weights=None, gemm=None, device=-1, graphs=None, md_fixed_shapes=None,
-                 cache_neighbors=None, memory_budget_bytes=0, max_batch_atoms=0):
+                 cache_neighbors=None, memory_budget_bytes=0, max_batch_atoms=0, recompute=None):
         self._h = None
         self._lib = load_library()
         if model_weights is None:  # a path prefix, as the reference's resolve_model accepts
@@ -239,6 +248,8 @@ class Calculator:
         if md_fixed_shapes is not None:  # Options::md_fixed_shapes (calculator.hpp:111-116)
             o.md_fixed_shapes = int(bool(md_fixed_shapes))
         o.memory_budget_bytes, o.max_batch_atoms = int(memory_budget_bytes), int(max_batch_atoms)
+        if recompute is not None:  # Options::recompute: "auto" | "never" | "wide" | "layers"
+            o.recompute = RECOMPUTE_TIERS[recompute] if isinstance(recompute, str) else int(recompute)
         if cache_neighbors:  # Options::cache_neighbors (calculator.hpp:36-40): a Verlet cache for staged batches
             o.cache_neighbors = 1
         h = C.c_void_p()
@@ -329,6 +340,24 @@ class Calculator:
         return a.value, e.value, m.value
 
     # ---- evaluation ----
+    def memory_plan(self):
+        """The latest evaluation's memory decision (Calculator::memory_plan): a dict with atoms, max_neighbors, edges,
+        tier ("never" | "wide" | "layers"), estimate_bytes, budget_bytes, pool_bytes."""
+        p = PetMemoryPlan()
+        self._check(self._lib.pet_memory_plan(self._h, C.byref(p)))
+        names = {v: k for k, v in RECOMPUTE_TIERS.items()}
+        return {"atoms": p.atoms, "max_neighbors": p.max_neighbors, "edges": p.edges, "tier": names.get(p.tier, "?"),
+                "estimate_bytes": p.estimate_bytes, "budget_bytes": p.budget_bytes, "pool_bytes": p.pool_bytes}
+
+    def memory_report(self):
+        buf = C.create_string_buffer(1024)
+        self._check(self._lib.pet_memory_report(self._h, buf, len(buf)))
+        return buf.value.decode()
+
+    @property
+    def recommended_batch_atoms(self):
+        return int(self._lib.pet_recommended_batch_atoms(self._h))
+
     def _results(self, B, N, forces, n_atoms, pairs=0):
         r = Results(np.zeros(B), np.zeros(N), n_atoms=list(n_atoms))
         pr = PetResults()

@@ -227,7 +227,7 @@ void attention_forward(Stream& st, const AttnArgs& p) {
   // qkv read and the output written once.
   const double D = double(p.H) * p.hd;
   const ProfScope ps(st, PC_ATTN_FWD, 4.0 * p.pairs * D, 4.0 * p.T * (4.0 * D + 2.0 * p.H));
-  if (p.tensor && attention_forward_mma(st, p)) return;
+  if (p.mode != ATTN_NATIVE && attention_forward_mma(st, p)) return;
   if (attention_forward_tiled(st, p)) return;
   switch (p.hd) {
     case 16: return fwd_hd<16>(st, p);
@@ -244,7 +244,7 @@ void attention_backward(Stream& st, const AttnArgs& p) {
   if (p.N == 0) return;
   const double D = double(p.H) * p.hd;
   const ProfScope ps(st, PC_ATTN_BWD, 10.0 * p.pairs * D, 4.0 * p.T * (8.0 * D + 3.0 * p.H));
-  if (p.tensor && attention_backward_mma(st, p)) return;
+  if (p.mode != ATTN_NATIVE && attention_backward_mma(st, p)) return;
   if (attention_backward_tiled(st, p)) return;
   switch (p.hd) {
     case 16: return bwd_hd<16>(st, p);

@@ -1,6 +1,9 @@
-// Attention on the tensor cores with fp32-class accuracy: warp-level mma.sync m16n8k8 on operands
-// split into a leading tf32 part and its remainder (three products per tile, small terms first),
-// fp32 accumulation. Same mathematics as attention.cu; used when an atom's tokens fit shared memory.
+// Attention on the tensor cores: warp-level mma.sync m16n8k8 with fp32 accumulation, in two forms. X3 (the
+// reference's AttentionMode::TF32x3, src/attention.cpp:949-1011): every operand split into a leading tf32 part and
+// its remainder, three products per tile, small terms first: fp32-class accuracy. Single pass (AttentionMode::TF32,
+// src/attention.cpp:1031-1225 with X3 = false): operands rounded to tf32, one product per tile: the speed mode that
+// goes with the tf32 and bf16 GEMM modes. Same mathematics as attention.cu; used when an atom's tokens fit shared
+// memory.
 //
 // One CTA per (atom, head), one warp per block of 16 query rows (and, in the backward, one more per
 // block of 16 keys). The head's Q, K, V (and dO) slices are staged once with a pitch
@@ -39,10 +42,18 @@ struct Frag {
 // x = hi + lo with hi the leading 11 significant bits of x (truncated) and lo the remainder rounded to 11 bits
 // (half of the last kept bit added, then masked). Integer and fp32-add instructions only: cvt.rna.tf32 runs on the
 // quarter-rate conversion pipe, which two conversions per operand element had saturated.
+// Single pass (X3 false): hi is x rounded to tf32 (nearest, half of the last kept bit added before the mask) and lo is
+// never read, so the compiler drops it.
+template <bool X3>
 __device__ __forceinline__ Frag split(float x) {
   Frag f;
-  f.hi = __float_as_uint(x) & 0xFFFFE000u;
-  f.lo = (__float_as_uint(x - __uint_as_float(f.hi)) + 0x1000u) & 0xFFFFE000u;
+  if (X3) {
+    f.hi = __float_as_uint(x) & 0xFFFFE000u;
+    f.lo = (__float_as_uint(x - __uint_as_float(f.hi)) + 0x1000u) & 0xFFFFE000u;
+  } else {
+    f.hi = (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u;
+    f.lo = 0u;
+  }
   return f;
 }
 __device__ __forceinline__ void mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -51,30 +62,29 @@ __device__ __forceinline__ void mma(float* c, uint32_t a0, uint32_t a1, uint32_t
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// c += a . b with both operands split: lo.hi + hi.lo + hi.hi
-__device__ __forceinline__ void mma3(float* c, const Frag* a, const Frag& b0, const Frag& b1) {
-  mma(c, a[0].lo, a[1].lo, a[2].lo, a[3].lo, b0.hi, b1.hi);
-  mma(c, a[0].hi, a[1].hi, a[2].hi, a[3].hi, b0.lo, b1.lo);
-  mma(c, a[0].hi, a[1].hi, a[2].hi, a[3].hi, b0.hi, b1.hi);
-}
 // The same for G independent accumulators that share the A operand, one term at a time: consecutive
 // instructions never depend on each other, so the tensor pipe's latency is covered inside one warp.
-template <int G>
+template <int G, bool X3>
 __device__ __forceinline__ void mma3_shared_a(float (*c)[4], const Frag* a, const Frag (*b)[2]) {
+  if (X3) {
 #pragma unroll
-  for (int j = 0; j < G; ++j) mma(c[j], a[0].lo, a[1].lo, a[2].lo, a[3].lo, b[j][0].hi, b[j][1].hi);
+    for (int j = 0; j < G; ++j) mma(c[j], a[0].lo, a[1].lo, a[2].lo, a[3].lo, b[j][0].hi, b[j][1].hi);
 #pragma unroll
-  for (int j = 0; j < G; ++j) mma(c[j], a[0].hi, a[1].hi, a[2].hi, a[3].hi, b[j][0].lo, b[j][1].lo);
+    for (int j = 0; j < G; ++j) mma(c[j], a[0].hi, a[1].hi, a[2].hi, a[3].hi, b[j][0].lo, b[j][1].lo);
+  }
 #pragma unroll
   for (int j = 0; j < G; ++j) mma(c[j], a[0].hi, a[1].hi, a[2].hi, a[3].hi, b[j][0].hi, b[j][1].hi);
 }
 // The same for two accumulators with their own A operands (two products that run side by side).
+template <bool X3>
 __device__ __forceinline__ void mma3_pair(float* c0, const Frag* a0, const Frag& p0, const Frag& p1, float* c1, const Frag* a1,
                                           const Frag& r0, const Frag& r1) {
-  mma(c0, a0[0].lo, a0[1].lo, a0[2].lo, a0[3].lo, p0.hi, p1.hi);
-  mma(c1, a1[0].lo, a1[1].lo, a1[2].lo, a1[3].lo, r0.hi, r1.hi);
-  mma(c0, a0[0].hi, a0[1].hi, a0[2].hi, a0[3].hi, p0.lo, p1.lo);
-  mma(c1, a1[0].hi, a1[1].hi, a1[2].hi, a1[3].hi, r0.lo, r1.lo);
+  if (X3) {
+    mma(c0, a0[0].lo, a0[1].lo, a0[2].lo, a0[3].lo, p0.hi, p1.hi);
+    mma(c1, a1[0].lo, a1[1].lo, a1[2].lo, a1[3].lo, r0.hi, r1.hi);
+    mma(c0, a0[0].hi, a0[1].hi, a0[2].hi, a0[3].hi, p0.lo, p1.lo);
+    mma(c1, a1[0].hi, a1[1].hi, a1[2].hi, a1[3].hi, r0.lo, r1.lo);
+  }
   mma(c0, a0[0].hi, a0[1].hi, a0[2].hi, a0[3].hi, p0.hi, p1.hi);
   mma(c1, a1[0].hi, a1[1].hi, a1[2].hi, a1[3].hi, r0.hi, r1.hi);
 }
@@ -107,19 +117,19 @@ __device__ __forceinline__ void stage(float* dst, const float* src, size_t ld, i
 }
 
 // The A fragments (hi, lo) of rows r0.. r0+15 of X [.][P] for every 8-wide step of the head dimension.
-template <int HD>
+template <int HD, bool X3>
 __device__ __forceinline__ void load_a(Frag (*f)[4], const float* x, int r0, int g, int t) {
   constexpr int P = HD + 4;
 #pragma unroll
   for (int ks = 0; ks < HD / 8; ++ks) {
-    f[ks][0] = split(x[(r0 + g) * P + 8 * ks + t]);
-    f[ks][1] = split(x[(r0 + g + 8) * P + 8 * ks + t]);
-    f[ks][2] = split(x[(r0 + g) * P + 8 * ks + t + 4]);
-    f[ks][3] = split(x[(r0 + g + 8) * P + 8 * ks + t + 4]);
+    f[ks][0] = split<X3>(x[(r0 + g) * P + 8 * ks + t]);
+    f[ks][1] = split<X3>(x[(r0 + g + 8) * P + 8 * ks + t]);
+    f[ks][2] = split<X3>(x[(r0 + g) * P + 8 * ks + t + 4]);
+    f[ks][3] = split<X3>(x[(r0 + g + 8) * P + 8 * ks + t + 4]);
   }
 }
 
-template <int HD, int MAXKB>
+template <int HD, int MAXKB, bool X3>
 __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k_attn_fwd_mma(AttnArgs p) {
   constexpr int P = HD + 4, KS = HD / 8, R = 8 * MAXKB;  // R: staged token rows, the kernel's most (zero past the atom's)
   constexpr int G = MAXKB % 5 == 0 ? 5 : (MAXKB % 4 == 0 ? 4 : 2);  // key blocks whose score tiles advance together
@@ -145,7 +155,7 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
   if (r0 >= cnt) return;
 
   Frag qf[KS][4];
-  load_a<HD>(qf, sq, r0, g, t);
+  load_a<HD, X3>(qf, sq, r0, g, t);
   float s[MAXKB][4];
 #pragma unroll
   for (int kb = 0; kb < MAXKB; ++kb) s[kb][0] = s[kb][1] = s[kb][2] = s[kb][3] = 0.f;
@@ -157,10 +167,10 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
         Frag b[G][2];
 #pragma unroll
         for (int j = 0; j < G; ++j) {
-          b[j][0] = split(sk[(8 * (kg + j) + g) * P + 8 * ks + t]);
-          b[j][1] = split(sk[(8 * (kg + j) + g) * P + 8 * ks + t + 4]);
+          b[j][0] = split<X3>(sk[(8 * (kg + j) + g) * P + 8 * ks + t]);
+          b[j][1] = split<X3>(sk[(8 * (kg + j) + g) * P + 8 * ks + t + 4]);
         }
-        mma3_shared_a<G>(&s[kg], qf[ks], b);
+        mma3_shared_a<G, X3>(&s[kg], qf[ks], b);
       }
     }
   }
@@ -203,14 +213,14 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
 #pragma unroll
   for (int kb = 0; kb < MAXKB; ++kb)
     if (kb < nkb) {
-      const Frag a[4] = {split(s[kb][0] * il0), split(s[kb][2] * il1), split(s[kb][1] * il0), split(s[kb][3] * il1)};
+      const Frag a[4] = {split<X3>(s[kb][0] * il0), split<X3>(s[kb][2] * il1), split<X3>(s[kb][1] * il0), split<X3>(s[kb][3] * il1)};
       Frag b[KS][2];
 #pragma unroll
       for (int db = 0; db < KS; ++db) {
-        b[db][0] = split(sv[(8 * kb + 2 * t) * P + 8 * db + g]);
-        b[db][1] = split(sv[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
+        b[db][0] = split<X3>(sv[(8 * kb + 2 * t) * P + 8 * db + g]);
+        b[db][1] = split<X3>(sv[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
       }
-      mma3_shared_a<KS>(o, a, b);
+      mma3_shared_a<KS, X3>(o, a, b);
     }
   const size_t g0 = q0 == 0 ? size_t(n) : size_t(p.N) + e0 + q0 - 1, g1 = size_t(p.N) + e0 + q1 - 1;
 #pragma unroll
@@ -224,7 +234,7 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
   }
 }
 
-template <int HD, int MAXT>
+template <int HD, int MAXT, bool X3>
 __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(AttnArgs p) {
   constexpr int P = HD + 4, KS = HD / 8;
   extern __shared__ __align__(16) float smem[];
@@ -275,8 +285,8 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
   const size_t g0 = i0 == 0 ? size_t(n) : size_t(p.N) + e0 + i0 - 1, g1 = size_t(p.N) + e0 + i1 - 1;
   if (!keys) {
     Frag qf[KS][4], gf[KS][4];
-    load_a<HD>(qf, sq, r0, g, t);
-    load_a<HD>(gf, sg, r0, g, t);
+    load_a<HD, X3>(qf, sq, r0, g, t);
+    load_a<HD, X3>(gf, sg, r0, g, t);
     const float m0 = sm[i0], m1 = sm[i1], il0 = sl[i0], il1 = sl[i1], dq0 = sd[i0], dq1 = sd[i1];
     float dq[KS][4];
 #pragma unroll
@@ -285,9 +295,9 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
       float cs[4] = {0.f, 0.f, 0.f, 0.f}, cp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
-        const Frag k0 = split(sk[(8 * kb + g) * P + 8 * ks + t]), k1 = split(sk[(8 * kb + g) * P + 8 * ks + t + 4]);
-        const Frag v0 = split(sv[(8 * kb + g) * P + 8 * ks + t]), v1 = split(sv[(8 * kb + g) * P + 8 * ks + t + 4]);
-        mma3_pair(cs, qf[ks], k0, k1, cp, gf[ks], v0, v1);
+        const Frag k0 = split<X3>(sk[(8 * kb + g) * P + 8 * ks + t]), k1 = split<X3>(sk[(8 * kb + g) * P + 8 * ks + t + 4]);
+        const Frag v0 = split<X3>(sv[(8 * kb + g) * P + 8 * ks + t]), v1 = split<X3>(sv[(8 * kb + g) * P + 8 * ks + t + 4]);
+        mma3_pair<X3>(cs, qf[ks], k0, k1, cp, gf[ks], v0, v1);
       }
       const int key = 8 * kb + 2 * t;
       const float lc0 = slc[key], lc1 = slc[key + 1];
@@ -295,14 +305,14 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
       const float P1 = (il0 > 0.f && !is_off(lc1)) ? __expf(cs[1] * p.sc + lc1 - m0) * il0 : 0.f;
       const float P2 = (il1 > 0.f && !is_off(lc0)) ? __expf(cs[2] * p.sc + lc0 - m1) * il1 : 0.f;
       const float P3 = (il1 > 0.f && !is_off(lc1)) ? __expf(cs[3] * p.sc + lc1 - m1) * il1 : 0.f;
-      const Frag a[4] = {split(P0 * (cp[0] - dq0)), split(P2 * (cp[2] - dq1)), split(P1 * (cp[1] - dq0)), split(P3 * (cp[3] - dq1))};
+      const Frag a[4] = {split<X3>(P0 * (cp[0] - dq0)), split<X3>(P2 * (cp[2] - dq1)), split<X3>(P1 * (cp[1] - dq0)), split<X3>(P3 * (cp[3] - dq1))};
       Frag b[KS][2];
 #pragma unroll
       for (int db = 0; db < KS; ++db) {
-        b[db][0] = split(sk[(8 * kb + 2 * t) * P + 8 * db + g]);
-        b[db][1] = split(sk[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
+        b[db][0] = split<X3>(sk[(8 * kb + 2 * t) * P + 8 * db + g]);
+        b[db][1] = split<X3>(sk[(8 * kb + 2 * t + 1) * P + 8 * db + g]);
       }
-      mma3_shared_a<KS>(dq, a, b);
+      mma3_shared_a<KS, X3>(dq, a, b);
     }
 #pragma unroll
     for (int db = 0; db < KS; ++db) {
@@ -315,8 +325,8 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
     // transposed: rows are keys. S^T = K Q^T and dP^T = V dO^T per block of 8 queries; the accumulator
     // fragment of dS^T (and P^T) is the A operand of dK = dS^T Q (and dV = P^T dO).
     Frag kf[KS][4], vf[KS][4];
-    load_a<HD>(kf, sk, r0, g, t);
-    load_a<HD>(vf, sv, r0, g, t);
+    load_a<HD, X3>(kf, sk, r0, g, t);
+    load_a<HD, X3>(vf, sv, r0, g, t);
     const float lc0 = slc[i0], lc1 = slc[i1];
     const bool on0 = !is_off(lc0), on1 = !is_off(lc1);
     float dk[KS][4], dv[KS][4], cf0 = 0.f, cf1 = 0.f;
@@ -327,9 +337,9 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
       float cs[4] = {0.f, 0.f, 0.f, 0.f}, cp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
-        const Frag q0 = split(sq[(8 * qb + g) * P + 8 * ks + t]), q1 = split(sq[(8 * qb + g) * P + 8 * ks + t + 4]);
-        const Frag d0 = split(sg[(8 * qb + g) * P + 8 * ks + t]), d1 = split(sg[(8 * qb + g) * P + 8 * ks + t + 4]);
-        mma3_pair(cs, kf[ks], q0, q1, cp, vf[ks], d0, d1);
+        const Frag q0 = split<X3>(sq[(8 * qb + g) * P + 8 * ks + t]), q1 = split<X3>(sq[(8 * qb + g) * P + 8 * ks + t + 4]);
+        const Frag d0 = split<X3>(sg[(8 * qb + g) * P + 8 * ks + t]), d1 = split<X3>(sg[(8 * qb + g) * P + 8 * ks + t + 4]);
+        mma3_pair<X3>(cs, kf[ks], q0, q1, cp, vf[ks], d0, d1);
       }
       const int qa = 8 * qb + 2 * t, qc = qa + 1;  // this lane's two queries of the block
       const float ma = sm[qa], mc = sm[qc], ila = sl[qa], ilc = sl[qc], da = sd[qa], dc = sd[qc];
@@ -339,19 +349,19 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
       const float P3 = (on1 && ilc > 0.f) ? __expf(cs[3] * p.sc + lc1 - mc) * ilc : 0.f;
       const float S0 = P0 * (cp[0] - da), S1 = P1 * (cp[1] - dc), S2 = P2 * (cp[2] - da), S3 = P3 * (cp[3] - dc);
       cf0 += S0 + S1, cf1 += S2 + S3;
-      const Frag as[4] = {split(S0), split(S2), split(S1), split(S3)};
-      const Frag ap[4] = {split(P0), split(P2), split(P1), split(P3)};
+      const Frag as[4] = {split<X3>(S0), split<X3>(S2), split<X3>(S1), split<X3>(S3)};
+      const Frag ap[4] = {split<X3>(P0), split<X3>(P2), split<X3>(P1), split<X3>(P3)};
       {
         Frag b[KS][2];
 #pragma unroll
-        for (int db = 0; db < KS; ++db) b[db][0] = split(sq[qa * P + 8 * db + g]), b[db][1] = split(sq[qc * P + 8 * db + g]);
-        mma3_shared_a<KS>(dk, as, b);
+        for (int db = 0; db < KS; ++db) b[db][0] = split<X3>(sq[qa * P + 8 * db + g]), b[db][1] = split<X3>(sq[qc * P + 8 * db + g]);
+        mma3_shared_a<KS, X3>(dk, as, b);
       }
       {
         Frag b[KS][2];
 #pragma unroll
-        for (int db = 0; db < KS; ++db) b[db][0] = split(sg[qa * P + 8 * db + g]), b[db][1] = split(sg[qc * P + 8 * db + g]);
-        mma3_shared_a<KS>(dv, ap, b);
+        for (int db = 0; db < KS; ++db) b[db][0] = split<X3>(sg[qa * P + 8 * db + g]), b[db][1] = split<X3>(sg[qc * P + 8 * db + g]);
+        mma3_shared_a<KS, X3>(dv, ap, b);
       }
     }
     cf0 += __shfl_xor_sync(0xffffffffu, cf0, 1), cf0 += __shfl_xor_sync(0xffffffffu, cf0, 2);
@@ -400,17 +410,17 @@ void launch(Stream& st, K kernel, const AttnArgs& p, size_t bytes, int threads, 
   PETB_LAUNCH_CHECK(st);
 }
 
-template <int HD>
+template <int HD, bool X3>
 bool fwd_hd(Stream& st, const AttnArgs& p) {
   const int S16 = round16(p.S), threads = 32 * (S16 / 16);
   if (S16 > 176 || fwd_bytes(22, HD) > 200 * 1024) return false;
   static SmemOptIn o10, o16, o22;
-  if (S16 <= 80) launch(st, k_attn_fwd_mma<HD, 10>, p, fwd_bytes(10, HD), threads, o10);
-  else if (S16 <= 128) launch(st, k_attn_fwd_mma<HD, 16>, p, fwd_bytes(16, HD), threads, o16);
-  else launch(st, k_attn_fwd_mma<HD, 22>, p, fwd_bytes(22, HD), threads, o22);
+  if (S16 <= 80) launch(st, k_attn_fwd_mma<HD, 10, X3>, p, fwd_bytes(10, HD), threads, o10);
+  else if (S16 <= 128) launch(st, k_attn_fwd_mma<HD, 16, X3>, p, fwd_bytes(16, HD), threads, o16);
+  else launch(st, k_attn_fwd_mma<HD, 22, X3>, p, fwd_bytes(22, HD), threads, o22);
   return true;
 }
-template <int HD>
+template <int HD, bool X3>
 bool bwd_hd(Stream& st, const AttnArgs& p) {
   const int S16 = round16(p.S);
   int threads = 2 * 32 * (S16 / 16);  // a warp per 16 queries and a warp per 16 keys, up to 512 threads: then blocks in turn
@@ -418,9 +428,28 @@ bool bwd_hd(Stream& st, const AttnArgs& p) {
   const size_t bytes = bwd_bytes(p.S, HD);
   if (bytes > 200 * 1024) return false;
   static SmemOptIn o320, o512;
-  if (threads <= 320) launch(st, k_attn_bwd_mma<HD, 320>, p, bytes, threads, o320);
-  else launch(st, k_attn_bwd_mma<HD, 512>, p, bytes, threads, o512);
+  if (threads <= 320) launch(st, k_attn_bwd_mma<HD, 320, X3>, p, bytes, threads, o320);
+  else launch(st, k_attn_bwd_mma<HD, 512, X3>, p, bytes, threads, o512);
   return true;
+}
+
+template <bool X3>
+bool fwd_any(Stream& st, const AttnArgs& p) {
+  switch (p.hd) {
+    case 16: return fwd_hd<16, X3>(st, p);
+    case 32: return fwd_hd<32, X3>(st, p);
+    case 64: return fwd_hd<64, X3>(st, p);
+    default: return false;
+  }
+}
+template <bool X3>
+bool bwd_any(Stream& st, const AttnArgs& p) {
+  switch (p.hd) {
+    case 16: return bwd_hd<16, X3>(st, p);
+    case 32: return bwd_hd<32, X3>(st, p);
+    case 64: return bwd_hd<64, X3>(st, p);
+    default: return false;
+  }
 }
 
 }  // namespace
@@ -428,22 +457,12 @@ bool bwd_hd(Stream& st, const AttnArgs& p) {
 // True if the tensor-core kernel took the pass; false leaves it to the other kernels.
 bool attention_forward_mma(Stream& st, const AttnArgs& p) {
   if (!enabled()) return false;
-  switch (p.hd) {
-    case 16: return fwd_hd<16>(st, p);
-    case 32: return fwd_hd<32>(st, p);
-    case 64: return fwd_hd<64>(st, p);
-    default: return false;
-  }
+  return p.mode == ATTN_TF32 ? fwd_any<false>(st, p) : fwd_any<true>(st, p);
 }
 
 bool attention_backward_mma(Stream& st, const AttnArgs& p) {
   if (!enabled()) return false;
-  switch (p.hd) {
-    case 16: return bwd_hd<16>(st, p);
-    case 32: return bwd_hd<32>(st, p);
-    case 64: return bwd_hd<64>(st, p);
-    default: return false;
-  }
+  return p.mode == ATTN_TF32 ? bwd_any<false>(st, p) : bwd_any<true>(st, p);
 }
 
 }  // namespace petb

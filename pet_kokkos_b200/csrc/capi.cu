@@ -141,6 +141,48 @@ int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neig
   if (max_neighbors) *max_neighbors = c->e->last_pk.M;
   return PET_OK;
 }
+int pet_memory_plan(const pet_calc* c, pet_memory_plan_info* out) {
+  if (!c || !c->e || !out) return PET_ERR_INVALID;
+  const Engine& e = *c->e;
+  *out = pet_memory_plan_info{};
+  out->atoms = e.last_pk.n_atoms, out->max_neighbors = e.last_pk.M, out->edges = e.last_pk.E;
+  out->tier = e.model->last_tier(), out->estimate_bytes = e.model->last_estimate();
+  out->budget_bytes = e.memory_budget;
+  out->pool_bytes = e.save_arena.capacity() + e.tmp_arena.capacity() + e.nbr_arena.capacity();
+  return PET_OK;
+}
+int pet_memory_report(const pet_calc* c, char* buf, size_t len) {
+  pet_memory_plan_info p;
+  if (!buf || !len || pet_memory_plan(c, &p) != PET_OK) return PET_ERR_INVALID;
+  size_t free_b = 0, total_b = 0;
+  cudaSetDevice(c->e->device);
+  cudaMemGetInfo(&free_b, &total_b);
+  const double GiB = 1024.0 * 1024.0 * 1024.0;
+  snprintf(buf, len,
+           "  %d atoms, %d neighbours at most, %ld edges; recompute %s\n"
+           "  estimated %.2f GiB for this tier, budget %.2f GiB (0: what the device has)\n"
+           "  pools hold %.2f GiB; device %.2f GiB free of %.2f GiB\n",
+           p.atoms, p.max_neighbors, p.edges, petb::recompute_name(p.tier), p.estimate_bytes / GiB, p.budget_bytes / GiB,
+           p.pool_bytes / GiB, free_b / GiB, total_b / GiB);
+  return PET_OK;
+}
+int pet_recommended_batch_atoms(const pet_calc* c) {
+  if (!c || !c->e) return 0;
+  const Engine& e = *c->e;
+  if (e.max_batch_atoms > 0) return e.max_batch_atoms;
+  // before anything has been evaluated the neighbour count is unknown: sizes that fit a small card
+  const double pool = double(e.save_arena.capacity() + e.tmp_arena.capacity() + e.nbr_arena.capacity());
+  if (pool <= 0.0 || e.peak_slots < 4096.0 || e.last_pk.M <= 0) return e.ckpt.hypers.feedforward ? 4096 : 2048;
+  size_t free_b = 0, total_b = 0;
+  cudaSetDevice(e.device);
+  if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) return 4096;
+  const double per_slot = pool / e.peak_slots;
+  const double budget = e.memory_budget ? double(e.memory_budget) : 0.8 * double(total_b);
+  const double by_memory = budget / per_slot / double(e.last_pk.M + 1);
+  const double by_throughput = double(1 << 22) / double(e.last_pk.M + 1);  // past ~4 M edge slots a batch gains nothing
+  const double atoms = std::min(by_memory, by_throughput);
+  return int(std::min(std::max(atoms, 256.0), 65536.0));
+}
 long long pet_kernel_launches(const pet_calc* c) { return c && c->e ? c->e->st.launches : 0; }
 long long pet_graph_replays(const pet_calc* c) { return c && c->e ? c->e->graph_replays : 0; }
 long long pet_oom_recoveries(const pet_calc* c) { return c && c->e ? c->e->oom_recoveries : 0; }

@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstddef>
 #include <cstdint>
 #include <cstdio>
@@ -61,8 +62,11 @@ class Arena {
       }
       ++cur_;
     }
-    size_t size = next_block_;
-    while (size < bytes) size *= 2;
+    // a block of the pool's step, or exactly this allocation when that is larger: nothing is rounded up to a power
+    // of two, so a pool of a hundred gigabytes wastes none of it; the step grows with the pool so that a large pool
+    // is not made of thousands of small blocks
+    const size_t size = std::max(next_block_, bytes);
+    next_block_ = std::max(next_block_, std::min(capacity() / 4, size_t(2) << 30));
     Block b;
     if (g_fail_alloc_in >= 0 && g_fail_alloc_in-- == 0)
       throw Error(4, "cudaMalloc: out of memory (injected for a test)");
@@ -96,6 +100,18 @@ class Arena {
     for (auto& b : blocks_) b.used = 0;
     cur_ = 0;
     used_total_ = 0;
+  }
+  // Before a pass whose need is known: one block of at least `bytes`, so that the pass allocates nothing on the way
+  // and the layout is the steady one from the first evaluation on. Only while nothing of the pool is in use.
+  void reserve(size_t bytes) {
+    if (used_total_ != 0 || capacity() >= bytes) return;
+    release();
+    Block b;
+    if (g_fail_alloc_in >= 0 && g_fail_alloc_in-- == 0) throw Error(4, "cudaMalloc: out of memory (injected for a test)");
+    PETB_CUDA(cudaMalloc(&b.ptr, bytes));
+    b.size = bytes;
+    blocks_.push_back(b);
+    ++generation_;
   }
   // A stack discipline for temporaries: everything allocated after mark() is handed
   // back by rewind(). Kernels run in stream order, so a later pass may reuse it.

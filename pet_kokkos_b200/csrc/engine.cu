@@ -144,6 +144,13 @@ Engine::Engine(const std::string& json, const std::string& weights, const pet_op
   cache_neighbors = (opts && opts->cache_neighbors > 0) || env_int("PET_CACHE_NEIGHBORS", 0) != 0;
   memory_budget = opts ? opts->memory_budget_bytes : 0;
   max_batch_atoms = opts && opts->max_batch_atoms > 0 ? opts->max_batch_atoms : 0;
+  recompute = opts && opts->recompute > 0 ? opts->recompute : RECOMPUTE_AUTO;
+  if (recompute == RECOMPUTE_AUTO)
+    if (const char* e = std::getenv("PET_RECOMPUTE")) {  // auto | never | wide | layers (Options::recompute)
+      const std::string v(e);
+      recompute = v == "never" ? RECOMPUTE_NEVER : v == "wide" ? RECOMPUTE_WIDE : v == "layers" ? RECOMPUTE_LAYERS : RECOMPUTE_AUTO;
+    }
+  if (recompute > RECOMPUTE_LAYERS) throw Error(2, "pet: unknown recompute tier " + std::to_string(recompute));
   PETB_CUDA(cudaStreamCreateWithFlags(&st.s, cudaStreamNonBlocking));
   PETB_CUDA(cudaEventCreate(&ev0));
   PETB_CUDA(cudaEventCreate(&ev1));
@@ -291,18 +298,42 @@ void Engine::drop_graphs() {
 // One pass of the network over packed edges: eagerly, or as a recorded CUDA graph once the same shapes and
 // buffers have been seen before (eager first, capture second, replay after). The key holds everything the
 // recorded launches depend on besides the weights: shapes, the input pointers, and the pools' generations.
+// What a pass may keep: the tier asked for, or under Auto the first one whose estimate fits the budget (the given
+// one, else nine tenths of what the device has free plus what the pools already hold).
+RunOptions Engine::run_options() const {
+  RunOptions o;
+  o.recompute = recompute, o.tier_floor = tier_floor;
+  o.budget = memory_budget;
+  if (o.budget == 0 && recompute == RECOMPUTE_AUTO) {
+    size_t free_b = 0, total_b = 0;
+    if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+      const double pool = double(save_arena.capacity() + tmp_arena.capacity());
+      o.budget = size_t(std::min(double(free_b) + pool, double(total_b)) * 0.9);
+    }
+  }
+  return o;
+}
+
 void Engine::run_model(const PackedEdges& pk, bool forces) {
   taps.clear();
+  const RunOptions ro = run_options();
+  const int tier = model->hypers().feedforward && forces ? model->choose_tier(ro, pk.N, pk.E) : int(RECOMPUTE_NEVER);
+  RunOptions fixed = ro;  // the tier is part of a recorded pass's key: run exactly the one chosen here
+  fixed.recompute = tier;
+  if (model->hypers().feedforward && forces) {  // size both pools for the pass before it starts
+    const MemoryNeed need = model->memory_need(tier, pk.N, pk.E, pk.n_live);
+    save_arena.reserve(need.save), tmp_arena.reserve(need.tmp);
+  }
   // An exchanged list calls back into the engine in the middle of the pass: it is never recorded.
   const bool eager_only = !graphs || want_taps || prof.on || pk.exchange != nullptr;
   if (eager_only) {
-    last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, want_taps ? &taps : nullptr);
+    last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, want_taps ? &taps : nullptr, fixed);
     last_pk = pk, have_out = true;
     return;
   }
   auto ptr = [](const void* q) { return uint64_t(reinterpret_cast<uintptr_t>(q)); };
   const std::vector<uint64_t> key = {uint64_t(pk.N),      uint64_t(pk.E),     uint64_t(pk.M),       uint64_t(pk.B),
-                                     uint64_t(pk.n_atoms), uint64_t(pk.n_local), uint64_t(forces),   uint64_t(gemm_mode),
+                                     uint64_t(pk.n_atoms), uint64_t(pk.n_local), uint64_t(forces),   uint64_t(gemm_mode) | (uint64_t(tier) << 8),
                                      ptr(pk.off),          ptr(pk.center),     ptr(pk.species),      ptr(pk.reverse),
                                      ptr(pk.vec),          ptr(pk.dist),       ptr(pk.cut),          ptr(pk.atom_species),
                                      ptr(pk.soff),         save_arena.generation(), tmp_arena.generation(),
@@ -330,7 +361,7 @@ void Engine::run_model(const PackedEdges& pk, bool forces) {
   if (!seen) {  // first time: eagerly (the pools may still grow, which a capture cannot contain)
     if (graph_seen.size() >= 32) graph_seen.erase(graph_seen.begin());
     graph_seen.push_back(key);
-    last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, nullptr);
+    last_out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, nullptr, fixed);
     last_pk = pk, have_out = true;
     return;
   }
@@ -341,7 +372,7 @@ void Engine::run_model(const PackedEdges& pk, bool forces) {
   cudaGraph_t graph = nullptr;
   PETB_CUDA(cudaStreamBeginCapture(st.s, cudaStreamCaptureModeRelaxed));
   try {
-    g.out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, nullptr);
+    g.out = model->run(st, save_arena, tmp_arena, pk, forces, gemm_mode, nullptr, fixed);
   } catch (...) {
     cudaStreamEndCapture(st.s, &graph);
     if (graph) cudaGraphDestroy(graph);
@@ -592,6 +623,13 @@ void Engine::compute(const pet_system* systems, int B, bool forces, pet_results*
       have_out = false, verlet.valid = false;
       save_arena.release(), tmp_arena.release(), nbr_arena.release(), cache_arena.release();
       ++oom_recoveries;
+      // one structure cannot be cut: keep less of its forward instead (the reference's tier drop, src/model.cpp:952-971)
+      bool cuttable = false;
+      for (const auto& r : runs) cuttable = cuttable || r.second - r.first > 1;
+      if (!cuttable && recompute == RECOMPUTE_AUTO && model->hypers().feedforward && tier_floor < RECOMPUTE_LAYERS) {
+        tier_floor = std::max(tier_floor, model->last_tier()) + 1;
+        continue;
+      }
       std::vector<std::pair<int, int>> halved;
       for (const auto& r : runs) {
         const int n = r.second - r.first;
@@ -1113,6 +1151,18 @@ void Engine::gemm_host(int mode, bool w_transposed, int m, int n, int k, const f
   PETB_CUDA(cudaMemcpyAsync(dW, hw, 4 * size_t(n) * k, cudaMemcpyHostToDevice, st.s));
   GemmArgs a;
   a.A = dA, a.lda = k, a.B = dW, a.ldb = k, a.C = dC, a.ldc = n, a.M = m, a.N = n, a.K = k;
+  std::vector<uint16_t> w16;
+  if (mode == GEMM_BF16) {  // the weight again as bf16, round to nearest even, as a loaded weight is kept
+    w16.resize(size_t(n) * k);
+    for (size_t i = 0; i < w16.size(); ++i) {
+      uint32_t u;
+      std::memcpy(&u, &hw[i], 4);
+      w16[i] = uint16_t((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+    }
+    uint16_t* d16 = tmp_arena.alloc<uint16_t>(w16.size());
+    PETB_CUDA(cudaMemcpyAsync(d16, w16.data(), 2 * w16.size(), cudaMemcpyHostToDevice, st.s));
+    a.B16 = d16;
+  }
   gemm(st, tmp_arena, a, mode);
   PETB_CUDA(cudaMemcpyAsync(C, dC, 4 * size_t(m) * n, cudaMemcpyDeviceToHost, st.s));
   PETB_CUDA(cudaStreamSynchronize(st.s));

@@ -94,6 +94,9 @@ struct Engine {
   bool cache_neighbors = false;  // Options::cache_neighbors / PET_CACHE_NEIGHBORS
   size_t memory_budget = 0;      // Options::memory_budget_bytes; 0: what the device has
   int max_batch_atoms = 0;       // Options::max_batch_atoms; 0: no limit
+  int recompute = RECOMPUTE_AUTO;  // Options::recompute / PET_RECOMPUTE: how much of the forward the backward keeps
+  int tier_floor = RECOMPUTE_NEVER;  // raised when an evaluation of one structure ran out of memory under Auto
+  RunOptions run_options() const;
   double peak_slots = 0.0;       // the most atoms x (neighbours + 1) one evaluation has held: samples bytes per slot
   long long batch_splits = 0;    // batches evaluated as more than one piece
   long long oom_recoveries = 0;  // evaluations retried after the device ran out of memory

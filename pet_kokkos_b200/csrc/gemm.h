@@ -38,6 +38,9 @@ struct GemmArgs {
   // Non-zero: B + b_lo_offset holds the low parts of B's 3xTF32 split, computed once when the weights were loaded
   // (same shape and pitch); the tensor-core kernel then loads them instead of splitting every B tile it stages.
   size_t b_lo_offset = 0;
+  // B again as bf16 [N,K] with the same pitch in elements (round to nearest even, made when the weights were loaded):
+  // what the bf16 mode's tensor-core kernel reads. Null: the bf16 mode runs this GEMM as tf32.
+  const uint16_t* B16 = nullptr;
   float* C = nullptr;        // [M, N] (EPI_SWIGLU: [M,N/2]; EPI_SWIGLU_BWD: [M,2N])
   int ldc = 0;
   int M = 0, N = 0, K = 0;

@@ -24,10 +24,16 @@
 //               are computed once when the model is loaded and arrive by a third TMA map. The
 //               issuer accumulates hi.lo + lo.hi + hi.hi in fp32, small terms first: fp32-class
 //               accuracy without reading the activations from L2 a second time.
+//               (bf16 mode) converter: the activations stay fp32 in memory; for every landed stage these warps
+//               round A's 128 x 32 fp32 slab to bf16 into a second, half-sized tile in the 64-byte-swizzled
+//               K-major layout the tensor core reads, while the weights arrive as bf16 (converted once when
+//               the model was loaded) by their own TMA map. The issuer then runs tcgen05.mma kind::f16 (K = 16
+//               per instruction) on the two bf16 tiles: twice the tf32 rate on half the operand bytes.
 // No TMA load here uses cluster multicast. Every wait is bounded: a wait that runs out sets an
 // error word the host checks, every role then leaves its loop, and the CTA still reaches its
 // tensor-memory release.
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include <cstdlib>
 #include <mutex>
@@ -99,6 +105,17 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(TBM >> 4) << 24);
 }
 
+// kind::f16 with bf16 operands: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), K-major, N >> 3, M >> 4.
+__host__ __device__ constexpr uint32_t idesc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(TBM >> 4) << 24);
+}
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
@@ -125,18 +142,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <int BN, int STAGES, bool X3>
+enum TcMode { TC_TF32 = 0, TC_X3 = 1, TC_BF16 = 2 };
+
+template <int BN, int STAGES, int MODE>
 struct Smem {
+  static constexpr bool X3 = MODE == TC_X3, B16 = MODE == TC_BF16;
   // fp32 elements of K per stage: a 128-byte swizzled row, or half of one where four stages of the widest 3x tile
   // have to fit (finer stages hide the load latency that two coarse ones cannot)
   static constexpr int BK = (X3 && BN == 256 && STAGES == 4) ? 16 : 32;
-  static constexpr int kA = TBM * BK * 4, kB = BN * BK * 4;  // bytes per stage
-  static constexpr int kHi = kA + kB;
-  static constexpr int kStage = kHi * (X3 ? 2 : 1);            // with the lo tiles in the 3x mode
+  static constexpr int kA = TBM * BK * 4;                     // A as it lands, fp32
+  static constexpr int kA16 = B16 ? TBM * BK * 2 : 0;         // A again as bf16 (64-byte rows)
+  static constexpr int kB = BN * BK * (B16 ? 2 : 4);          // B: fp32, or bf16 straight from memory
+  static constexpr int kHi = kA + kA16 + kB;
+  static constexpr int kStage = kHi * (X3 ? 2 : 1);           // with the lo tiles in the 3x mode
   static constexpr int kTiles = STAGES * kStage;
   static constexpr int kPads = kEpiWarps * 32 * kPad * 4;
   static constexpr int kTotal = kTiles + kPads + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr int kThreads = X3 ? 512 : 384;
+  static constexpr int kThreads = (X3 || B16) ? 512 : 384;
 };
 
 // The low part of the 3xTF32 split. The tensor core reads the top 19 bits of an fp32 operand (sign, exponent, 10
@@ -149,11 +171,12 @@ __device__ __forceinline__ float tf32_lo(float x) {
   return __uint_as_float(__float_as_uint(x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u)) + 0x1000u);
 }
 
-template <int EPI, int BN, int STAGES, bool X3>
-__global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
+template <int EPI, int BN, int STAGES, int MODE>
+__global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
     k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const __grid_constant__ CUtensorMap map_blo, GemmArgs p, int* err) {
-  using L = Smem<BN, STAGES, X3>;
+  using L = Smem<BN, STAGES, MODE>;
+  constexpr bool X3 = L::X3, B16 = L::B16;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* pads = reinterpret_cast<float*>(tiles + L::kTiles);
@@ -206,7 +229,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
           const bool b_lo = X3 && p.b_lo_offset != 0;  // B's low parts come from memory, not from the splitter
           mbar_expect_tx(full + s, L::kHi + (b_lo ? L::kB : 0));
           tma_load_2d(sa, &map_a, full + s, kb * TBK, m0);
-          tma_load_2d(sa + L::kA, &map_b, full + s, kb * TBK, n0);
+          tma_load_2d(sa + L::kA + L::kA16, &map_b, full + s, kb * TBK, n0);
           if (b_lo) tma_load_2d(sa + L::kHi + L::kA, &map_blo, full + s, kb * TBK, n0);
         }
         if (!ok) break;
@@ -223,9 +246,17 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
         const uint32_t acc = tmem + uint32_t(b * BN);
         for (int kb = 0; ok && kb < nkb; ++kb, ++g) {
           const int s = g % STAGES;
-          if (!(ok = mbar_wait(X3 ? split + s : full + s, (g / STAGES) & 1, abort_flag))) break;
+          if (!(ok = mbar_wait((X3 || B16) ? split + s : full + s, (g / STAGES) & 1, abort_flag))) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a0 = smem_u32(tiles + size_t(s) * L::kStage), b0 = a0 + L::kA;
+          const uint32_t a0 = smem_u32(tiles + size_t(s) * L::kStage), b0 = a0 + L::kA + L::kA16;
+          if (B16) {  // 16 bf16 = 32 bytes along K per instruction, on the converted A tile and the bf16 B tile
+            constexpr uint32_t idesc16 = idesc_bf16(BN);
+#pragma unroll
+            for (int k = 0; k < TBK / 16; ++k)
+              mma_bf16(acc, smem_desc<16>(a0 + L::kA + 32 * k), smem_desc<16>(b0 + 32 * k), idesc16, (kb | k) != 0);
+            mma_commit(empty + s);
+            continue;
+          }
 #pragma unroll
           for (int k = 0; k < TBK / 8; ++k) {  // 8 tf32 = 32 bytes along K per instruction
             const uint64_t da = smem_desc<TBK>(a0 + 32 * k), db = smem_desc<TBK>(b0 + 32 * k);
@@ -293,6 +324,34 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, X3>::kThreads, 1)
             }
           }
         }
+      }
+    }
+  } else if (B16 && warp >= kSplitWarp0) {
+    // A's fp32 slab (128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7)) rounded to bf16 into the tile beside
+    // it (64-byte rows, chunk c of row r at chunk c ^ ((r >> 1) & 3): the 64-byte swizzle). A thread owns a row: the
+    // eight lanes of a quarter warp then touch eight different 16-byte columns on the reads and on the writes.
+    const int r = threadIdx.x - kSplitWarp0 * 32;
+    int g = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+      for (int kb = 0; kb < nkb; ++kb, ++g) {
+        const int s = g % STAGES;
+        if (!(ok = mbar_wait(full + s, (g / STAGES) & 1, abort_flag))) break;
+        const uint8_t* src = tiles + size_t(s) * L::kStage + size_t(r) * 128;
+        uint8_t* dst = tiles + size_t(s) * L::kStage + L::kA + size_t(r) * 64;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float4 x = *reinterpret_cast<const float4*>(src + (((2 * c) ^ (r & 7)) << 4));
+          const float4 y = *reinterpret_cast<const float4*>(src + (((2 * c + 1) ^ (r & 7)) << 4));
+          const __nv_bfloat162 q0 = __floats2bfloat162_rn(x.x, x.y), q1 = __floats2bfloat162_rn(x.z, x.w);
+          const __nv_bfloat162 q2 = __floats2bfloat162_rn(y.x, y.y), q3 = __floats2bfloat162_rn(y.z, y.w);
+          uint4 o;
+          o.x = *reinterpret_cast<const uint32_t*>(&q0), o.y = *reinterpret_cast<const uint32_t*>(&q1);
+          o.z = *reinterpret_cast<const uint32_t*>(&q2), o.w = *reinterpret_cast<const uint32_t*>(&q3);
+          *reinterpret_cast<uint4*>(dst + ((c ^ ((r >> 1) & 3)) << 4)) = o;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes visible to the tensor core
+        mbar_arrive(split + s);
       }
     }
   } else if (X3 && warp >= kSplitWarp0) {
@@ -382,15 +441,30 @@ CUtensorMap make_map(const float* base, int rows, int K, int ld, int box_rows, i
   return m;
 }
 
-template <int EPI, int BN, int STAGES, bool X3>
+// B [rows, K] bf16 row-major as a 2-D tensor map with a 32 x box_rows box (64-byte rows), 64-byte swizzle.
+CUtensorMap make_map_bf16(const uint16_t* base, int rows, int K, int ld, int box_rows) {
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+  const cuuint32_t box[2] = {32, cuuint32_t(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = state().encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(base), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw Error(5, "gemm: cuTensorMapEncodeTiled (bf16) failed with code " + std::to_string(int(r)));
+  return m;
+}
+
+template <int EPI, int BN, int STAGES, int MODE>
 void launch_tc(Stream& st, const GemmArgs& a) {
-  using L = Smem<BN, STAGES, X3>;
+  using L = Smem<BN, STAGES, MODE>;
   static_assert(L::kTotal <= 227 * 1024, "the tile pipeline does not fit shared memory");
   static SmemOptIn opted;
-  auto kernel = k_gemm_tc<EPI, BN, STAGES, X3>;
+  auto kernel = k_gemm_tc<EPI, BN, STAGES, MODE>;
   opt_in_shared_memory(kernel, L::kTotal, opted);
-  const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM, L::BK), mb = make_map(a.B, a.N, a.K, a.ldb, BN, L::BK);
-  const CUtensorMap mblo = a.b_lo_offset ? make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, BN, L::BK) : mb;
+  const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM, L::BK);
+  const CUtensorMap mb = L::B16 ? make_map_bf16(a.B16, a.N, a.K, a.ldb, BN) : make_map(a.B, a.N, a.K, a.ldb, BN, L::BK);
+  const CUtensorMap mblo = (L::X3 && a.b_lo_offset) ? make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, BN, L::BK) : mb;
   const long long tiles = (long long) cdiv(a.M, TBM) * cdiv(a.N, BN);
   const int grid = int(tiles < state().sms ? tiles : state().sms);
   kernel<<<grid, L::kThreads, L::kTotal, st.s>>>(ma, mb, mblo, a, state().err);
@@ -409,7 +483,7 @@ bool fine_stages() {
 
 template <int EPI>
 void dispatch_tc(Stream& st, const GemmArgs& a, int mode) {
-  const bool x3 = mode == GEMM_TF32X3;
+  const bool x3 = mode == GEMM_TF32X3, b16 = mode == GEMM_BF16;
   // The widest tile that still gives every SM a tile: a GEMM over the atoms' rows (a few thousand) would
   // otherwise run on a handful of CTAs with a long, latency-bound K loop each.
   const long long mt = cdiv(a.M, TBM);
@@ -419,15 +493,18 @@ void dispatch_tc(Stream& st, const GemmArgs& a, int mode) {
   else if (a.N % 128 == 0 && mt * (a.N / 128) >= sms) bn = 128;
   else if (a.N % 64 != 0) bn = a.N % 256 == 0 ? 256 : 128;  // ragged widths: a wide tile with a zero-filled edge
   if (bn == 256) {
-    if (x3) return fine_stages() ? launch_tc<EPI, 256, 4, true>(st, a) : launch_tc<EPI, 256, 2, true>(st, a);
-    return launch_tc<EPI, 256, 4, false>(st, a);
+    if (b16) return launch_tc<EPI, 256, 4, TC_BF16>(st, a);
+    if (x3) return fine_stages() ? launch_tc<EPI, 256, 4, TC_X3>(st, a) : launch_tc<EPI, 256, 2, TC_X3>(st, a);
+    return launch_tc<EPI, 256, 4, TC_TF32>(st, a);
   }
   if (bn == 128) {
-    if (x3) return launch_tc<EPI, 128, 3, true>(st, a);
-    return launch_tc<EPI, 128, 4, false>(st, a);
+    if (b16) return launch_tc<EPI, 128, 6, TC_BF16>(st, a);
+    if (x3) return launch_tc<EPI, 128, 3, TC_X3>(st, a);
+    return launch_tc<EPI, 128, 4, TC_TF32>(st, a);
   }
-  if (x3) return launch_tc<EPI, 64, 4, true>(st, a);
-  return launch_tc<EPI, 64, 6, false>(st, a);
+  if (b16) return launch_tc<EPI, 64, 6, TC_BF16>(st, a);
+  if (x3) return launch_tc<EPI, 64, 4, TC_X3>(st, a);
+  return launch_tc<EPI, 64, 6, TC_TF32>(st, a);
 }
 
 }  // namespace
@@ -445,7 +522,9 @@ bool gemm_tensor_usable(const GemmArgs& a, int mode) {
 }
 
 void gemm_tensor(Stream& st, Arena&, const GemmArgs& a, int mode) {
-  if (mode == GEMM_BF16) mode = GEMM_TF32;  // operands are kept in fp32: the bf16 mode runs the tf32 kernel
+  // a GEMM without a bf16 copy of its second operand (a caller's own matrix) or with rows that a bf16 TMA map cannot
+  // stride runs as tf32, which is more exact
+  if (mode == GEMM_BF16 && (!a.B16 || a.ldb % 8 || (reinterpret_cast<uintptr_t>(a.B16) & 15))) mode = GEMM_TF32;
   switch (a.epi) {
     case EPI_PLAIN: return dispatch_tc<EPI_PLAIN>(st, a, mode);
     case EPI_SILU: return dispatch_tc<EPI_SILU>(st, a, mode);

@@ -253,16 +253,18 @@ Model::~Model() {
 
 namespace {
 
-// The attention mode that goes with a GEMM mode unless PET_ATTN names one (native | tf32x3), as the reference's
-// Options::attention / PET_ATTN (include/pet/calculator.hpp:46-49): Native with native GEMMs, TF32x3 otherwise.
-bool attention_on_tensor_cores(int gemm_mode) {
+// The attention mode that goes with a GEMM mode unless PET_ATTN names one (native | tf32x3 | tf32), as the reference's
+// Options::attention / PET_ATTN (include/pet/calculator.hpp:46-49): Native with native GEMMs, TF32x3 with 3xTF32 GEMMs,
+// and the single-pass TF32 form with the tf32 and bf16 speed modes.
+int attention_mode_for(int gemm_mode) {
   static const int forced = [] {
     const char* e = std::getenv("PET_ATTN");
     if (!e) return -1;
     const std::string v(e);
-    return v == "native" ? 0 : (v == "tf32x3" || v == "3xtf32") ? 1 : -1;
+    return v == "native" ? int(ATTN_NATIVE) : (v == "tf32x3" || v == "3xtf32") ? int(ATTN_TF32X3) : v == "tf32" ? int(ATTN_TF32) : -1;
   }();
-  return forced >= 0 ? forced == 1 : gemm_mode != GEMM_NATIVE;
+  if (forced >= 0) return forced;
+  return gemm_mode == GEMM_NATIVE ? ATTN_NATIVE : gemm_mode == GEMM_TF32X3 ? ATTN_TF32X3 : ATTN_TF32;
 }
 
 struct Gemms {
@@ -274,42 +276,42 @@ struct Gemms {
   void linear(float* out, const float* in, const Mat& W, const float* bias, int M, const float* res = nullptr,
               int res_row0 = 0) const {
     GemmArgs a;
-    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.C = out, a.ldc = W.rows;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.B16 = W.w16, a.C = out, a.ldc = W.rows;
     a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.res = res, a.ldr = W.rows, a.res_row0 = res_row0;
     gemm(st, tmp, a, mode);
   }
   // out = silu(pre), pre = in . W^T + bias, kept when `pre` is given
   void linear_silu(float* out, float* pre, const float* in, const Mat& W, const float* bias, int M) const {
     GemmArgs a;
-    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.C = out, a.ldc = W.rows;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.B16 = W.w16, a.C = out, a.ldc = W.rows;
     a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.pre = pre, a.ldp = W.rows, a.epi = EPI_SILU;
     gemm(st, tmp, a, mode);
   }
   // pre[M, 2F] = in . W^T + bias (interleaved v, g); h[M, F] = v * sigmoid(g)
   void swiglu_in(float* h, float* pre, const float* in, const Mat& W, const float* bias, int M) const {
     GemmArgs a;
-    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.C = h, a.ldc = W.rows / 2;
+    a.A = in, a.lda = W.cols, a.B = W.w, a.ldb = W.cols, a.b_lo_offset = W.lo_off, a.B16 = W.w16, a.C = h, a.ldc = W.rows / 2;
     a.M = M, a.N = W.rows, a.K = W.cols, a.bias = bias, a.pre = pre, a.ldp = W.rows, a.epi = EPI_SWIGLU;
     gemm(st, tmp, a, mode);
   }
   // in_adj[M, W.cols] (+)= out_adj[M, W.rows] . W
   void linear_bwd(float* in_adj, const float* out_adj, const Mat& W, int M, bool acc) const {
     GemmArgs a;
-    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.b_lo_offset = W.lo_off, a.C = in_adj, a.ldc = W.cols;
+    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.b_lo_offset = W.lo_off, a.B16 = W.wt16, a.C = in_adj, a.ldc = W.cols;
     a.M = M, a.N = W.cols, a.K = W.rows, a.res = acc ? in_adj : nullptr, a.ldr = W.cols;
     gemm(st, tmp, a, mode);
   }
   // grad[M, W.cols] = (out_adj . W) * silu'(pre)
   void linear_silu_bwd(float* grad, const float* out_adj, const Mat& W, const float* pre, int M) const {
     GemmArgs a;
-    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.b_lo_offset = W.lo_off, a.C = grad, a.ldc = W.cols;
+    a.A = out_adj, a.lda = W.rows, a.B = W.wt, a.ldb = W.rows, a.b_lo_offset = W.lo_off, a.B16 = W.wt16, a.C = grad, a.ldc = W.cols;
     a.M = M, a.N = W.cols, a.K = W.rows, a.pre = const_cast<float*>(pre), a.ldp = W.cols, a.epi = EPI_SILU_BWD;
     gemm(st, tmp, a, mode);
   }
   // pre_adj[M, 2F] from h_adj = out_adj . W_out and the saved pre
   void swiglu_out_bwd(float* pre_adj, const float* out_adj, const Mat& w_out, const float* pre, int M) const {
     GemmArgs a;
-    a.A = out_adj, a.lda = w_out.rows, a.B = w_out.wt, a.ldb = w_out.rows, a.b_lo_offset = w_out.lo_off, a.C = pre_adj, a.ldc = 2 * w_out.cols;
+    a.A = out_adj, a.lda = w_out.rows, a.B = w_out.wt, a.ldb = w_out.rows, a.b_lo_offset = w_out.lo_off, a.B16 = w_out.wt16, a.C = pre_adj, a.ldc = 2 * w_out.cols;
     a.M = M, a.N = w_out.cols, a.K = w_out.rows, a.pre = const_cast<float*>(pre), a.ldp = 2 * w_out.cols;
     a.epi = EPI_SWIGLU_BWD;
     gemm(st, tmp, a, mode);
@@ -358,14 +360,75 @@ PassOut Model::finish(Stream& st, Arena& save, const PackedEdges& pk, bool grad,
   return out;
 }
 
-PassOut Model::run(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode, Taps* taps) {
-  if (h_.feedforward) return run_feedforward(st, save, tmp, pk, grad, mode, taps);
+PassOut Model::run(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode, Taps* taps,
+                   const RunOptions& opt) {
+  if (h_.feedforward) return run_feedforward(st, save, tmp, pk, grad, mode, taps, opt);
+  last_tier_ = RECOMPUTE_NEVER, last_estimate_ = 0;
   return run_residual(st, save, tmp, pk, grad, mode, taps);
 }
 
 // ---- the feedforward featurizer ---------------------------------------------------
+//
+// How much of the forward the backward keeps (the reference's Recompute tiers, include/pet/config.hpp:19-24,
+// src/feedforward.cpp:355-420): Never keeps every saved activation; Wide drops the two widest per block (the
+// attention's qkv [T,3D] and the edge MLP's pre-activation [E,2F]) and rebuilds them in the backward with one norm and
+// one GEMM each; Layers also keeps only each layer's inputs and re-runs one layer's forward at a time in the
+// backward. Under Wide and Layers the edge MLP runs a chunk of edge rows at a time, forward and backward, so its wide
+// temporaries are a chunk's. A row's GEMM result does not depend on which rows share its launch, so in the native
+// mode every tier gives the bits of Never.
 
-PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode, Taps* taps) {
+int Model::edge_chunk_rows(int E) {
+  if (const char* c = std::getenv("PET_EDGE_CHUNK"))
+    if (std::atoi(c) > 0) return std::atoi(c);
+  const int eighth = (E + 7) / 8;
+  return eighth > 65536 ? eighth : 65536;  // an eighth of the edges, never so few rows that the GEMMs run short
+}
+
+// Bytes the two pools hold at their fullest during one feedforward evaluation with forces under a tier: the sums of
+// what run_feedforward takes from `save` and the largest of its scopes of `tmp`, from the shapes; 3 % and a few MiB on
+// top for the pools' 256-byte rounding and the small per-atom and per-structure arrays of the force fold.
+MemoryNeed Model::memory_need(int tier, int N, int E, int n_live) const {
+  MemoryNeed need;
+  if (!h_.feedforward) return need;
+  const double D = h_.d_pet, H = h_.num_heads, F = h_.d_feedforward, Dn = h_.d_node, Dh = h_.d_head;
+  const double G = h_.num_gnn_layers, A = h_.num_attention_layers;
+  const double n = N, e = E, T = n + e, live = n_live;
+  const bool keep = tier == RECOMPUTE_NEVER, relayer = tier == RECOMPUTE_LAYERS;
+  const double c = keep ? e : std::min(e, double(edge_chunk_rows(E)));
+  // save: what lives for the whole pass
+  double save = (G + 1) * n * Dn + e * D + G * live * D + (relayer ? G * e * D : 0.0);
+  const double block = T * (2 * D + 2 * H) + n * (Dn + 4 * Dn + Dn) + (keep ? T * 3 * D + e * 2 * F : 0.0);
+  const double layer = (A + 1) * T * D + e * 3 * D + A * block + (relayer ? n * Dn : 0.0);
+  save += (relayer ? 1.0 : G) * layer;
+  save += 2 * n * Dh + 2 * e * Dh + 2 * n + e + 2 * n;              // readout
+  save += 5 * e + n * Dn + e * D + T * D + 6 * e + 30 * n;          // adjoints, edge gradients (doubles), forces, virials
+  // tmp: the fullest scope
+  const double attention_bwd = T * (5 * D + H) + (keep ? 0.0 : T * 4 * D);
+  const double attention_fwd = T * D + (keep ? 0.0 : T * 3 * D);
+  const double edge_mlp = c * (2 * F + D) + (keep ? c * F : c * (2 * F + D));
+  const double combination = e * 4 * D + 2 * live * D;
+  const double heads = 2 * n * Dh + 2 * e * Dh;
+  double tmp = std::max(std::max(attention_bwd, attention_fwd), std::max(std::max(edge_mlp, combination), heads));
+  tmp = std::max(tmp, n * 5 * Dn);
+  need.save = size_t(save * 4.0 * 1.03) + (size_t(8) << 20);
+  need.tmp = size_t(tmp * 4.0 * 1.03) + (size_t(8) << 20);
+  return need;
+}
+
+size_t Model::memory_estimate(int tier, int N, int E) const {
+  const MemoryNeed need = memory_need(tier, N, E, 0);
+  return need.save + need.tmp;
+}
+
+int Model::choose_tier(const RunOptions& o, int N, int E) const {
+  if (o.recompute != RECOMPUTE_AUTO) return o.recompute;
+  for (int tier = std::max(int(RECOMPUTE_NEVER), o.tier_floor); tier < RECOMPUTE_LAYERS; ++tier)
+    if (o.budget == 0 || memory_estimate(tier, N, E) <= o.budget) return tier;
+  return RECOMPUTE_LAYERS;
+}
+
+PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode, Taps* taps,
+                               const RunOptions& opt) {
   const int N = pk.N, E = pk.E, T = N + E, S = pk.M + 1;
   const int D = h_.d_pet, Dn = h_.d_node, Dh = h_.d_head, H = h_.num_heads, hd = h_.head_dim;
   const int G = h_.num_gnn_layers, A = h_.num_attention_layers;
@@ -373,24 +436,47 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
   const float sc = float(1.0 / (std::sqrt(double(hd)) * h_.attention_temperature));
   const size_t Ea = E > 0 ? E : 1, Ta = T > 0 ? T : 1, Na = N > 0 ? N : 1;
 
+  // taps name buffers that a recompute would overwrite or never keep: a tapped pass keeps everything
+  const int tier = (taps || !grad) ? int(RECOMPUTE_NEVER) : choose_tier(opt, N, E);
+  last_tier_ = tier, last_estimate_ = memory_estimate(tier, N, E);
+  const bool keep_wide = tier == RECOMPUTE_NEVER, relayer = grad && tier == RECOMPUTE_LAYERS;
+  const int chunk = keep_wide ? 0 : edge_chunk_rows(E);
+
   struct Block {
     float *tok, *qkv, *merged, *ml, *eps, *node_res, *pre_c, *pre_e;
   };
   struct Layer {
     float *cpre, *cph_pre, *out_edge;
-    float* remote_in = nullptr;  // [n_live, D] partner rows received from other ranks (an exchanged list)
     std::vector<Block> blk;
   };
-  std::vector<Layer> sav(G);
+  auto attention_args = [&](const Block& b, const float* qkv) {
+    AttnArgs at;
+    at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
+    at.mode = attention_mode_for(mode);
+    at.pairs = pk.pairs, at.T = T;
+    at.qkv = qkv, at.merged = b.merged, at.ml = b.ml;
+    return at;
+  };
+  // qkv = W_in . norm(tokens) + b
+  auto make_qkv = [&](float* qkv, const std::string& tl, float* tok) {
+    Scope s(tmp);
+    float* attn_in = tmp.alloc<float>(Ta * D);
+    norm_fwd(st, attn_in, tok, nullptr, vec(tl + ".norm_attention.weight"), nullptr, T, D);
+    gm.linear(qkv, attn_in, mat(tl + ".attention.input_linear.weight"), vec(tl + ".attention.input_linear.bias"), T);
+  };
+  // The edge MLP's first half on rows [r0, r0 + nr): pre = W_in . norm(eps) + b and, with `he`, v * sigmoid(g).
+  auto edge_mlp_in = [&](float* he, float* pre, const float* eps_rows, const std::string& tl, int nr) {
+    float* edge_norm = tmp.alloc<float>(size_t(nr) * D);
+    norm_fwd(st, edge_norm, const_cast<float*>(eps_rows), nullptr, vec(tl + ".norm_mlp.weight"), nullptr, nr, D);
+    gm.swiglu_in(he, pre, edge_norm, mat(tl + ".mlp.w_in.weight"), vec(tl + ".mlp.w_in.bias"), nr);
+  };
 
-  float* node = save.alloc<float>(Na * Dn);
-  float* input_edge = save.alloc<float>(Ea * D);
-  gather_rows(st, node, mat("node_embedders.0.weight").w, pk.atom_species, N, Dn);
-  gather_rows(st, input_edge, mat("edge_embedder.weight").w, pk.species, E, D);
-
-  for (int L = 0; L < G; ++L) {
+  // One message-passing layer forward: node_in [N,Dn] -> node_out, input_edge [E,D] updated in place, saves in `sl`
+  // (from `save`; the wide ones only with keep). `remote_in` [n_live, D] holds the partner rows of an exchanged list:
+  // asked for from the other ranks when `ask`, else the rows a first run of this layer received.
+  auto layer_forward = [&](int L, const float* node_in, float* node_out, float* input_edge, Layer& sl, bool keep,
+                           float* remote_in, bool ask) {
     const std::string g = "gnn_layers." + std::to_string(L), ls = std::to_string(L), c0 = g + ".compress.0";
-    Layer& sl = sav[L];
     sl.blk.resize(A);
     // Token buffers: block a's tokens are [input_node ; edge_cur]; its edge output is written
     // straight into the edge rows of block a+1's, the last one's being the layer's out_edge.
@@ -405,7 +491,8 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
       } else {
         const Mat& wi = mat(c0 + "@in");
         GemmArgs a;
-        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.b_lo_offset = wi.lo_off, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
+        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.b_lo_offset = wi.lo_off, a.B16 = wi.w16, a.C = cact, a.ldc = D;
+        a.M = E, a.N = D, a.K = D;
         a.bias = vec(c0 + "@b"), a.pre = sl.cpre, a.ldp = D, a.tab = mat(c0 + "@tab").w, a.sp = pk.species;
         a.wx = mat(c0 + "@x4").w, a.vec = pk.vec, a.dist = pk.dist, a.epi = EPI_COMPRESS;
         gemm(st, tmp, a, mode);
@@ -414,36 +501,29 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
     }
     tap(taps, "et" + ls, tokbuf[0] + size_t(N) * D, size_t(E) * D);
 
-    float* node_cur = node;
+    const float* node_cur = node_in;
     for (int a = 0; a < A; ++a) {
       const std::string tl = g + ".trans.layers." + std::to_string(a), tag = ls + "_" + std::to_string(a);
       Block& b = sl.blk[a];
+      const Mat &w_cin = mat(tl + ".center_mlp.w_in.weight"), &w_ein = mat(tl + ".mlp.w_in.weight");
       b.tok = tokbuf[a];
-      b.qkv = save.alloc<float>(Ta * 3 * D);
       b.merged = save.alloc<float>(Ta * D);
       b.ml = save.alloc<float>(Ta * H * 2);
       b.eps = save.alloc<float>(Ta * D);  // rows < N: the attention output's atom rows; rows >= N: eps
       b.node_res = save.alloc<float>(Na * Dn);
-      const Mat &w_cin = mat(tl + ".center_mlp.w_in.weight"), &w_ein = mat(tl + ".mlp.w_in.weight");
       b.pre_c = save.alloc<float>(Na * w_cin.rows);
-      b.pre_e = save.alloc<float>(Ea * w_ein.rows);
-      float* node_next = save.alloc<float>(Na * Dn);
-      float* edge_cur = b.tok + size_t(N) * D;
+      b.qkv = keep ? save.alloc<float>(Ta * 3 * D) : nullptr;
+      b.pre_e = keep ? save.alloc<float>(Ea * w_ein.rows) : nullptr;
+      float* node_next = a + 1 == A ? node_out : save.alloc<float>(Na * Dn);
       float* edge_next = tokbuf[a + 1] + size_t(N) * D;
 
       gm.linear(b.tok, node_cur, mat(tl + ".center_contraction.weight"), vec(tl + ".center_contraction.bias"), N);
       {
         Scope s1(tmp);
-        float* attn_in = tmp.alloc<float>(Ta * D);
-        norm_fwd(st, attn_in, b.tok, nullptr, vec(tl + ".norm_attention.weight"), nullptr, T, D);
-        gm.linear(b.qkv, attn_in, mat(tl + ".attention.input_linear.weight"), vec(tl + ".attention.input_linear.bias"), T);
+        float* qkv = keep ? b.qkv : tmp.alloc<float>(Ta * 3 * D);
+        make_qkv(qkv, tl, b.tok);
+        attention_forward(st, attention_args(b, qkv));
       }
-      AttnArgs at;
-      at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
-      at.tensor = attention_on_tensor_cores(mode);
-      at.pairs = pk.pairs, at.T = T;
-      at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml;
-      attention_forward(st, at);
       tap(taps, "merged" + tag, b.merged, size_t(T) * D);
       // attn_out = merged W_out^T + b; its edge rows take the residual: eps = attn_out + edge_cur.
       gm.linear(b.eps, b.merged, mat(tl + ".attention.output_linear.weight"), vec(tl + ".attention.output_linear.bias"), T,
@@ -458,21 +538,20 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
         gm.swiglu_in(hc, b.pre_c, node_norm, w_cin, vec(tl + ".center_mlp.w_in.bias"), N);
         gm.linear(node_next, hc, mat(tl + ".center_mlp.w_out.weight"), vec(tl + ".center_mlp.w_out.bias"), N, b.node_res, 0);
       }
-      {
+      const int rows = keep || chunk <= 0 ? (E > 0 ? E : 1) : chunk;
+      for (int r0 = 0; r0 < E; r0 += rows) {
+        const int nr = std::min(rows, E - r0);
         Scope s3(tmp);
-        float* eps_e = b.eps + size_t(N) * D;
-        float* edge_norm = tmp.alloc<float>(Ea * D);
-        float* he = tmp.alloc<float>(Ea * (w_ein.rows / 2));
-        norm_fwd(st, edge_norm, eps_e, nullptr, vec(tl + ".norm_mlp.weight"), nullptr, E, D);
-        gm.swiglu_in(he, b.pre_e, edge_norm, w_ein, vec(tl + ".mlp.w_in.bias"), E);
-        gm.linear(edge_next, he, mat(tl + ".mlp.w_out.weight"), vec(tl + ".mlp.w_out.bias"), E, eps_e, 0);
+        float* eps_rows = b.eps + (size_t(N) + r0) * D;
+        float* he = tmp.alloc<float>(size_t(nr) * (w_ein.rows / 2));
+        float* pre = keep ? b.pre_e + size_t(r0) * w_ein.rows : tmp.alloc<float>(size_t(nr) * w_ein.rows);
+        edge_mlp_in(he, pre, eps_rows, tl, nr);
+        gm.linear(edge_next + size_t(r0) * D, he, mat(tl + ".mlp.w_out.weight"), vec(tl + ".mlp.w_out.bias"), nr, eps_rows, 0);
       }
-      (void) edge_cur;
       node_cur = node_next;
       tap(taps, "node" + tag, node_cur, size_t(N) * Dn);
       tap(taps, "edge" + tag, edge_next, size_t(E) * D);
     }
-    node = node_cur;
     sl.out_edge = tokbuf[A] + size_t(N) * D;
     sl.cph_pre = save.alloc<float>(Ea * 2 * D);
     {
@@ -481,12 +560,12 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
       float* cph = tmp.alloc<float>(Ea * 2 * D);
       RemoteRows remote;
       if (pk.exchange) {  // edges to ghosts read their partners' rows from the ghosts' ranks (src/feedforward.cpp:171-179)
-        const size_t La = size_t(pk.n_live > 0 ? pk.n_live : 1) * D;
-        float* send = tmp.alloc<float>(La);
-        sl.remote_in = save.alloc<float>(La);
-        gather_live(st, send, sl.out_edge, D, 0, pk.live_packed, pk.n_live, D);
-        exchange_rows(st, pk, send, sl.remote_in, D);
-        remote = RemoteRows{pk.remote_of, sl.remote_in};
+        if (ask) {
+          float* send = tmp.alloc<float>(size_t(pk.n_live > 0 ? pk.n_live : 1) * D);
+          gather_live(st, send, sl.out_edge, D, 0, pk.live_packed, pk.n_live, D);
+          exchange_rows(st, pk, send, remote_in, D);
+        }
+        remote = RemoteRows{pk.remote_of, remote_in};
       }
       concat_norm_fwd(st, comb, sl.out_edge, pk.reverse, input_edge, vec("combination_norms." + ls + ".weight"),
                       vec("combination_norms." + ls + ".bias"), E, D, remote);
@@ -495,7 +574,29 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
                 input_edge, 0);
     }
     tap(taps, "input_edge" + ls, input_edge, size_t(E) * D);
+  };
+
+  // ---- forward ----
+  std::vector<Layer> sav(G);
+  std::vector<float*> node_at(G + 1), ie_at(G, nullptr), remote_in(G, nullptr);
+  for (int L = 0; L <= G; ++L) node_at[L] = save.alloc<float>(Na * Dn);  // the nodes entering layer L; [G]: the readout's
+  float* input_edge = save.alloc<float>(Ea * D);
+  if (pk.exchange)
+    for (int L = 0; L < G; ++L) remote_in[L] = save.alloc<float>(size_t(pk.n_live > 0 ? pk.n_live : 1) * D);
+  if (relayer)
+    for (int L = 0; L < G; ++L) ie_at[L] = save.alloc<float>(Ea * D);  // input_edge as it entered layer L
+  gather_rows(st, node_at[0], mat("node_embedders.0.weight").w, pk.atom_species, N, Dn);
+  gather_rows(st, input_edge, mat("edge_embedder.weight").w, pk.species, E, D);
+  for (int L = 0; L < G; ++L) {
+    if (relayer) {
+      PETB_CUDA(cudaMemcpyAsync(ie_at[L], input_edge, sizeof(float) * size_t(E) * D, cudaMemcpyDeviceToDevice, st.s));
+      Scope layer_saves(save);  // nothing of the layer is kept: the backward runs it again
+      layer_forward(L, node_at[L], node_at[L + 1], input_edge, sav[L], false, remote_in[L], true);
+    } else {
+      layer_forward(L, node_at[L], node_at[L + 1], input_edge, sav[L], grad && keep_wide, remote_in[L], true);
+    }
   }
+  float* node = node_at[G];
 
   // ---- readout (src/model.cpp:656-691) ----
   float* nh0_pre = save.alloc<float>(Na * Dh);
@@ -551,7 +652,13 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
   }
   for (int L = G - 1; L >= 0; --L) {
     const std::string g = "gnn_layers." + std::to_string(L), ls = std::to_string(L), c0 = g + ".compress.0";
-    const Layer& sl = sav[L];
+    Scope relayered(save);  // under Layers: this layer's saves, made again below and dropped after its backward
+    Layer again;
+    if (relayer) {
+      float* scratch_node = save.alloc<float>(Na * Dn);
+      layer_forward(L, node_at[L], scratch_node, ie_at[L], again, false, remote_in[L], false);
+    }
+    const Layer& sl = relayer ? again : sav[L];
     {
       Scope s7(tmp);
       float* cph_adj = tmp.alloc<float>(Ea * 2 * D);
@@ -564,7 +671,7 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
         const size_t La = size_t(pk.n_live > 0 ? pk.n_live : 1) * D;
         float* send = tmp.alloc<float>(La);
         remote_adj = tmp.alloc<float>(La);
-        remote = RemoteRows{pk.remote_of, sl.remote_in};
+        remote = RemoteRows{pk.remote_of, remote_in[L]};
         concat_norm_remote_bwd(st, send, cnorm_adj, sl.out_edge, vec("combination_norms." + ls + ".weight"), pk.live_packed,
                                pk.n_live, D, remote);
         exchange_rows(st, pk, send, remote_adj, D);
@@ -576,13 +683,24 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
       const std::string tl = g + ".trans.layers." + std::to_string(a);
       const Block& b = sl.blk[a];
       const Mat &w_cin = mat(tl + ".center_mlp.w_in.weight"), &w_ein = mat(tl + ".mlp.w_in.weight");
-      {  // the two MLPs: afterwards edge_adj and node_adj are eps's and node_res's
+      // the two MLPs: afterwards edge_adj and node_adj are eps's and node_res's
+      const int rows = b.pre_e || chunk <= 0 ? (E > 0 ? E : 1) : chunk;
+      for (int r0 = 0; r0 < E; r0 += rows) {
+        const int nr = std::min(rows, E - r0);
         Scope s8(tmp);
-        float* pre_adj = tmp.alloc<float>(Ea * w_ein.rows);
-        float* enorm_adj = tmp.alloc<float>(Ea * D);
-        gm.swiglu_out_bwd(pre_adj, edge_adj, mat(tl + ".mlp.w_out.weight"), b.pre_e, E);
-        gm.linear_bwd(enorm_adj, pre_adj, w_ein, E, false);
-        norm_bwd(st, edge_adj, enorm_adj, b.eps + size_t(N) * D, vec(tl + ".norm_mlp.weight"), false, E, D, 0);
+        const float* eps_rows = b.eps + (size_t(N) + r0) * D;
+        float* adj_rows = edge_adj + size_t(r0) * D;
+        const float* pre = b.pre_e ? b.pre_e + size_t(r0) * w_ein.rows : nullptr;
+        if (!pre) {  // the pre-activation was not kept: these rows' again
+          float* again_pre = tmp.alloc<float>(size_t(nr) * w_ein.rows);
+          edge_mlp_in(nullptr, again_pre, eps_rows, tl, nr);
+          pre = again_pre;
+        }
+        float* pre_adj = tmp.alloc<float>(size_t(nr) * w_ein.rows);
+        float* enorm_adj = tmp.alloc<float>(size_t(nr) * D);
+        gm.swiglu_out_bwd(pre_adj, adj_rows, mat(tl + ".mlp.w_out.weight"), pre, nr);
+        gm.linear_bwd(enorm_adj, pre_adj, w_ein, nr, false);
+        norm_bwd(st, adj_rows, enorm_adj, eps_rows, vec(tl + ".norm_mlp.weight"), false, nr, D, 0);
       }
       {
         Scope s9(tmp);
@@ -598,13 +716,16 @@ PassOut Model::run_feedforward(Stream& st, Arena& save, Arena& tmp, const Packed
         float* qkv_adj = tmp.alloc<float>(Ta * 3 * D);
         float* cfh = tmp.alloc<float>(Ta * H);
         float* attn_in_adj = tmp.alloc<float>(Ta * D);
+        const float* qkv = b.qkv;
+        if (!qkv) {
+          float* again_qkv = tmp.alloc<float>(Ta * 3 * D);
+          make_qkv(again_qkv, tl, b.tok);
+          qkv = again_qkv;
+        }
         gm.linear_bwd(tok_adj, node_adj, mat(tl + ".center_expansion.weight"), N, false);
         gm.linear_bwd(dmerged, tok_adj, mat(tl + ".attention.output_linear.weight"), T, false);
-        AttnArgs at;
-        at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
-      at.tensor = attention_on_tensor_cores(mode);
-        at.pairs = pk.pairs, at.T = T;
-        at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml, at.dmerged = dmerged, at.qkv_adj = qkv_adj, at.cfh = cfh;
+        AttnArgs at = attention_args(b, qkv);
+        at.dmerged = dmerged, at.qkv_adj = qkv_adj, at.cfh = cfh;
         attention_backward(st, at);
         cutoff_share(st, cf_adj, cfh, pk.cut, N, E, H);
         gm.linear_bwd(attn_in_adj, qkv_adj, mat(tl + ".attention.input_linear.weight"), T, false);
@@ -674,7 +795,7 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
       } else {
         const Mat& wi = mat(c0 + "@in");
         GemmArgs a;
-        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.b_lo_offset = wi.lo_off, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
+        a.A = input_edge, a.lda = D, a.B = wi.w, a.ldb = D, a.b_lo_offset = wi.lo_off, a.B16 = wi.w16, a.C = cact, a.ldc = D, a.M = E, a.N = D, a.K = D;
         a.bias = vec(c0 + "@b"), a.pre = sl.cpre, a.ldp = D, a.tab = mat(c0 + "@tab").w, a.sp = pk.species;
         a.wx = mat(c0 + "@x4").w, a.vec = pk.vec, a.dist = pk.dist, a.epi = EPI_COMPRESS;
         gemm(st, tmp, a, mode);
@@ -694,7 +815,7 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
       gm.linear(b.qkv, tokens, mat(tl + ".attention.input_linear.weight"), vec(tl + ".attention.input_linear.bias"), T);
       AttnArgs at;
       at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
-      at.tensor = attention_on_tensor_cores(mode);
+      at.mode = attention_mode_for(mode);
       at.pairs = pk.pairs, at.T = T;
       at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml;
       attention_forward(st, at);
@@ -821,7 +942,7 @@ PassOut Model::run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdg
         gm.linear_bwd(dmerged, s1_adj, mat(tl + ".attention.output_linear.weight"), T, false);
         AttnArgs at;
         at.N = N, at.H = H, at.hd = hd, at.S = S, at.sc = sc, at.off = pk.off, at.cut = pk.cut;
-      at.tensor = attention_on_tensor_cores(mode);
+      at.mode = attention_mode_for(mode);
         at.pairs = pk.pairs, at.T = T;
         at.qkv = b.qkv, at.merged = b.merged, at.ml = b.ml, at.dmerged = dmerged, at.qkv_adj = qkv_adj, at.cfh = cfh;
         attention_backward(st, at);

@@ -33,6 +33,24 @@ struct PassOut {
   bool has_forces = false;
 };
 
+// How much of the forward the backward keeps (the reference's Recompute, include/pet/config.hpp:19-24).
+enum RecomputeTier { RECOMPUTE_AUTO = 0, RECOMPUTE_NEVER = 1, RECOMPUTE_WIDE = 2, RECOMPUTE_LAYERS = 3 };
+inline const char* recompute_name(int t) {
+  static const char* names[] = {"auto", "never", "wide", "layers"};
+  return t >= 0 && t < 4 ? names[t] : "?";
+}
+
+// Bytes of the two scratch pools at their fullest during one evaluation.
+struct MemoryNeed {
+  size_t save = 0, tmp = 0;
+};
+
+struct RunOptions {
+  int recompute = RECOMPUTE_AUTO;    // a tier, or Auto: the first that fits `budget`
+  int tier_floor = RECOMPUTE_NEVER;  // Auto starts here (raised after an evaluation ran out of memory)
+  size_t budget = 0;                 // bytes the pools may hold; 0: no limit known, keep everything
+};
+
 class Model {
  public:
   explicit Model(const Checkpoint& ckpt);
@@ -56,11 +74,22 @@ class Model {
   // from `tmp`; both are rewound by the caller. With `taps`, named intermediates are
   // recorded as (pointer, element count) for inspection after the pass.
   PassOut run(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int gemm_mode,
-              std::map<std::string, std::pair<const float*, size_t>>* taps);
+              std::map<std::string, std::pair<const float*, size_t>>* taps, const RunOptions& opt = RunOptions());
+
+  // The tier the latest pass ran under and the bytes estimated for it (Calculator::memory_plan / memory_report).
+  int last_tier() const { return last_tier_; }
+  size_t last_estimate() const { return last_estimate_; }
+  // Bytes the pools hold for one evaluation with forces of N atoms and E kept edges under a tier.
+  size_t memory_estimate(int tier, int N, int E) const;
+  MemoryNeed memory_need(int tier, int N, int E, int n_live) const;
+  int choose_tier(const RunOptions& opt, int N, int E) const;
+  // Rows of a chunk of the edge MLP under Wide and Layers: an eighth of the edges, at least 64 Ki; PET_EDGE_CHUNK=rows
+  // overrides it so that small structures exercise the chunking (edge_chunk_rows, src/model.cpp:813-817).
+  static int edge_chunk_rows(int E);
 
  private:
   PassOut run_feedforward(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode,
-                          std::map<std::string, std::pair<const float*, size_t>>* taps);
+                          std::map<std::string, std::pair<const float*, size_t>>* taps, const RunOptions& opt);
   PassOut run_residual(Stream& st, Arena& save, Arena& tmp, const PackedEdges& pk, bool grad, int mode,
                        std::map<std::string, std::pair<const float*, size_t>>* taps);
   PassOut finish(Stream& st, Arena& save, const PackedEdges& pk, bool grad, float* x4_adj, const float* cutoff_adj,
@@ -75,6 +104,8 @@ class Model {
 
   Hypers h_;
   double scale_ = 1.0;
+  int last_tier_ = RECOMPUTE_NEVER;
+  size_t last_estimate_ = 0;
   double* comp_ = nullptr;  // [n_species] composition energies
   double* probes_ = nullptr;  // [n_probes_] the grid adaptive cutoff's radii (adaptive_probes, src/neighbors.cpp:23-27)
   int n_probes_ = 0;

@@ -254,6 +254,12 @@ def view_of(fields, exchange):
                         n_local=fields["n_local"], exchange=exchange)
 
 
+def make_exchange(calc, routing, dist=None, group=None):
+    """The exchange a rank of a torch.distributed job hands to its Calculator: NcclExchange over the job's NCCL
+    group."""
+    return NcclExchange(routing, group)
+
+
 def fold_to_owners(results, owner, n_atoms):
     """This rank's share of the whole cell: (energy, forces [n_atoms, 3] with ghost forces added onto their owners,
     virial [6])."""
