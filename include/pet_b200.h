@@ -205,6 +205,18 @@ int pet_compute(pet_calc* c, const pet_system* systems, int n_systems, int compu
 int pet_stage(pet_calc* c, const pet_system* systems, int n_systems);
 int pet_compute_staged(pet_calc* c, int compute_forces);
 int pet_fetch_results(pet_calc* c, pet_results* out);
+/* pet::DeviceGeom (include/pet/device_geometry.hpp; Calculator::stage, calculator.hpp:210-213): where the staged
+ * batch lies on the device. A caller that steps the structures there (a relaxation, MD) writes new positions into
+ * `positions` on the calculator's stream or after synchronizing with it, then calls pet_compute_staged. Cells change
+ * through pet_update_staged, which also refreshes the inverse cells and the search grid derived from them. */
+typedef struct pet_device_geom {
+  int n_structures, n_atoms;
+  double* positions;         /* [n_atoms * 3] device */
+  const double* cells;       /* [n_structures * 9] device */
+  const int* struct_id;      /* [n_atoms] device */
+  void* stream;              /* the calculator's cudaStream_t */
+} pet_device_geom;
+int pet_staged_geometry(pet_calc* c, pet_device_geom* out);
 /* Moves the staged positions (and cells when non-null) on the device from host arrays. */
 int pet_update_staged(pet_calc* c, const double* positions, const double* cells);
 
@@ -212,7 +224,8 @@ int pet_update_staged(pet_calc* c, const double* positions, const double* cells)
 int pet_compute_edges(pet_calc* c, const pet_edge_list* list, int compute_forces, int edge_gradients, pet_results* out);
 /* Calculator::set_neighbors(const EdgeListView&) (calculator.hpp:235). */
 int pet_set_neighbors(pet_calc* c, const pet_edge_list* list);
-/* Calculator::compute_step(positions, cell, forces, edge_gradients) (calculator.hpp:238). */
+/* Calculator::compute_step(positions, cell, forces, edge_gradients) (calculator.hpp:238). With out == NULL the
+ * results are left on the device (pet_device_results_of) and nothing is copied back or waited for. */
 int pet_compute_step(pet_calc* c, const double* positions, const double* cell, int compute_forces,
                      int edge_gradients, pet_results* out);
 /* Calculator::compute_step(const DeviceArrays&, cell) (calculator.hpp:259). */
@@ -307,6 +320,40 @@ int pet_debug_fetch(pet_calc* c, const char* name, float* out, size_t capacity, 
  * given PET_GEMM_* mode, on host arrays (weight_gemm, src/ops.cpp:18-24; pins
  * tests/test_gemm_modes.cpp:63-103). */
 int pet_gemm_host(pet_calc* c, int mode, int w_transposed, int m, int n, int k, const float* A, const float* W, float* C);
+
+/* A ready-made pet_exchange over NCCL: what an MD engine's pair style does around pet::Exchange
+ * (lammps/ML-PET/pair_pet.cpp:268-360 routing, :396-472 exchange_rows, :479-555 set_live / edges), inside the
+ * library. Rows of edges to ghosts are packed by a kernel, cross with ncclSend / ncclRecv on the calculator's own
+ * stream and are unpacked by a kernel: nothing synchronizes the host inside a pass. NCCL is taken from the process at
+ * run time (libnccl.so.2), so a program without it still links and runs on one GPU.
+ *   pet_nccl_unique_id          rank 0 makes the 128-byte id; the caller hands it to every rank (MPI, a file, ...)
+ *   pet_nccl_exchange_create    collective over all ranks. dest[n_remote][2]: for each of this rank's edges from an
+ *                               owned atom to a ghost, in list order, (rank, index among that rank's edges to ghosts) of
+ *                               its partner edge. owner[n_listed] (optional, with n_total): the atom of the whole cell
+ *                               that each listed atom is (itself or its ghost image), for pet_nccl_exchange_reduce.
+ *   pet_nccl_exchange_callbacks the pet_exchange to put into pet_edge_list.exchange (valid until destroy)
+ *   pet_nccl_exchange_reduce    after an evaluation: folds this rank's forces (device, [n_listed,3]) onto the cell's
+ *                               atoms in list order, adds energy and virial, sums over the ranks with one
+ *                               ncclAllReduce and copies [energy, virial(6), forces(3 n_total)] to out_host
+ *   pet_nccl_exchange_timing    CUDA-event time spent inside edges() since the last call, and how many calls
+ * All return PET_OK or an error code; pet_nccl_last_error() has the message (per host thread). */
+typedef struct pet_nccl_exchange pet_nccl_exchange;
+const char* pet_nccl_last_error(void);
+/* The static schedule pet_nccl_exchange_create derives from a rank's routing, as host arrays (no GPU, no NCCL
+ * needed): count[world] rows to and from each rank, send_slot[n_remote] / recv_slot[n_remote] each edge's row in the
+ * send buffer and its partner's row in the receive buffer, both laid out as one block per rank in rank order. */
+int pet_exchange_schedule(const int* dest, int n_remote, int world, int* count, int* send_slot, int* recv_slot);
+int pet_nccl_unique_id(char* id128);
+int pet_nccl_exchange_create(const char* id128, int rank, int world, int device, const int* dest, int n_remote,
+                             const int* owner, int n_listed, int n_total, pet_nccl_exchange** out);
+void pet_nccl_exchange_destroy(pet_nccl_exchange* x);
+const pet_exchange* pet_nccl_exchange_callbacks(pet_nccl_exchange* x);
+int pet_nccl_exchange_reduce(pet_nccl_exchange* x, const double* forces, const double* energy, const double* virial6,
+                             void* stream, double* out_host);
+int pet_nccl_exchange_timing(pet_nccl_exchange* x, int enable, double* ms, int* calls);
+/* The latest evaluation's results where they lie on the device (forces [n_atoms,3], energy [B], virial [B,6]; null
+ * before any evaluation or without forces) and the calculator's cudaStream_t: what pet_nccl_exchange_reduce reads. */
+int pet_device_results_of(pet_calc* c, pet_device_results* out, void** stream);
 
 /* C[m,n] = A[m,k] . W^T, W [n,k], fp32 on the CUDA cores, on host arrays, WITHOUT allocating
  * device memory. It has no counterpart in the reference. It exists for callers that cannot

@@ -21,7 +21,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler",
           "--expt-relaxed-constexpr", "-Xcudafe", "--diag_suppress=177"]
 # neighbour kernels: every fp64 product and sum rounded on its own (bit-exact edge decisions)
 PER_FILE = {"neighbors.cu": ["-fmad=false"]}
-SOURCES = ["checkpoint.cpp", "neighbors.cu", "ops.cu", "adaptive.cu", "attention.cu", "attention_tile.cu", "attention_mma.cu", "gemm_simt.cu", "gemm_tc.cu", "model.cu", "static_gemm.cu",
+SOURCES = ["checkpoint.cpp", "neighbors.cu", "ops.cu", "adaptive.cu", "attention.cu", "attention_tile.cu", "attention_mma.cu", "gemm_simt.cu", "gemm_tc.cu", "model.cu", "static_gemm.cu", "nccl_exchange.cu",
            "engine.cu", "capi.cu"]
 
 
@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         list(ex.map(run, jobs))
     objs = [str(OBJ / (s + ".o")) for s in SOURCES]
     if jobs or force or not OUT.exists():
-        cmd = [nvcc(), *ARCH, "-shared", "-o", str(OUT), *objs, "-lcudart", "-lcuda"]
+        cmd = [nvcc(), *ARCH, "-shared", "-o", str(OUT), *objs, "-lcudart", "-lcuda", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)

@@ -84,6 +84,11 @@ class PetDeviceResults(C.Structure):
                 ("virial", C.c_void_p)]
 
 
+class PetDeviceGeom(C.Structure):
+    _fields_ = [("n_structures", C.c_int), ("n_atoms", C.c_int), ("positions", C.c_void_p), ("cells", C.c_void_p),
+                ("struct_id", C.c_void_p), ("stream", C.c_void_p)]
+
+
 class PetTotals(C.Structure):
     _fields_ = [("energy", C.c_double), ("virial", C.c_double * 6)]
 
@@ -125,6 +130,17 @@ SIGNATURES = {
     "pet_supports": (C.c_int, [C.c_void_p, C.c_int]),
     "pet_workspace_bytes": (C.c_size_t, [C.c_void_p]),
     "pet_last_shapes": (C.c_int, [C.c_void_p, _P(C.c_int), _P(C.c_int), _P(C.c_int)]),
+    "pet_nccl_last_error": (C.c_char_p, []),
+    "pet_exchange_schedule": (C.c_int, [_P(C.c_int), C.c_int, C.c_int, _P(C.c_int), _P(C.c_int), _P(C.c_int)]),
+    "pet_nccl_unique_id": (C.c_int, [C.c_char_p]),
+    "pet_nccl_exchange_create": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, _P(C.c_int), C.c_int, _P(C.c_int), C.c_int,
+                                           C.c_int, _P(C.c_void_p)]),
+    "pet_nccl_exchange_destroy": (None, [C.c_void_p]),
+    "pet_nccl_exchange_callbacks": (C.c_void_p, [C.c_void_p]),
+    "pet_nccl_exchange_reduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, _P(C.c_double)]),
+    "pet_nccl_exchange_timing": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_double), _P(C.c_int)]),
+    "pet_staged_geometry": (C.c_int, [C.c_void_p, _P(PetDeviceGeom)]),
+    "pet_device_results_of": (C.c_int, [C.c_void_p, _P(PetDeviceResults), _P(C.c_void_p)]),
     "pet_memory_plan": (C.c_int, [C.c_void_p, _P(PetMemoryPlan)]),
     "pet_memory_report": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
     "pet_recommended_batch_atoms": (C.c_int, [C.c_void_p]),
@@ -144,6 +160,31 @@ SIGNATURES = {
     "pet_gemm_host": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P(C.c_float), _P(C.c_float),
                                 _P(C.c_float)]),
 }
+
+
+def model_search_dirs():
+    """Where a named model is looked for, in order (the reference's model_search_dirs, src/calculator.cpp:131-150):
+    $PET_MODEL_DIR (':'-separated), ./models and ., $XDG_DATA_HOME/pet/models (else ~/.local/share/pet/models)."""
+    dirs = [d for d in os.environ.get("PET_MODEL_DIR", "").split(":") if d] + ["models", "."]
+    if os.environ.get("XDG_DATA_HOME"):
+        dirs.append(os.path.join(os.environ["XDG_DATA_HOME"], "pet", "models"))
+    elif os.environ.get("HOME"):
+        dirs.append(os.path.join(os.environ["HOME"], ".local", "share", "pet", "models"))
+    return dirs
+
+
+def resolve_model(spec):
+    """A model name or a path prefix to (<spec>.json, <spec>.safetensors) (resolve_model, src/calculator.cpp:152-166).
+    This library ships no default model, so an empty spec is refused."""
+    if not spec:
+        raise ValueError("pet: no model given (this library ships no default model)")
+    if "/" in spec or os.path.exists(spec + ".json"):
+        return spec + ".json", spec + ".safetensors"
+    for d in model_search_dirs():
+        base = os.path.join(d, spec)
+        if os.path.exists(base + ".json") and os.path.exists(base + ".safetensors"):
+            return base + ".json", base + ".safetensors"
+    raise RuntimeError(f"pet: model '{spec}' not found in {', '.join(model_search_dirs())}")
 
 
 def load_library(path=None):
@@ -237,8 +278,8 @@ class Calculator:
                  cache_neighbors=None, memory_budget_bytes=0, max_batch_atoms=0, recompute=None):
         self._h = None
         self._lib = load_library()
-        if model_weights is None:  # a path prefix, as the reference's resolve_model accepts
-            model_json, model_weights = str(model_json) + ".json", str(model_json) + ".safetensors"
+        if model_weights is None:  # a path prefix or a model's name, as the reference's resolve_model accepts
+            model_json, model_weights = resolve_model(str(model_json))
         o = PetOptions()
         o.device, o.gemm_mode, o.graphs, o.md_fixed_shapes = device, -1, -1, -1
         if gemm is not None:
@@ -420,7 +461,11 @@ class Calculator:
         if v.cell is not None:
             keep["cell"] = np.ascontiguousarray(v.cell, dtype=np.float64).reshape(9)
             el.cell = _dptr(keep["cell"])
-        if v.exchange is not None:
+        if v.exchange is not None and getattr(v.exchange, "native_callbacks", None):
+            # callbacks that live in the library itself (exchange.NativeNcclExchange): no Python in the pass
+            el.exchange = C.cast(C.c_void_p(v.exchange.native_callbacks), _P(PetExchange))
+            keep["exchange"] = v.exchange
+        elif v.exchange is not None:
             ex = v.exchange
 
             def _guard(fn):
@@ -458,6 +503,22 @@ class Calculator:
         self._check(self._lib.pet_compute_step(self._h, _dptr(x), None if c is None else _dptr(c), int(compute_forces),
                                                int(edge_gradients), C.byref(pr)))
         return r
+
+    def compute_step_on_device(self, positions, cell=None, compute_forces=True):
+        """compute_step with the results left on the device: nothing is copied back or waited for. device_results()
+        says where they lie; an exchange's reduce() reads them there."""
+        x = np.ascontiguousarray(positions, dtype=np.float64).reshape(-1, 3)
+        if len(x) != self._session_atoms:
+            raise ValueError("positions do not match the list set by set_neighbors")
+        c = None if cell is None else np.ascontiguousarray(cell, dtype=np.float64).reshape(9)
+        self._step_keep = (x, c)  # the copy to the device is asynchronous: the arrays must outlive it
+        self._check(self._lib.pet_compute_step(self._h, _dptr(x), None if c is None else _dptr(c), int(compute_forces), 0, None))
+
+    def device_results(self):
+        """(PetDeviceResults with device addresses as integers, the calculator's cudaStream_t as an integer)."""
+        r, s = PetDeviceResults(), C.c_void_p()
+        self._check(self._lib.pet_device_results_of(self._h, C.byref(r), C.byref(s)))
+        return r, s.value or 0
 
     def compute_edges(self, view: EdgeListView, compute_forces=True, edge_gradients=True):
         """Calculator::compute_edges (calculator.hpp:227)."""

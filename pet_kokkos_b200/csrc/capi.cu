@@ -141,6 +141,27 @@ int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neig
   if (max_neighbors) *max_neighbors = c->e->last_pk.M;
   return PET_OK;
 }
+int pet_staged_geometry(pet_calc* c, pet_device_geom* out) {
+  if (!c || !c->e || !out) return PET_ERR_INVALID;
+  const Engine& e = *c->e;
+  *out = pet_device_geom{};
+  out->n_structures = e.geom.B, out->n_atoms = e.geom.Ntot;
+  out->positions = e.geom.pos, out->cells = e.geom.scell, out->struct_id = e.geom.sid;
+  out->stream = static_cast<void*>(e.st.s);
+  return PET_OK;
+}
+int pet_device_results_of(pet_calc* c, pet_device_results* out, void** stream) {
+  if (!c || !c->e || !out) return PET_ERR_INVALID;
+  const Engine& e = *c->e;
+  *out = pet_device_results{};
+  out->n_atoms = e.last_N;
+  if (e.have_out) {
+    out->energy = e.last_out.f.energy, out->per_atom_energy = e.last_out.per_atom;
+    if (e.last_out.has_forces) out->forces = e.last_out.f.forces, out->virial = e.last_out.f.vir6;
+  }
+  if (stream) *stream = static_cast<void*>(e.st.s);
+  return PET_OK;
+}
 int pet_memory_plan(const pet_calc* c, pet_memory_plan_info* out) {
   if (!c || !c->e || !out) return PET_ERR_INVALID;
   const Engine& e = *c->e;

@@ -907,6 +907,7 @@ void Engine::compute_step(const double* positions, const double* cell, bool forc
     g.resize(3 * size_t(md.E));
     PETB_CUDA(cudaMemcpyAsync(g.data(), so.eg_raw, 24 * size_t(md.E), cudaMemcpyDeviceToHost, st.s));
   }
+  if (!out) return;  // the results stay on the device (pet_device_results_of): a caller that reduces them there
   fetch(out);
   if (forces && edge_gradients && out && out->edge_gradient) {
     // A half list's pair gets both directions: g(i -> j) - g(j -> i)  (src/calculator.cpp:689-699).

@@ -254,9 +254,78 @@ def view_of(fields, exchange):
                         n_local=fields["n_local"], exchange=exchange)
 
 
-def make_exchange(calc, routing, dist=None, group=None):
-    """The exchange a rank of a torch.distributed job hands to its Calculator: NcclExchange over the job's NCCL
-    group."""
+class NativeNcclExchange:
+    """One rank's exchange with everything inside the library (csrc/nccl_exchange.cu): pack and unpack kernels and
+    ncclSend / ncclRecv on the calculator's stream, ghost forces folded on the device, one ncclAllReduce. Python only
+    hands over the routing and carries NCCL's id from rank 0 to the others (here with torch.distributed; an MD engine
+    would use MPI).
+
+    `dest` is this rank's routing ([n_remote, 2] from `route`), `owner` the global atom of every listed atom."""
+
+    def __init__(self, dest, owner, n_total, device, group=None, single=False):
+        from .calculator import load_library
+        self._lib = load_library()
+        self._h = None
+        idbuf = ctypes.create_string_buffer(128)
+        if single:  # one rank, no job around it: every ghost is an image of one of this rank's own atoms
+            rank, world = 0, 1
+            if self._lib.pet_nccl_unique_id(idbuf):
+                raise RuntimeError(self._lib.pet_nccl_last_error().decode())
+        else:
+            import torch
+            import torch.distributed as dist
+            rank, world = dist.get_rank(group), dist.get_world_size(group)
+            if rank == 0 and self._lib.pet_nccl_unique_id(idbuf):
+                raise RuntimeError(self._lib.pet_nccl_last_error().decode())
+            t = torch.frombuffer(bytearray(idbuf.raw), dtype=torch.uint8).clone()
+            t = t.cuda() if dist.get_backend(group) == "nccl" else t
+            dist.broadcast(t, src=0, group=group)
+            idbuf = ctypes.create_string_buffer(bytes(t.cpu().numpy().tobytes()), 128)
+        d = np.ascontiguousarray(np.asarray(dest).reshape(-1, 2), dtype=np.int32)
+        o = np.ascontiguousarray(owner, dtype=np.int32)
+        h = ctypes.c_void_p()
+        ip = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+        rc = self._lib.pet_nccl_exchange_create(idbuf, rank, world, int(device), ip(d), len(d), ip(o), len(o), int(n_total),
+                                                ctypes.byref(h))
+        if rc:
+            raise RuntimeError(self._lib.pet_nccl_last_error().decode())
+        self._h, self.n_total = h, int(n_total)
+        self.native_callbacks = self._lib.pet_nccl_exchange_callbacks(h)
+
+    def reduce(self, calc):
+        """After an evaluation of `calc`: the whole cell's [energy, virial(6), forces(3 n_total)] on every rank."""
+        r, stream = calc.device_results()
+        out = np.empty(7 + 3 * self.n_total)
+        rc = self._lib.pet_nccl_exchange_reduce(self._h, r.forces, r.energy, r.virial, stream,
+                                                out.ctypes.data_as(ctypes.POINTER(ctypes.c_double)))
+        if rc:
+            raise RuntimeError(self._lib.pet_nccl_last_error().decode())
+        return out
+
+    def timing(self, enable=True):
+        """(milliseconds inside edges() since the last call, number of calls); switches the CUDA-event brackets on or off."""
+        ms, n = ctypes.c_double(), ctypes.c_int()
+        if self._lib.pet_nccl_exchange_timing(self._h, int(enable), ctypes.byref(ms), ctypes.byref(n)):
+            raise RuntimeError(self._lib.pet_nccl_last_error().decode())
+        return ms.value, n.value
+
+    def close(self):
+        if self._h is not None:
+            self._lib.pet_nccl_exchange_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def make_exchange(calc, routing, owner=None, n_total=0, device=0, group=None, native=True):
+    """The exchange a rank of a torch.distributed job hands to its Calculator: the library's own over NCCL, or (with
+    native=False) the torch.distributed one that the tests keep as a second opinion."""
+    if native:
+        return NativeNcclExchange(routing, owner, n_total, device, group)
     return NcclExchange(routing, group)
 
 
@@ -303,15 +372,24 @@ def compute_threads(calcs, system, cutoff, mute=False):
     return E, F, W, hub
 
 
-def compute_distributed(calc, system, cutoff, group=None, steps=1, positions=None):
+def compute_distributed(calc, system, cutoff, group=None, steps=1, positions=None, native=False):
     """One process per GPU (torch.distributed initialised, NCCL): this rank evaluates its domain of `system` with
-    ghosts one cutoff deep and an NcclExchange; returns the whole cell's (energy, forces, virial) on every rank.
-    With steps > 1 the list is set once and compute_step runs `steps` times (an MD engine between list rebuilds)."""
+    ghosts one cutoff deep and an exchange over NCCL; returns the whole cell's (energy, forces, virial) on every rank.
+    With steps > 1 the list is set once and compute_step runs `steps` times (an MD engine between list rebuilds).
+    native: the library's own exchange and device-side reduction instead of the torch.distributed ones."""
     import torch
     import torch.distributed as dist
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     domains = [exchange_domain(system, r, world, cutoff) for r in range(world)]
     fields, owner, _, _ = domains[rank]
+    if native:
+        ex = NativeNcclExchange(route(domains)[rank], owner, system["n_atoms"], torch.cuda.current_device(), group)
+        calc.set_neighbors(view_of(fields, ex))
+        for _ in range(steps):
+            calc.compute_step_on_device(fields["positions"], None, True)
+            out = ex.reduce(calc)
+        ex.close()
+        return out[0], out[7:].reshape(-1, 3), out[1:7]
     ex = NcclExchange(route(domains)[rank], group)
     view = view_of(fields, ex)
     if steps == 1:

@@ -35,6 +35,14 @@ def main():
             print(f"rank {rank} {featurizer}: dE {de:.2e} dF {df:.2e} dW {dw:.2e}", flush=True)
             assert de <= 1e-6 and df <= 1e-5 and dw <= 1e-5, (de, df, dw)
             worst = max(worst, de, df, dw)
+            # the library's own exchange (pack / ncclSend / ncclRecv / unpack on the calculator's stream, forces folded
+            # and reduced on the device): the same rows cross, so the answer differs only by the order of the last sums
+            En, Fn, Wn = exchange.compute_distributed(calc, s, calc.cutoff, native=True)
+            assert abs(En - E) <= 1e-12 * e_scale and np.abs(Fn - F).max() <= 1e-12 * max(1.0, np.abs(F).max())
+            assert np.abs(Wn - W).max() <= 1e-12 * max(1.0, np.abs(W).max())
+            En3, Fn3, _ = exchange.compute_distributed(calc, s, calc.cutoff, steps=3, native=True)
+            assert En3 == En and np.array_equal(Fn3, Fn), "stepping the native exchange repeats the same bits"
+            print(f"rank {rank} {featurizer}: native exchange agrees", flush=True)
             calc.close()
     dist.barrier()
     if rank == 0:

@@ -42,6 +42,38 @@ def test_muting_the_exchange_changes_the_answer(lib_path, models):
         c.close()
 
 
+@pytest.mark.parametrize("featurizer", ["feedforward", "residual"])
+def test_native_exchange_on_one_rank_reproduces_the_periodic_cell(lib_path, models, featurizer):
+    """The library's own exchange (csrc/nccl_exchange.cu) with a single rank: every ghost is then an image of one of
+    the rank's own atoms, so all partner rows take the on-rank path (pack kernel, device copy, unpack kernel), the
+    forces are folded onto their owners on the device and the one-rank NCCL communicator reduces nothing. The answer
+    must be the periodic cell's; a list set once and stepped must repeat the same bits."""
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("tiny", featurizer, "scaled", 31)
+    s = st.diamond(2, jitter=0.05, seed=6)
+    calc = Calculator(jp, sp)
+    ref = calc.compute(s)
+    fields, owner, _, remote = exchange.exchange_domain(s, 0, 1, calc.cutoff)
+    assert len(remote) > 0
+    ex = exchange.NativeNcclExchange(exchange.route([(fields, owner, None, remote)])[0], owner, s["n_atoms"], 0, single=True)
+    calc.set_neighbors(exchange.view_of(fields, ex))
+    outs = []
+    for _ in range(2):
+        calc.compute_step_on_device(fields["positions"], None, True)
+        outs.append(ex.reduce(calc))
+    assert np.array_equal(outs[0], outs[1])
+    E, W, F = outs[0][0], outs[0][1:7], outs[0][7:].reshape(-1, 3)
+    assert abs(E - ref.energy[0]) <= 1e-6 * max(abs(ref.energy[0]), np.abs(ref.per_atom_energy).sum())
+    assert np.abs(F - ref.forces).max() <= 1e-5 * max(1.0, np.abs(ref.forces).max())
+    assert np.abs(W - ref.virial[0]).max() <= 1e-5 * max(1.0, np.abs(ref.virial).max())
+    ms, calls = ex.timing(True)
+    calc.compute_step_on_device(fields["positions"], None, True)
+    ms, calls = ex.timing(False)
+    assert calls >= 2 and ms > 0.0
+    ex.close()
+    calc.close()
+
+
 def test_one_process_per_gpu_over_nccl():
     """The same decomposition with real ranks: torchrun, one process per GPU, rows crossing with NCCL all-to-all.
     Needs two GPUs; NVLS is switched off as for every test in which a rank could leave early."""
