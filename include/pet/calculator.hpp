@@ -250,6 +250,12 @@ class Calculator {
     check(pet_staged_geometry(h_, &g));
     return DeviceGeom{g.n_structures, g.n_atoms, g.positions, g.cells, g.struct_id, g.stream};
   }
+  // The staged batch shrinks to the structures `still_running` (indices into it, in their new order), e.g. as the
+  // structures of a batched relaxation converge; a Verlet cache follows them without searching again.
+  DeviceGeom keep(const std::vector<int>& still_running) const {
+    check(pet_keep_staged(h_, still_running.data(), int(still_running.size())));
+    return staged();
+  }
   // New positions [Ntot * 3] and / or cells [B * 9] for the staged batch, from host arrays.
   void update_staged(const double* positions, const double* cells = nullptr) const { check(pet_update_staged(h_, positions, cells)); }
   // From the staged geometry, results left on the device.

@@ -217,6 +217,12 @@ typedef struct pet_device_geom {
   void* stream;              /* the calculator's cudaStream_t */
 } pet_device_geom;
 int pet_staged_geometry(pet_calc* c, pet_device_geom* out);
+/* A staged batch that shrinks (a batched relaxation whose structures finish one by one): keep[n_keep] names the
+ * staged structures that stay, in the order they have from now on; they keep the positions they have on the device,
+ * and under Options::cache_neighbors their cached pairs follow them, renumbered, without a new search. The
+ * reference's compute_device with a smaller DeviceGeom and its `staged` map (calculator.hpp:214-218;
+ * cache_reassemble, src/device_geometry.cpp:203-246). */
+int pet_keep_staged(pet_calc* c, const int* keep, int n_keep);
 /* Moves the staged positions (and cells when non-null) on the device from host arrays. */
 int pet_update_staged(pet_calc* c, const double* positions, const double* cells);
 
@@ -368,6 +374,9 @@ int pet_device_results_of(pet_calc* c, pet_device_results* out, void** stream);
  *     k % 4 == 0; a larger problem is refused with PET_ERR_INVALID and a message in errbuf;
  *   - the first call on each device resolves the array's device address (cudaGetSymbolAddress):
  *     make that first call before any stream capture starts;
+ *   - the operands are ordinary (pageable) host arrays, and CUDA refuses copies from such memory in every thread
+ *     while any thread has a stream capture open in the global mode; for the length of the call the calling thread
+ *     therefore switches its own capture mode to relaxed (cudaThreadExchangeStreamCaptureMode) and restores it after;
  *   - every call uses the same array, which keeps the previous call's contents (the kernel
  *     overwrites all of C, so nothing needs clearing); calls that overlap on one GPU (two host
  *     threads) race.

@@ -140,6 +140,7 @@ SIGNATURES = {
     "pet_nccl_exchange_reduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, _P(C.c_double)]),
     "pet_nccl_exchange_timing": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_double), _P(C.c_int)]),
     "pet_staged_geometry": (C.c_int, [C.c_void_p, _P(PetDeviceGeom)]),
+    "pet_keep_staged": (C.c_int, [C.c_void_p, _P(C.c_int), C.c_int]),
     "pet_device_results_of": (C.c_int, [C.c_void_p, _P(PetDeviceResults), _P(C.c_void_p)]),
     "pet_memory_plan": (C.c_int, [C.c_void_p, _P(PetMemoryPlan)]),
     "pet_memory_report": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
@@ -428,6 +429,15 @@ class Calculator:
         p = _Packed(systems)
         self._check(self._lib.pet_stage(self._h, p.arr, p.n))
         self._staged = (p.n, p.total, p.n_atoms)
+
+    def keep_staged(self, keep):
+        """The staged batch shrinks to the structures `keep` (indices into it, in their new order); positions stay as they
+        are on the device and a Verlet cache follows without searching again (pet_keep_staged)."""
+        k = np.ascontiguousarray(keep, dtype=np.int32)
+        B, N, n_atoms = self._staged
+        self._check(self._lib.pet_keep_staged(self._h, _iptr(k), len(k)))
+        kept = [n_atoms[i] for i in k]
+        self._staged = (len(k), int(sum(kept)), kept)
 
     def update_staged(self, positions=None, cells=None):
         x = None if positions is None else np.ascontiguousarray(positions, dtype=np.float64)

@@ -141,6 +141,9 @@ int pet_last_shapes(const pet_calc* c, int* n_atoms, int* n_edges, int* max_neig
   if (max_neighbors) *max_neighbors = c->e->last_pk.M;
   return PET_OK;
 }
+int pet_keep_staged(pet_calc* c, const int* keep, int n_keep) {
+  return guarded(c, [&](Engine& e) { e.keep_staged(keep, n_keep); });
+}
 int pet_staged_geometry(pet_calc* c, pet_device_geom* out) {
   if (!c || !c->e || !out) return PET_ERR_INVALID;
   const Engine& e = *c->e;

@@ -132,6 +132,13 @@ class Arena {
     used_total_ = 0;
     ++generation_;
   }
+  // Trades everything with another pool (the pools are not copyable: they own device memory).
+  void swap(Arena& o) {
+    blocks_.swap(o.blocks_);
+    std::swap(cur_, o.cur_), std::swap(next_block_, o.next_block_), std::swap(used_total_, o.used_total_);
+    std::swap(generation_, o.generation_);
+    ++generation_, ++o.generation_;
+  }
   size_t capacity() const {
     size_t t = 0;
     for (auto& b : blocks_) t += b.size;

@@ -93,6 +93,48 @@ __global__ void k_orphan_forces(double* __restrict__ forces, const double* __res
     for (int c = 0; c < 3; ++c) forces[3 * size_t(a) + c] -= eg[3 * size_t(oedge[k]) + c];
 }
 
+// out(k) = in(idx(k)): the edge offsets at structure boundaries, for the host.
+__global__ void k_pick(int* __restrict__ out, const int* __restrict__ in, const int* __restrict__ idx, int n) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k < n) out[k] = in[idx[k]];
+}
+// out(i, :) = in(map(i), :), `w` doubles per row.
+__global__ void k_gather_rows_f64(double* __restrict__ out, const double* __restrict__ in, const int* __restrict__ map, int n, int w) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < n * w) out[t] = in[size_t(map[t / w]) * w + t % w];
+}
+// The cached pairs of the structures that stay, renumbered for where each structure now sits (the reference's
+// cache_reassemble, src/device_geometry.cpp:203-246). Slot k of the smaller batch holds the structure whose atoms
+// were at atom_old(k).. and whose pairs were at edge_old(k)..; they move to atom_new(k).. and edge_new(k)...
+// Pairs never cross structures, so a block's partners stay inside it.
+__global__ void k_reassemble_pairs(RawEdges out, RawEdges in, const int* __restrict__ edge_new, const int* __restrict__ edge_old,
+                                   const int* __restrict__ atom_new, const int* __restrict__ atom_old, int slots, int E) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  int lo = 0, hi = slots - 1;  // the slot whose range of new pairs holds e
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) / 2;
+    if (edge_new[mid] <= e) lo = mid;
+    else hi = mid - 1;
+  }
+  const int from = edge_old[lo] + e - edge_new[lo], moved = atom_new[lo] - atom_old[lo];
+  out.i[e] = in.i[from] + moved, out.j[e] = in.j[from] + moved;
+  out.reverse[e] = in.reverse[from] < 0 ? -1 : in.reverse[from] - edge_old[lo] + edge_new[lo];
+  for (int d = 0; d < 3; ++d) out.shift[3 * size_t(e) + d] = in.shift[3 * size_t(from) + d];
+}
+__global__ void k_reassemble_offsets(int* __restrict__ off_new, const int* __restrict__ off_old, const int* __restrict__ atom_map,
+                                     const int* __restrict__ slot_of_atom, const int* __restrict__ edge_new,
+                                     const int* __restrict__ edge_old, int N, int E) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > N) return;
+  if (i == N) {
+    off_new[N] = E;
+    return;
+  }
+  const int k = slot_of_atom[i];
+  off_new[i] = off_old[atom_map[i]] - edge_old[k] + edge_new[k];
+}
+
 // `skip`, unless null, is the fixed-shape overflow flag: a step that did not fit adds nothing (it is redone).
 __global__ void k_add_arrays(double* __restrict__ f, const double* __restrict__ forces, double* __restrict__ e,
                              const double* __restrict__ per_atom, int N, const int* __restrict__ skip) {
@@ -131,7 +173,7 @@ __global__ void k_atom_virial(double* __restrict__ w, const double* __restrict__
 
 Engine::Engine(const std::string& json, const std::string& weights, const pet_options* opts)
     : ckpt(json, weights), geom_arena(size_t(1) << 20), nbr_arena(size_t(16) << 20), save_arena(size_t(64) << 20),
-      tmp_arena(size_t(64) << 20), session_arena(size_t(4) << 20), cache_arena(size_t(4) << 20) {
+      tmp_arena(size_t(64) << 20), session_arena(size_t(4) << 20), cache_arena(size_t(4) << 20), cache_spare(size_t(4) << 20) {
   int count = 0;
   if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
     throw Error(5, "no CUDA device: this evaluator has no CPU path");
@@ -259,6 +301,118 @@ void Engine::stage(const pet_system* systems, int B, bool keep_cache) {
   verlet.valid = verlet.valid && keep_cache && was_natoms == h_natoms && was_per == h_per && was_species == h_species;
   // the copy must finish before the staging block is reused by another stage()
   PETB_CUDA(cudaStreamSynchronize(st.s));
+}
+
+// A batch being stepped shrinks as its structures finish (a batched relaxation): the structures `keep` (indices into
+// the staged batch, in the order they shall have from now on) stay, with the positions they have on the device now,
+// and the Verlet cache follows them without a new search: each kept structure's block of cached pairs is copied and
+// renumbered. The reference does the same when compute_device is given a smaller DeviceGeom whose `staged` says
+// where each structure went (include/pet/calculator.hpp:214-218, src/device_geometry.cpp:203-246,262-310).
+void Engine::keep_staged(const int* keep, int n_keep) {
+  PETB_CUDA(cudaSetDevice(device));
+  const int B = geom.B, N = geom.Ntot;
+  if (n_keep < 0 || (n_keep > 0 && !keep)) throw Error(2, "pet: no structures given to keep");
+  if (B == 0 && N == 0) throw Error(3, "pet: nothing is staged");
+  std::vector<char> seen(B, 0);
+  for (int k = 0; k < n_keep; ++k) {
+    if (keep[k] < 0 || keep[k] >= B || seen[keep[k]]) throw Error(2, "pet: keep names a structure twice or one that is not staged");
+    seen[keep[k]] = 1;
+  }
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  std::vector<int> soff_old(B + 1, 0);
+  for (int b = 0; b < B; ++b) soff_old[b + 1] = soff_old[b] + h_natoms[b];
+  // the kept structures, slot by slot: their atoms' old indices, and host copies of what staging needs
+  std::vector<int> atom_map, slot_of_atom, atom_new(n_keep + 1, 0), atom_old(n_keep > 0 ? n_keep : 1, 0);
+  for (int k = 0; k < n_keep; ++k) {
+    const int b = keep[k];
+    atom_old[k] = soff_old[b], atom_new[k + 1] = atom_new[k] + h_natoms[b];
+    for (int a = 0; a < h_natoms[b]; ++a) atom_map.push_back(soff_old[b] + a), slot_of_atom.push_back(k);
+  }
+  const int Nn = atom_new[n_keep];
+  tmp_arena.reset();
+  int* d_map = tmp_arena.alloc<int>(size_t(Nn > 0 ? Nn : 1));
+  double* d_pos = tmp_arena.alloc<double>(3 * size_t(Nn > 0 ? Nn : 1));
+  std::vector<double> pos(3 * size_t(Nn));
+  if (Nn) {
+    PETB_CUDA(cudaMemcpyAsync(d_map, atom_map.data(), 4 * size_t(Nn), cudaMemcpyHostToDevice, st.s));
+    k_gather_rows_f64<<<cdiv(3 * size_t(Nn), 256), 256, 0, st.s>>>(d_pos, geom.pos, d_map, Nn, 3);
+    PETB_LAUNCH_CHECK(st);
+    PETB_CUDA(cudaMemcpyAsync(pos.data(), d_pos, 24 * size_t(Nn), cudaMemcpyDeviceToHost, st.s));
+  }
+  // the cache's pairs for the smaller batch, in the pool that is not holding the current ones
+  VerletCache next;
+  const bool follow = cache_neighbors && verlet.valid && Nn > 0;
+  if (follow) {
+    const VerletCache& c = verlet;
+    std::vector<int> bounds(n_keep + 1), edge_at(size_t(n_keep) * 2);
+    int* d_idx = tmp_arena.alloc<int>(size_t(n_keep) * 2);
+    int* d_val = tmp_arena.alloc<int>(size_t(n_keep) * 2);
+    std::vector<int> idx(size_t(n_keep) * 2);
+    for (int k = 0; k < n_keep; ++k) idx[2 * k] = soff_old[keep[k]], idx[2 * k + 1] = soff_old[keep[k] + 1];
+    PETB_CUDA(cudaMemcpyAsync(d_idx, idx.data(), 4 * idx.size(), cudaMemcpyHostToDevice, st.s));
+    k_pick<<<cdiv(idx.size(), 256), 256, 0, st.s>>>(d_val, c.ref.off, d_idx, int(idx.size()));
+    PETB_LAUNCH_CHECK(st);
+    PETB_CUDA(cudaMemcpyAsync(edge_at.data(), d_val, 4 * edge_at.size(), cudaMemcpyDeviceToHost, st.s));
+    PETB_CUDA(cudaStreamSynchronize(st.s));
+    std::vector<int> edge_old(n_keep), edge_new(n_keep + 1, 0);
+    for (int k = 0; k < n_keep; ++k) edge_old[k] = edge_at[2 * k], edge_new[k + 1] = edge_new[k] + edge_at[2 * k + 1] - edge_at[2 * k];
+    const int En = edge_new[n_keep];
+    Arena& pool = cache_spare;
+    pool.reset();
+    const size_t Ea = En > 0 ? En : 1;
+    RawEdges r;
+    r.E = En;
+    r.i = pool.alloc<int>(Ea), r.j = pool.alloc<int>(Ea), r.shift = pool.alloc<int>(3 * Ea);
+    r.vec = pool.alloc<double>(3 * Ea), r.dist = pool.alloc<double>(Ea);
+    r.off = pool.alloc<int>(size_t(Nn) + 1), r.reverse = pool.alloc<int>(Ea);
+    next.pos0 = pool.alloc<double>(3 * size_t(Nn)), next.cinv0 = pool.alloc<double>(9 * size_t(n_keep));
+    next.worst = pool.alloc<double>(1);
+    int* d_tab = tmp_arena.alloc<int>(4 * size_t(n_keep) + 2 + size_t(Nn));
+    int *d_enew = d_tab, *d_eold = d_enew + n_keep + 1, *d_anew = d_eold + n_keep, *d_aold = d_anew + n_keep + 1;
+    int* d_slot = d_aold + n_keep;
+    int* d_keep = tmp_arena.alloc<int>(n_keep);
+    PETB_CUDA(cudaMemcpyAsync(d_enew, edge_new.data(), 4 * size_t(n_keep + 1), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(d_eold, edge_old.data(), 4 * size_t(n_keep), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(d_anew, atom_new.data(), 4 * size_t(n_keep + 1), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(d_aold, atom_old.data(), 4 * size_t(n_keep), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(d_slot, slot_of_atom.data(), 4 * size_t(Nn), cudaMemcpyHostToDevice, st.s));
+    PETB_CUDA(cudaMemcpyAsync(d_keep, keep, 4 * size_t(n_keep), cudaMemcpyHostToDevice, st.s));
+    if (En) {
+      k_reassemble_pairs<<<cdiv(En, 256), 256, 0, st.s>>>(r, c.ref, d_enew, d_eold, d_anew, d_aold, n_keep, En);
+      PETB_LAUNCH_CHECK(st);
+    }
+    k_reassemble_offsets<<<cdiv(Nn + 1, 256), 256, 0, st.s>>>(r.off, c.ref.off, d_map, d_slot, d_enew, d_eold, Nn, En);
+    PETB_LAUNCH_CHECK(st);
+    k_gather_rows_f64<<<cdiv(3 * size_t(Nn), 256), 256, 0, st.s>>>(next.pos0, c.pos0, d_map, Nn, 3);
+    PETB_LAUNCH_CHECK(st);
+    k_gather_rows_f64<<<cdiv(9 * size_t(n_keep), 256), 256, 0, st.s>>>(next.cinv0, c.cinv0, d_keep, n_keep, 9);
+    PETB_LAUNCH_CHECK(st);
+    next.ref = r, next.valid = true, next.searches = c.searches, next.reuses = c.reuses;
+  }
+  PETB_CUDA(cudaStreamSynchronize(st.s));
+  // stage the kept structures again from what the host knows of them and the positions just read
+  std::vector<int> z_of_species(ckpt.n_species > 0 ? ckpt.n_species : 1, 0);
+  for (int Z = int(ckpt.species_to_index.size()) - 1; Z >= 0; --Z)
+    if (ckpt.species_to_index[Z] >= 0 && ckpt.species_to_index[Z] < int(z_of_species.size())) z_of_species[ckpt.species_to_index[Z]] = Z;
+  std::vector<int> numbers(Nn > 0 ? Nn : 1);
+  for (int i = 0; i < Nn; ++i) numbers[i] = z_of_species[h_species[atom_map[i]]];
+  std::vector<pet_system> sys(n_keep);
+  for (int k = 0; k < n_keep; ++k) {
+    const int b = keep[k];
+    pet_system& s = sys[k];
+    s = pet_system{};
+    s.n_atoms = h_natoms[b], s.atomic_numbers = numbers.data() + atom_new[k], s.positions = pos.data() + 3 * size_t(atom_new[k]);
+    for (int e = 0; e < 9; ++e) s.cell[e] = h_cells[size_t(b) * 9 + e];
+    for (int d = 0; d < 3; ++d) s.pbc[d] = (h_per[b] >> d) & 1;
+    s.spin_multiplicity = 1;
+  }
+  const long long searches = verlet.searches, reuses = verlet.reuses;
+  stage(sys.data(), n_keep, false);
+  if (follow) {
+    cache_arena.swap(cache_spare);  // the new pairs' pool becomes the cache's; the old one is spare from now on
+    verlet = next;
+  }
+  verlet.searches = searches, verlet.reuses = reuses;
 }
 
 void Engine::update_staged(const double* positions, const double* cells) {
@@ -621,7 +775,7 @@ void Engine::compute(const pet_system* systems, int B, bool forces, pet_results*
       drop_graphs();       // they replay into pool addresses
       graph_seen.clear();
       have_out = false, verlet.valid = false;
-      save_arena.release(), tmp_arena.release(), nbr_arena.release(), cache_arena.release();
+      save_arena.release(), tmp_arena.release(), nbr_arena.release(), cache_arena.release(), cache_spare.release();
       ++oom_recoveries;
       // one structure cannot be cut: keep less of its forward instead (the reference's tier drop, src/model.cpp:952-971)
       bool cuttable = false;
@@ -1136,7 +1290,7 @@ void Engine::gemm_host(int mode, bool w_transposed, int m, int n, int k, const f
   PETB_CUDA(cudaStreamSynchronize(st.s));
   tmp_arena.reset();
   float* dA = tmp_arena.alloc<float>(size_t(m) * k);
-  float* dW = tmp_arena.alloc<float>(size_t(n) * k);
+  float* dW = tmp_arena.alloc<float>(2 * size_t(n) * k);  // and, for the 3xTF32 mode, the low parts of its split behind it
   float* dC = tmp_arena.alloc<float>(size_t(m) * n);
   PETB_CUDA(cudaMemcpyAsync(dA, A, 4 * size_t(m) * k, cudaMemcpyHostToDevice, st.s));
   // The kernels take the weight K-major, [n, k]; the other orientation is transposed here, as a
@@ -1152,6 +1306,23 @@ void Engine::gemm_host(int mode, bool w_transposed, int m, int n, int k, const f
   PETB_CUDA(cudaMemcpyAsync(dW, hw, 4 * size_t(n) * k, cudaMemcpyHostToDevice, st.s));
   GemmArgs a;
   a.A = dA, a.lda = k, a.B = dW, a.ldb = k, a.C = dC, a.ldc = n, a.M = m, a.N = n, a.K = k;
+  std::vector<float> wlo;
+  if (mode == GEMM_TF32X3) {  // the weight's low parts, made once as for a loaded weight (x minus its leading 11 bits, rounded)
+    wlo.resize(size_t(n) * k);
+    for (size_t i = 0; i < wlo.size(); ++i) {
+      uint32_t bits, lo;
+      std::memcpy(&bits, &hw[i], 4);
+      bits &= 0xFFFFE000u;
+      float hi;
+      std::memcpy(&hi, &bits, 4);
+      const float r = hw[i] - hi;
+      std::memcpy(&lo, &r, 4);
+      lo += 0x1000u;
+      std::memcpy(&wlo[i], &lo, 4);
+    }
+    PETB_CUDA(cudaMemcpyAsync(dW + size_t(n) * k, wlo.data(), 4 * wlo.size(), cudaMemcpyHostToDevice, st.s));
+    a.b_lo_offset = size_t(n) * k;
+  }
   std::vector<uint16_t> w16;
   if (mode == GEMM_BF16) {  // the weight again as bf16, round to nearest even, as a loaded weight is kept
     w16.resize(size_t(n) * k);

@@ -51,8 +51,8 @@ struct Session {
 // The pairs of a staged batch within cutoff + skin, kept between evaluations while no atom has moved (and no cell
 // strained) far enough for a pair outside to have come inside the cutoff: the reference's NefCache
 // (include/pet/device_geometry.hpp:198-228, src/device_geometry.cpp:165-352). The shifts are in terms of the
-// unwrapped positions, so a pair survives an atom crossing a cell face. Staging drops it; a batch whose
-// composition changes is staged again and so searched again (the reference reassembles a shrinking batch's pairs).
+// unwrapped positions, so a pair survives an atom crossing a cell face. Staging drops it; a batch that shrinks
+// (Engine::keep_staged) keeps the pairs of the structures that stay, renumbered.
 struct VerletCache {
   static constexpr double kSkin = 1.0;  // Angstrom, as the reference's
   bool valid = false;
@@ -73,6 +73,7 @@ struct Engine {
   // Options::cache_neighbors steps a structure this way, src/calculator.cpp:638-644); Calculator::stage drops it.
   void stage(const pet_system* systems, int B, bool keep_cache = false);
   void update_staged(const double* positions, const double* cells);
+  void keep_staged(const int* keep, int n_keep);
   void compute_staged(bool forces);
   void fetch(pet_results* out);
   void neighbor_list(const pet_system* systems, int B, pet_raw_edges* out);
@@ -109,7 +110,7 @@ struct Engine {
   Profiler prof;
   Checkpoint ckpt;
   std::unique_ptr<Model> model;
-  Arena geom_arena, nbr_arena, save_arena, tmp_arena, session_arena, cache_arena;
+  Arena geom_arena, nbr_arena, save_arena, tmp_arena, session_arena, cache_arena, cache_spare;
   VerletCache verlet;
   Geom geom;                  // staged batch
   std::vector<double> h_cells;  // staged cells on the host (the grid is chosen there)

@@ -35,6 +35,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -227,7 +228,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
           if (!(ok = mbar_wait(empty + s, ((g / STAGES) & 1) ^ 1, abort_flag))) break;
           uint8_t* sa = tiles + size_t(s) * L::kStage;
           const bool b_lo = X3 && p.b_lo_offset != 0;  // B's low parts come from memory, not from the splitter
-          mbar_expect_tx(full + s, L::kHi + (b_lo ? L::kB : 0));
+          mbar_expect_tx(full + s, L::kA + L::kB + (b_lo ? L::kB : 0));  // what TMA brings: not the converter's bf16 A tile
           tma_load_2d(sa, &map_a, full + s, kb * TBK, m0);
           tma_load_2d(sa + L::kA + L::kA16, &map_b, full + s, kb * TBK, n0);
           if (b_lo) tma_load_2d(sa + L::kHi + L::kA, &map_blo, full + s, kb * TBK, n0);
@@ -387,6 +388,267 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
   if (threadIdx.x == 0 && *abort_flag) atomicExch(err, 1);
 }
 
+
+// ---- the same product on a pair of CTAs ------------------------------------------------------
+//
+// k_gemm_tc above is short of shared-memory bandwidth in the 3xTF32 mode: per 8 columns of K a CTA moves 64 KB through
+// shared memory (TMA writes, the splitter, three MMAs' operand reads) against 384 clocks of MMA, and two thirds of it
+// is the B tile. Here two CTAs of a cluster share one 256 x 256 tile: each stages its own 128 rows of A and HALF of
+// the B tile (128 of its 256 rows, hi and lo), and one thread of the even CTA issues tcgen05.mma.cta_group::2
+// (M = 256, N = 256, K = 8): the tensor cores of both SMs read both halves of B, each half once. Per CTA and 8
+// columns of K that is 44 KB of shared-memory traffic against the same 384 clocks.
+//
+// Who signals whom (every barrier exists in both CTAs at the same offset; "leader" is the even CTA):
+//   full[s]    own CTA's TMA loads landed (each CTA loads with the plain, CTA-local form; no multicast anywhere)
+//   split[s]   LEADER's: 256 arrivals, the splitter threads of both CTAs (the odd CTA's arrive remotely) once their lo
+//              tile is written: both CTAs' operands of the stage are then complete
+//   empty[s]   own CTA's: the leader's issuer commits the stage's MMAs to its own and to the odd CTA's barrier
+//   tfull[b]   own CTA's: the leader commits the finished accumulator to both
+//   tempty[b]  LEADER's: 16 arrivals, the epilogue warps of both CTAs once they have read the accumulator
+// Tensor memory is allocated by warp 1 of both CTAs together (cta_group::2); each CTA's half of the accumulator is in
+// its own tensor memory and its own epilogue warps write its 128 rows. Every wait is bounded as above; the CTAs meet
+// at a cluster barrier after set-up and before release, so neither signals a peer that is not there.
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address of the same shared-memory location in another CTA of the cluster.
+__device__ __forceinline__ uint32_t peer_smem(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// A bounded wait that also acquires what the other CTA of the cluster wrote before it arrived.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (*abort_flag) return false;
+    if ((unsigned long long) (clock64() - t0) > kSpinLimit) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on a barrier (of this CTA or, by its cluster address, of the peer) once the pair's MMAs issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+__host__ __device__ constexpr uint32_t idesc_tf32_pair(int n) {  // M = 256 over the two CTAs
+  return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(256 >> 4) << 24);
+}
+
+template <int STAGES>
+struct SmemPair {
+  static constexpr int BN = 256, BK = 32;
+  static constexpr int kA = TBM * BK * 4, kBh = (BN / 2) * BK * 4;  // A's rows, and this CTA's half of B's
+  static constexpr int kHi = kA + kBh;
+  static constexpr int kStage = 2 * kHi;  // with the lo tiles
+  static constexpr int kTiles = STAGES * kStage;
+  static constexpr int kPads = kEpiWarps * 32 * kPad * 4;
+  static constexpr int kTotal = kTiles + kPads + 1024 + 256;
+  static constexpr int kThreads = 512;
+};
+
+template <int EPI, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
+    k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_blo, GemmArgs p, int* err) {
+  using L = SmemPair<STAGES>;
+  constexpr int BN = L::BN, TBK = L::BK;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* pads = reinterpret_cast<float*>(tiles + L::kTiles);
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::kTiles + L::kPads);
+  uint64_t* empty = full + STAGES;
+  uint64_t* split = empty + STAGES;
+  uint64_t* tfull = split + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + 2 * TBM - 1) / (2 * TBM);
+  const int n_tiles = tiles_m * tiles_n, pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int nkb = (p.K + TBK - 1) / TBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+      mbar_init(split + s, 256);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull + b, 1);
+      mbar_init(tempty + b, 2 * kEpiWarps);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // both CTAs' warp 1, together: two accumulators of 256 columns in each CTA's tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything signals them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {  // each CTA loads its own rows of A and its half of B
+      int g = 0;
+      for (int t = pair; t < n_tiles; t += n_pairs) {
+        const int m0 = (t / tiles_n) * 2 * TBM + int(rank) * TBM, n0 = (t % tiles_n) * BN + int(rank) * (BN / 2);
+        bool ok = true;
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const int s = g % STAGES;
+          if (!(ok = mbar_wait(empty + s, ((g / STAGES) & 1) ^ 1, abort_flag))) break;
+          uint8_t* sa = tiles + size_t(s) * L::kStage;
+          mbar_expect_tx(full + s, L::kA + 2 * L::kBh);
+          tma_load_2d(sa, &map_a, full + s, kb * TBK, m0);
+          tma_load_2d(sa + L::kA, &map_b, full + s, kb * TBK, n0);
+          tma_load_2d(sa + L::kHi + L::kA, &map_blo, full + s, kb * TBK, n0);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = idesc_tf32_pair(BN);
+      int g = 0, i = 0;
+      for (int t = pair; t < n_tiles; t += n_pairs, ++i) {
+        const int b = i & 1;
+        bool ok = mbar_wait_cluster(tempty + b, ((i >> 1) & 1) ^ 1, abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + uint32_t(b * BN);
+        for (int kb = 0; ok && kb < nkb; ++kb, ++g) {
+          const int s = g % STAGES;
+          if (!(ok = mbar_wait_cluster(split + s, (g / STAGES) & 1, abort_flag))) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a0 = smem_u32(tiles + size_t(s) * L::kStage), b0 = a0 + L::kA;
+#pragma unroll
+          for (int k = 0; k < TBK / 8; ++k) {
+            const uint64_t da = smem_desc<TBK>(a0 + 32 * k), db = smem_desc<TBK>(b0 + 32 * k);
+            const uint64_t dal = smem_desc<TBK>(a0 + L::kHi + 32 * k), dbl = smem_desc<TBK>(b0 + L::kHi + 32 * k);
+            mma_tf32_pair(acc, da, dbl, idesc, (kb | k) != 0);
+            mma_tf32_pair(acc, dal, db, idesc, 1);
+            mma_tf32_pair(acc, da, db, idesc, 1);
+          }
+          mma_commit_pair(smem_u32(empty + s));
+          mma_commit_pair(peer_smem(empty + s, 1));
+        }
+        if (!ok) break;
+        mma_commit_pair(smem_u32(tfull + b));
+        mma_commit_pair(peer_smem(tfull + b, 1));
+      }
+    }
+  } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps) {
+    const int ew = warp - kEpiWarp0;
+    const int q = warp & 3;
+    const int half = ew >> 2;
+    float* pad = pads + size_t(ew) * 32 * kPad;
+    const int sub = lane >> 3, c4 = (lane & 7) * 4;
+    int i = 0;
+    for (int t = pair; t < n_tiles; t += n_pairs, ++i) {
+      const int b = i & 1;
+      const int m0 = (t / tiles_n) * 2 * TBM + int(rank) * TBM, n0 = (t % tiles_n) * BN;
+      if (!mbar_wait(tfull + b, (i >> 1) & 1, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t acc = tmem + uint32_t(b * BN) + (uint32_t(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+        float v[32];
+        tmem_ld32(acc + c0, v);
+        if (c0 + 32 == (half + 1) * (BN / 2)) {  // read: the leader's issuer may reuse this accumulator in both CTAs
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(peer_smem(tempty + b, 0));
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(pad + lane * kPad + (((j >> 2) ^ (lane & 7)) << 2)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        __syncwarp();
+        const int col = n0 + c0 + c4;
+        if (col < p.N) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            EpiLoad ld[4];
+            int rows[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              rows[u] = m0 + q * 32 + (h * 4 + u) * 4 + sub;
+              if (rows[u] < p.M) ld[u] = epilogue_load4<EPI>(p, rows[u], col);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (rows[u] < p.M) {
+                const int rr = (h * 4 + u) * 4 + sub;
+                const float4 a = *reinterpret_cast<const float4*>(pad + rr * kPad + (((lane & 7) ^ (rr & 7)) << 2));
+                const float accv[4] = {a.x, a.y, a.z, a.w};
+                epilogue_apply4<EPI>(p, rows[u], col, accv, ld[u]);
+              }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp >= kSplitWarp0) {
+    const int tid = threadIdx.x - kSplitWarp0 * 32;
+    constexpr int n16 = L::kA / 16;  // A's 16-byte pieces; B's lo half arrives split
+    const uint32_t split0 = peer_smem(split, 0);  // the leader's barriers
+    int g = 0;
+    bool ok = true;
+    for (int t = pair; ok && t < n_tiles; t += n_pairs) {
+      for (int kb = 0; kb < nkb; ++kb, ++g) {
+        const int s = g % STAGES;
+        if (!(ok = mbar_wait(full + s, (g / STAGES) & 1, abort_flag))) break;
+        const float4* hi = reinterpret_cast<const float4*>(tiles + size_t(s) * L::kStage);
+        float4* lo = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage + L::kHi);
+#pragma unroll 8
+        for (int e = tid; e < n16; e += 128) {
+          const float4 x = hi[e];
+          float4 y;
+          y.x = tf32_lo(x.x), y.y = tf32_lo(x.y), y.z = tf32_lo(x.z), y.w = tf32_lo(x.w);
+          lo[e] = y;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive_cluster(split0 + 8u * uint32_t(s));
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while the other CTA may still signal it or read its tiles
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(err, 1);
+}
+
 // ---- host side ---------------------------------------------------------------------------
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -471,6 +733,29 @@ void launch_tc(Stream& st, const GemmArgs& a) {
   PETB_LAUNCH_CHECK(st);
 }
 
+// The pair kernel serves the 3xTF32 mode's widest tiles (N a multiple of 256, weights pre-split) when PET_GEMM_PAIR=1.
+bool pair_enabled() {  // read at every call, so that one process can compare the two kernels
+  const char* e = std::getenv("PET_GEMM_PAIR");
+  return e && e[0] == '1';
+}
+
+template <int EPI>
+void launch_tc_pair(Stream& st, const GemmArgs& a) {
+  constexpr int STAGES = 3;
+  using L = SmemPair<STAGES>;
+  static_assert(L::kTotal <= 227 * 1024, "the pair's tile pipeline does not fit shared memory");
+  static SmemOptIn opted;
+  auto kernel = k_gemm_tc_pair<EPI, STAGES>;
+  opt_in_shared_memory(kernel, L::kTotal, opted);
+  const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM, L::BK);
+  const CUtensorMap mb = make_map(a.B, a.N, a.K, a.ldb, L::BN / 2, L::BK);
+  const CUtensorMap mblo = make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, L::BN / 2, L::BK);
+  const long long tiles = (long long) cdiv(a.M, 2 * TBM) * cdiv(a.N, L::BN);
+  const long long pairs = std::min<long long>(tiles, state().sms / 2);
+  kernel<<<unsigned(2 * pairs), L::kThreads, L::kTotal, st.s>>>(ma, mb, mblo, a, state().err);
+  PETB_LAUNCH_CHECK(st);
+}
+
 // The widest 3x tile runs four 16-column stages (64-byte swizzle) rather than two 32-column ones: the same bytes in
 // flight, handed over in finer pieces (2 % faster on the 1728-atom benchmark). PET_GEMM_FINE=0 picks the coarse form.
 bool fine_stages() {
@@ -493,6 +778,7 @@ void dispatch_tc(Stream& st, const GemmArgs& a, int mode) {
   else if (a.N % 128 == 0 && mt * (a.N / 128) >= sms) bn = 128;
   else if (a.N % 64 != 0) bn = a.N % 256 == 0 ? 256 : 128;  // ragged widths: a wide tile with a zero-filled edge
   if (bn == 256) {
+    if (x3 && a.b_lo_offset && pair_enabled() && cdiv(a.M, 2 * TBM) * (a.N / 256) >= sms / 2) return launch_tc_pair<EPI>(st, a);
     if (b16) return launch_tc<EPI, 256, 4, TC_BF16>(st, a);
     if (x3) return fine_stages() ? launch_tc<EPI, 256, 4, TC_X3>(st, a) : launch_tc<EPI, 256, 2, TC_X3>(st, a);
     return launch_tc<EPI, 256, 4, TC_TF32>(st, a);

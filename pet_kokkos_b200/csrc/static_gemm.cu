@@ -36,6 +36,17 @@ std::atomic<float*> g_scratch_ptr[kMaxDevices];
 
 size_t round64(size_t n) { return (n + 63) & ~size_t(63); }
 
+// While some thread of the process has a stream capture open in the global mode, CUDA refuses calls it counts as
+// potentially unsafe from every thread, and a refused call also spoils that capture. Copies from and to pageable
+// host memory are among them, and this entry point's operands are ordinary host arrays. For the length of a call
+// the calling thread therefore declares its own calls unrelated to any capture (the relaxed mode), and puts back
+// the mode it found when the call ends.
+struct RelaxedCaptureMode {
+  cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+  RelaxedCaptureMode() { cudaThreadExchangeStreamCaptureMode(&mode); }
+  ~RelaxedCaptureMode() { cudaThreadExchangeStreamCaptureMode(&mode); }
+};
+
 int fail(char* buf, size_t len, int code, const char* msg) {
   if (buf && len) snprintf(buf, len, "%s", msg);
   return code;
@@ -75,6 +86,7 @@ extern "C" int pet_gemm_host_static(int m, int n, int k, const float* A, const f
   }
   float* dW = dA + na;
   float* dC = dW + nw;
+  const RelaxedCaptureMode not_part_of_any_capture;
   try {
     petb::Stream st;  // this thread's own stream; nothing here allocates
     st.s = cudaStreamPerThread;

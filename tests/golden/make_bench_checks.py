@@ -33,11 +33,15 @@ def main():
         for tag, shape, systems in (("batch", "s", st.workload("batch512x64")[:4]),
                                     ("cell", "l", [st.diamond(4, jitter=0.05, seed=0)])):
             jp, sp = ck.write_random_checkpoint(Path(tmp) / f"bench_{shape}", shape, seed=0, init="n002")
-            _, tens = ck.load_checkpoint(jp, sp)
+            meta, tens = ck.load_checkpoint(jp, sp)
             r = rl.ReferenceCalculator(str(jp), str(sp), blas=True).compute(systems)
             out[f"{tag}_digest"] = weights_digest(tens)
             for k in ("energy", "per_atom_energy", "forces", "virial"):
                 out[f"{tag}_{k}"] = np.asarray(r[k])
+            # what the network itself adds up to, per structure at most: the scale its fp32 rounding is relative to
+            z = np.concatenate([s["atomic_numbers"] for s in systems])
+            comp = np.asarray(meta["composition_energies"])[np.asarray(meta["species_to_index"])[z]]
+            out[f"{tag}_network_scale"] = float(np.abs(np.asarray(r["per_atom_energy"]) - comp).sum() / len(systems))
             print(tag, "E", r["energy"], "max |F|", np.abs(r["forces"]).max())
     np.savez_compressed(Path(__file__).resolve().parent / "bench_checks.npz", **out)
 

@@ -49,3 +49,25 @@ def test_native_rows_do_not_depend_on_the_batch(calc):
     full = calc.gemm(A, W, "native")
     part = calc.gemm(A[:77], W, "native")
     assert (full[:77] == part).all()
+
+
+def test_pair_kernel_gives_the_bits_of_the_single_cta_kernel(lib_path, models, monkeypatch):
+    """The 3xTF32 product on a pair of CTAs (tcgen05.mma.cta_group::2 over a 256 x 256 tile, each CTA staging half of the
+    weight tile; PET_GEMM_PAIR=1) adds the same products in the same order as the one-CTA kernel, so it must return
+    the same bits; both are held to the fp64 product. Shapes: every row tile full, a ragged last pair (one whose second
+    CTA has no rows at all), two column tiles, a contraction that is not a multiple of the 32-column stage."""
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("tiny"))
+    rng = np.random.default_rng(5)
+    for m, n, k in [(19200, 256, 256), (19001, 256, 264), (10100, 512, 512), (38500, 256, 1024)]:
+        A = rng.normal(size=(m, k)).astype(np.float32)
+        W = rng.normal(size=(n, k)).astype(np.float32)
+        monkeypatch.setenv("PET_GEMM_PAIR", "0")
+        one = c.gemm(A, W, "3xtf32")
+        monkeypatch.setenv("PET_GEMM_PAIR", "1")
+        two = c.gemm(A, W, "3xtf32")
+        ref = A.astype(np.float64) @ W.T.astype(np.float64)
+        err = np.abs(two - ref).max() / np.abs(ref).max()
+        assert err <= 2e-6 + 0.5 * (3 * k / 8) * 2.0 ** -24, (m, n, k, err)
+        assert np.array_equal(one, two), (m, n, k, np.abs(one - two).max())
+    c.close()

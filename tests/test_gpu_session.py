@@ -25,6 +25,22 @@ def full_list(s, cutoff, skin=0.0):
     return EdgeListView(s["positions"], s["atomic_numbers"], off, idx[:, 1], idx[:, 2:5], s["cell"])
 
 
+def held_to_the_reference(reference, models, view, r):
+    """The same list through the reference's own compute_edges (its host build): energy, forces and virial within the
+    parity bands. The device-list forms below are compared with the host list's answer to the bit; this ties that
+    answer, on the very list of the test, to the reference."""
+    jp, sp = models("tiny", "feedforward", "scaled", 1)
+    lst = {"positions": np.asarray(view.positions), "atomic_numbers": np.asarray(view.atomic_numbers, np.int32),
+           "offsets": np.asarray(view.offsets, np.int32), "neighbors": np.asarray(view.neighbors, np.int32),
+           "shifts": None if view.shifts is None else np.asarray(view.shifts, np.int32), "cell": view.cell,
+           "n_local": -1, "half": False}
+    ref = reference.ReferenceCalculator(str(jp), str(sp)).compute_edges(lst, True, False)
+    scale = max(abs(ref["energy"][0]), np.abs(ref["per_atom_energy"]).sum())
+    assert abs(r.energy[0] - ref["energy"][0]) <= 1e-6 * scale
+    assert np.abs(r.forces - ref["forces"]).max() <= 1e-5 * max(1.0, np.abs(ref["forces"]).max())
+    assert np.abs(r.virial - ref["virial"]).max() <= 1e-5 * max(1.0, np.abs(ref["virial"]).max())
+
+
 def test_shifts_list_matches_own_search(calc):
     """tests/test_edges.cpp:180-208: an engine's periodic list with shifts gives the periodic answer."""
     s = st.diamond(2, jitter=0.05, seed=0)
@@ -217,7 +233,7 @@ def test_device_arrays_step_adds_into_the_engines_arrays(lib_path, models, fixed
 
 @pytest.mark.parametrize("renumbered", [False, True])
 @pytest.mark.parametrize("order", ["listed", "interleaved", "strided"])
-def test_flat_pair_list_on_the_device_gets_what_the_host_list_does(calc, renumbered, order):
+def test_flat_pair_list_on_the_device_gets_what_the_host_list_does(calc, reference, models, renumbered, order):
     """tests/test_edges.cpp:709-779: the engine numbers the atoms backwards and hands the pairs over flat, in list
     order or each atom's pairs interleaved with the others'; with the renumbering the answer comes back in ours."""
     import torch
@@ -225,6 +241,7 @@ def test_flat_pair_list_on_the_device_gets_what_the_host_list_does(calc, renumbe
     n = s["n_atoms"]
     v = full_list(s, calc.cutoff, skin=0.5)
     ref = calc.compute_edges(v)
+    held_to_the_reference(reference, models, v, ref)
     off = np.asarray(v.offsets)
     P = int(off[-1])
     theirs = np.arange(n)[::-1].copy() if renumbered else np.arange(n)
@@ -302,7 +319,7 @@ def test_flat_pair_list_errors(calc):
 
 
 @pytest.mark.parametrize("layout", ["rows", "columns"])
-def test_device_list_gets_the_bits_of_the_host_list(calc, layout):
+def test_device_list_gets_the_bits_of_the_host_list(calc, reference, models, layout):
     """tests/test_edges.cpp:528-587: the engine's 2-D neighbour array in device memory (either layout, the engine's
     flag bits above the index masked off, centres listed out of order) gives what the same list gives from the host."""
     import torch
@@ -313,6 +330,7 @@ def test_device_list_gets_the_bits_of_the_host_list(calc, layout):
     v = full_list(c, calc.cutoff, skin=0.4)
     calc.set_neighbors(v)
     ref = calc.compute_step(c["positions"], c["cell"])  # the host list carries (zero) shifts
+    held_to_the_reference(reference, models, v, ref)
     off = np.asarray(v.offsets)
     counts = np.diff(off)
     M = int(counts.max())

@@ -151,3 +151,80 @@ def test_adaptive_cutoff_over_cached_pairs(models, tmp_path):
     close(staged(cached, systems, x), staged(plain, systems, x))
     assert cached.neighbor_searches == 1 and cached.neighbor_reuses == 1
     plain.close(), cached.close()
+
+
+def moved_systems(systems, x):
+    out, at = [], 0
+    for s in systems:
+        n = s["n_atoms"]
+        out.append(st.make_system(s["atomic_numbers"], x[at:at + n], s["cell"], pbc=tuple(s["pbc"])))
+        at += n
+    return out
+
+
+def ref_close(r, ref):
+    scale = max(np.abs(ref["energy"]).max(), 1e-3)
+    assert np.abs(r.energy - ref["energy"]).max() <= 1e-6 * scale
+    assert np.abs(r.forces - ref["forces"]).max() <= 1e-5 * max(1.0, np.abs(ref["forces"]).max())
+    assert np.abs(r.virial - ref["virial"]).max() <= 1e-5 * max(1.0, np.abs(ref["virial"]).max())
+
+
+@pytest.mark.parametrize("featurizer", ["feedforward", "residual"])
+def test_cached_steps_match_the_reference_at_the_moved_positions(reference, models, featurizer):
+    """The cached pairs' answers against the reference's own evaluation of the moved structures (its Calculator::compute
+    on the host build), not only against this library's plain search."""
+    cached = make(models, True, featurizer)
+    rcalc = reference.ReferenceCalculator(*[str(p) for p in models("tiny", featurizer, "scaled", 3)])
+    systems = batch()
+    ref_close(staged(cached, systems, first=True), rcalc.compute(systems))
+    x = np.concatenate([s["positions"] for s in systems])
+    rng = np.random.default_rng(4)
+    for _ in range(3):
+        x = x + rng.normal(0, 0.04, x.shape)
+        ref_close(staged(cached, systems, x), rcalc.compute(moved_systems(systems, x)))
+    assert cached.neighbor_searches == 1 and cached.neighbor_reuses == 3
+    cached.close()
+
+
+def test_a_shrinking_batch_keeps_its_cached_pairs(reference, models):
+    """A batched relaxation: structures finish one by one and the batch is packed to the front (the reference's
+    geom.staged, include/pet/calculator.hpp:214-218; cache_reassemble, src/device_geometry.cpp:203-246). The structures
+    that stay keep the positions they have on the device and their cached pairs, renumbered: no new search, and the
+    answers are those of the reference for the remaining structures where they are now."""
+    cached, plain = make(models, True), make(models, False)
+    rcalc = reference.ReferenceCalculator(*[str(p) for p in models("tiny", "feedforward", "scaled", 3)])
+    systems = batch()
+    staged(cached, systems, first=True)
+    x = np.concatenate([s["positions"] for s in systems])
+    x = x + np.random.default_rng(5).normal(0, 0.03, x.shape)
+    all4 = staged(cached, systems, x)
+    assert cached.neighbor_searches == 1 and cached.neighbor_reuses == 1
+    now = moved_systems(systems, x)
+    # structure 1 is done; the others move on, 3 first
+    keep = [3, 0, 2]
+    cached.keep_staged(keep)
+    cached.compute_staged(True)
+    r = cached.fetch()
+    kept = [now[k] for k in keep]
+    ref_close(r, rcalc.compute(kept))
+    close(r, plain.compute(kept))
+    off = np.concatenate([[0], np.cumsum([s["n_atoms"] for s in systems])])
+    for slot, k in enumerate(keep):  # and each structure's numbers are the ones it had in the whole batch
+        assert abs(r.energy[slot] - all4.energy[k]) <= 1e-6 * max(abs(all4.energy[k]), 1e-3)
+    assert cached.neighbor_searches == 1 and cached.neighbor_reuses == 2, "the pairs followed the structures"
+    # stepping goes on in the smaller batch, and shrinking once more still needs no search
+    x3 = np.concatenate([s["positions"] for s in kept])
+    x3 = x3 + np.random.default_rng(6).normal(0, 0.03, x3.shape)
+    ref_close(staged(cached, kept, x3), rcalc.compute(moved_systems(kept, x3)))
+    cached.keep_staged([1])
+    cached.compute_staged(True)
+    ref_close(cached.fetch(), rcalc.compute([moved_systems(kept, x3)[1]]))
+    assert cached.neighbor_searches == 1 and cached.neighbor_reuses == 4
+    # without a cache the same call just restages the kept structures
+    staged(plain, systems, first=True)
+    plain.keep_staged([2])
+    plain.compute_staged(True)
+    ref_close(plain.fetch(), rcalc.compute([systems[2]]))
+    with pytest.raises(ValueError):
+        cached.keep_staged([0, 0])
+    cached.close(), plain.close()
