@@ -353,7 +353,7 @@ def measure_cell(args, workload, rank, world, local, dist, steps, warmup, tmpdir
         step_ms = float(np.sum(dev_ms))
     rec = {"workload": workload, "model": f"random-init pet-omat-{shape}-like", "scaling": "strong", "n_gpus": world,
            "value": n_total * steps / wall, "unit": UNIT, "steps": steps, "warmup": warmup,
-           "ms_per_step": wall / steps * 1e3, "device_ms_per_step": step_ms / steps, "atoms_total": n_total,
+           "ms_per_step": wall / steps * 1e3, "device_ms_per_step": (step_ms / steps) or None, "atoms_total": n_total,
            "kept_edges_rank0": n_edges, "max_neighbors": max_nb, "recompute": plan["tier"],
            "pool_gib_rank0": plan["pool_bytes"] / 2 ** 30, "gpu_launches": int(launches), "classes_rank0": classes,
            "non_kernel_ms_per_step": wall / steps * 1e3 - sum(v["ms"] for v in prof.values()),

@@ -20,6 +20,7 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <numeric>
@@ -47,7 +48,12 @@ const NcclApi& nccl() {
   static NcclApi api;
   static std::once_flag once;
   std::call_once(once, [] {
-    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    // PET_NCCL_LIB names the library file; otherwise the soname, which resolves to a copy the process has already
+    // loaded (PyTorch's bundled one, an MD engine's) before it looks on the search path. A process that will load
+    // PyTorch later should load it first: two different NCCL versions under one soname do not mix.
+    void* h = nullptr;
+    if (const char* path = std::getenv("PET_NCCL_LIB")) h = dlopen(path, RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
     if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
     if (!h) return;
     auto sym = [&](const char* n) { return dlsym(h, n); };

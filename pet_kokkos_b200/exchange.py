@@ -263,6 +263,7 @@ class NativeNcclExchange:
     `dest` is this rank's routing ([n_remote, 2] from `route`), `owner` the global atom of every listed atom."""
 
     def __init__(self, dest, owner, n_total, device, group=None, single=False):
+        import torch  # noqa: F401  before the library looks for NCCL: it then finds the copy PyTorch bundles, not another
         from .calculator import load_library
         self._lib = load_library()
         self._h = None
