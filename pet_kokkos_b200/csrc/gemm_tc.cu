@@ -172,6 +172,88 @@ __device__ __forceinline__ float tf32_lo(float x) {
   return __uint_as_float(__float_as_uint(x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u)) + 0x1000u);
 }
 
+// ---- the epilogue of one tile, shared by the kernels below -------------------------------------
+//
+// What an epilogue reads from global memory (a residual, a saved pre-activation) does not depend on the accumulator,
+// and a DRAM round trip per batch of rows was what made an epilogue last longer than the next tile's MMAs: with two
+// accumulators in tensor memory the tile period is then (epilogue + MMAs) / 2 instead of the MMAs' time. So (1) while
+// an epilogue warp waits for its tile's accumulator it asks the L2 for the lines it is going to read, and (2) inside
+// a 32-column chunk the loads of all eight row groups are issued before the accumulator is fetched from tensor memory.
+template <int EPI>
+__device__ __forceinline__ void epilogue_prefetch(const GemmArgs& p, int row, int col0, int ncols) {
+  if (row >= p.M) return;
+  const float* base = nullptr;
+  size_t ld = 0;
+  int wide = 1;
+  if (EPI == EPI_PLAIN) {
+    if (!p.res || row < p.res_row0) return;
+    base = p.res, ld = size_t(p.ldr);
+  } else if (EPI == EPI_SILU_BWD) {
+    base = p.pre, ld = size_t(p.ldp);
+  } else if (EPI == EPI_SWIGLU_BWD) {
+    base = p.pre, ld = size_t(p.ldp), wide = 2;
+  } else {
+    return;
+  }
+  if (col0 + ncols > p.N) ncols = p.N - col0;
+  const float* r = base + size_t(row) * ld + size_t(wide) * col0;
+  for (int c = 0; c < wide * ncols; c += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(r + c));
+}
+
+// Rows m0 + 32 q .. + 31, columns n0 + half BN/2 .. of the accumulator at `acc` (this warp's quarter of the lanes
+// already in the address), through this warp's pad; `release` runs once the accumulator has been read.
+template <int EPI, int BN, class Release>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& p, uint32_t acc, float* pad, int m0, int n0, int q, int half, int lane,
+                                              Release release) {
+  constexpr int kBatch = (EPI == EPI_SWIGLU_BWD || EPI == EPI_COMPRESS) ? 4 : 8;  // row groups whose loads are in flight together
+  const int sub = lane >> 3, c4 = (lane & 7) * 4;  // row-within-group and column of this lane's 16 bytes
+#pragma unroll 1
+  for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+    const int col = n0 + c0 + c4;
+    EpiLoad ld[8];
+    if (kBatch == 8 && col < p.N) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int row = m0 + q * 32 + u * 4 + sub;
+        if (row < p.M) ld[u] = epilogue_load4<EPI>(p, row, col);
+      }
+    }
+    float v[32];
+    tmem_ld32(acc + c0, v);
+    if (c0 + 32 == (half + 1) * (BN / 2)) {  // the accumulator has been read: the issuer may reuse it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) release();
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      *reinterpret_cast<float4*>(pad + lane * kPad + (((j >> 2) ^ (lane & 7)) << 2)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    __syncwarp();
+    if (col < p.N) {
+#pragma unroll
+      for (int h = 0; h < 8 / kBatch; ++h) {
+        if (kBatch == 4) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int row = m0 + q * 32 + (h * 4 + u) * 4 + sub;
+            if (row < p.M) ld[u] = epilogue_load4<EPI>(p, row, col);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const int rr = (h * kBatch + u) * 4 + sub, row = m0 + q * 32 + rr;
+          if (row < p.M) {
+            const float4 a = *reinterpret_cast<const float4*>(pad + rr * kPad + (((lane & 7) ^ (rr & 7)) << 2));
+            const float accv[4] = {a.x, a.y, a.z, a.w};
+            epilogue_apply4<EPI>(p, row, col, accv, ld[u]);
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int EPI, int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
     k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -281,51 +363,15 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
     const int q = warp & 3;          // the quarter of the 128 lanes this warp may read
     const int half = ew >> 2;        // which half of the BN columns
     float* pad = pads + size_t(ew) * 32 * kPad;
-    const int sub = lane >> 3, c4 = (lane & 7) * 4;  // row-within-group and column of this lane's 16 bytes
     int i = 0;
     for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++i) {
       const int b = i & 1;
       const int m0 = (t / tiles_n) * TBM, n0 = (t % tiles_n) * BN;
+      epilogue_prefetch<EPI>(p, m0 + q * 32 + lane, n0 + half * (BN / 2), BN / 2);
       if (!mbar_wait(tfull + b, (i >> 1) & 1, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t acc = tmem + uint32_t(b * BN) + (uint32_t(q * 32) << 16);
-#pragma unroll 1
-      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
-        float v[32];
-        tmem_ld32(acc + c0, v);
-        if (c0 + 32 == (half + 1) * (BN / 2)) {  // the accumulator has been read: the issuer may reuse it
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(tempty + b);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(pad + lane * kPad + (((j >> 2) ^ (lane & 7)) << 2)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        __syncwarp();
-        const int col = n0 + c0 + c4;
-        if (col < p.N) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {  // four row groups at a time: their loads first, then their arithmetic and stores
-            EpiLoad ld[4];
-            int rows[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              rows[u] = m0 + q * 32 + (h * 4 + u) * 4 + sub;
-              if (rows[u] < p.M) ld[u] = epilogue_load4<EPI>(p, rows[u], col);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              if (rows[u] < p.M) {
-                const int rr = (h * 4 + u) * 4 + sub;
-                const float4 a = *reinterpret_cast<const float4*>(pad + rr * kPad + (((lane & 7) ^ (rr & 7)) << 2));
-                const float accv[4] = {a.x, a.y, a.z, a.w};
-                epilogue_apply4<EPI>(p, rows[u], col, accv, ld[u]);
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile<EPI, BN>(p, acc, pad, m0, n0, q, half, lane, [&] { mbar_arrive(tempty + b); });
     }
   } else if (B16 && warp >= kSplitWarp0) {
     // A's fp32 slab (128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7)) rounded to bf16 into the tile beside
@@ -389,6 +435,177 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
 }
 
 
+// ---- the 3xTF32 product with A on its own, deeper ring ---------------------------------------
+//
+// In k_gemm_tc's 3xTF32 form a stage holds 16 columns of A, A's low part and both parts of the 256-row B tile: 48 KB,
+// of which A itself is 8 KB, so four stages keep at most 24 KB of A in flight per SM. A comes from HBM (B, the weights,
+// sits in L2), and an SM's share of the HBM bandwidth times a DRAM round trip under load is about 50 KB: the A stream
+// runs short of bytes in flight, a tile takes 19.6 k clocks against 12.3 k of MMA, and the tf32 form, whose four
+// stages hold 64 KB of A, does not have the problem. Here A gets its own ring of eight 8 KB slots (seven in flight),
+// while B (hi and lo) and A's low part, which need no look-ahead beyond hiding an L2 round trip and the splitter,
+// share a ring of three. One producer thread feeds each ring. Same MMAs in the same order: same bits.
+template <int NA_, int NB_>
+struct SmemRing {
+  static constexpr int BN = 256, BK = 16, kASlots = NA_, kBSlots = NB_;
+  static constexpr int kA = TBM * BK * 4, kB = BN * BK * 4;     // 8 KB, 16 KB
+  static constexpr int kRingA = kASlots * kA;                   // A as it lands
+  static constexpr int kSlotB = 2 * kB + kA;                    // B hi, B lo, A lo
+  static constexpr int kTiles = kRingA + kBSlots * kSlotB;
+  static constexpr int kPads = kEpiWarps * 32 * kPad * 4;
+  static constexpr int kTotal = kTiles + kPads + 1024 + 256;
+  static constexpr int kThreads = 512;
+};
+
+template <int EPI, int NA_, int NB_>
+__global__ void __launch_bounds__(512, 1)
+    k_gemm_tc_ring(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_blo, GemmArgs p, int* err) {
+  using L = SmemRing<NA_, NB_>;
+  constexpr int BN = L::BN, TBK = L::BK, NA = L::kASlots, NB = L::kBSlots;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring_b = tiles + L::kRingA;
+  float* pads = reinterpret_cast<float*>(tiles + L::kTiles);
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(tiles + L::kTiles + L::kPads);  // [NA] A slot landed
+  uint64_t* empty_a = full_a + NA;    // [NA] the slot's MMAs are done
+  uint64_t* full_b = empty_a + NA;    // [NB] B hi and lo landed
+  uint64_t* empty_b = full_b + NB;    // [NB] the slot's MMAs are done (B and A's low part with them)
+  uint64_t* split = empty_b + NB;     // [NB] A's low part written
+  uint64_t* tfull = split + NB;       // [2]
+  uint64_t* tempty = tfull + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + TBM - 1) / TBM;
+  const int n_tiles = tiles_m * tiles_n;
+  const int nkb = (p.K + TBK - 1) / TBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NA; ++s) mbar_init(full_a + s, 1), mbar_init(empty_a + s, 1);
+    for (int s = 0; s < NB; ++s) mbar_init(full_b + s, 1), mbar_init(empty_b + s, 1), mbar_init(split + s, 128);
+    for (int b = 0; b < 2; ++b) mbar_init(tfull + b, 1), mbar_init(tempty + b, kEpiWarps);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {  // A: up to seven slots ahead of the MMAs
+      int g = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * TBM;
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const int s = g % NA;
+          if (!(ok = mbar_wait(empty_a + s, ((g / NA) & 1) ^ 1, abort_flag))) break;
+          mbar_expect_tx(full_a + s, L::kA);
+          tma_load_2d(tiles + size_t(s) * L::kA, &map_a, full_a + s, kb * TBK, m0);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {  // B, both parts
+      int g = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+        const int n0 = (t % tiles_n) * BN;
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const int s = g % NB;
+          if (!(ok = mbar_wait(empty_b + s, ((g / NB) & 1) ^ 1, abort_flag))) break;
+          uint8_t* sb = ring_b + size_t(s) * L::kSlotB;
+          mbar_expect_tx(full_b + s, 2 * L::kB);
+          tma_load_2d(sb, &map_b, full_b + s, kb * TBK, n0);
+          tma_load_2d(sb + L::kB, &map_blo, full_b + s, kb * TBK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(BN);
+      int g = 0, i = 0;
+      for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++i) {
+        const int b = i & 1;
+        bool ok = mbar_wait(tempty + b, ((i >> 1) & 1) ^ 1, abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + uint32_t(b * BN);
+        for (int kb = 0; ok && kb < nkb; ++kb, ++g) {
+          const int sa = g % NA, sb = g % NB;
+          if (!(ok = mbar_wait(split + sb, (g / NB) & 1, abort_flag))) break;   // A landed and its low part is written
+          if (!(ok = mbar_wait(full_b + sb, (g / NB) & 1, abort_flag))) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a0 = smem_u32(tiles + size_t(sa) * L::kA);
+          const uint32_t b0 = smem_u32(ring_b + size_t(sb) * L::kSlotB), bl0 = b0 + L::kB, al0 = b0 + 2 * L::kB;
+#pragma unroll
+          for (int k = 0; k < TBK / 8; ++k) {
+            const uint64_t da = smem_desc<TBK>(a0 + 32 * k), db = smem_desc<TBK>(b0 + 32 * k);
+            const uint64_t dal = smem_desc<TBK>(al0 + 32 * k), dbl = smem_desc<TBK>(bl0 + 32 * k);
+            mma_tf32(acc, da, dbl, idesc, (kb | k) != 0);
+            mma_tf32(acc, dal, db, idesc, 1);
+            mma_tf32(acc, da, db, idesc, 1);
+          }
+          mma_commit(empty_a + sa);
+          mma_commit(empty_b + sb);
+        }
+        if (!ok) break;
+        mma_commit(tfull + b);
+      }
+    }
+  } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps) {
+    const int ew = warp - kEpiWarp0;
+    const int q = warp & 3;
+    const int half = ew >> 2;
+    float* pad = pads + size_t(ew) * 32 * kPad;
+    int i = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++i) {
+      const int b = i & 1;
+      const int m0 = (t / tiles_n) * TBM, n0 = (t % tiles_n) * BN;
+      epilogue_prefetch<EPI>(p, m0 + q * 32 + lane, n0 + half * (BN / 2), BN / 2);
+      if (!mbar_wait(tfull + b, (i >> 1) & 1, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t acc = tmem + uint32_t(b * BN) + (uint32_t(q * 32) << 16);
+      epilogue_tile<EPI, BN>(p, acc, pad, m0, n0, q, half, lane, [&] { mbar_arrive(tempty + b); });
+    }
+  } else if (warp >= kSplitWarp0) {
+    // A's low part, from its ring slot into the B slot that travels with it: needs the A slot landed and the B slot free
+    const int tid = threadIdx.x - kSplitWarp0 * 32;
+    constexpr int n16 = L::kA / 16;
+    int g = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+      for (int kb = 0; kb < nkb; ++kb, ++g) {
+        const int sa = g % NA, sb = g % NB;
+        if (!(ok = mbar_wait(empty_b + sb, ((g / NB) & 1) ^ 1, abort_flag))) break;
+        if (!(ok = mbar_wait(full_a + sa, (g / NA) & 1, abort_flag))) break;
+        const float4* hi = reinterpret_cast<const float4*>(tiles + size_t(sa) * L::kA);
+        float4* lo = reinterpret_cast<float4*>(ring_b + size_t(sb) * L::kSlotB + 2 * L::kB);
+#pragma unroll 4
+        for (int e = tid; e < n16; e += 128) {
+          const float4 x = hi[e];
+          float4 y;
+          y.x = tf32_lo(x.x), y.y = tf32_lo(x.y), y.z = tf32_lo(x.z), y.w = tf32_lo(x.w);
+          lo[e] = y;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(split + sb);
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(err, 1);
+}
+
 // ---- the same product on a pair of CTAs ------------------------------------------------------
 //
 // k_gemm_tc above is short of shared-memory bandwidth in the 3xTF32 mode: per 8 columns of K a CTA moves 64 KB through
@@ -400,8 +617,8 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
 //
 // Who signals whom (every barrier exists in both CTAs at the same offset; "leader" is the even CTA):
 //   full[s]    own CTA's TMA loads landed (each CTA loads with the plain, CTA-local form; no multicast anywhere)
-//   split[s]   LEADER's: 256 arrivals, the splitter threads of both CTAs (the odd CTA's arrive remotely) once their lo
-//              tile is written: both CTAs' operands of the stage are then complete
+//   split[s]   LEADER's: 2 arrivals, one thread of each CTA's splitter warps (the odd CTA's arrives remotely) once the
+//              four warps have written their lo tile and met at a named barrier: both CTAs' operands are then complete
 //   empty[s]   own CTA's: the leader's issuer commits the stage's MMAs to its own and to the odd CTA's barrier
 //   tfull[b]   own CTA's: the leader commits the finished accumulator to both
 //   tempty[b]  LEADER's: 16 arrivals, the epilogue warps of both CTAs once they have read the accumulator
@@ -458,9 +675,9 @@ __host__ __device__ constexpr uint32_t idesc_tf32_pair(int n) {  // M = 256 over
   return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(256 >> 4) << 24);
 }
 
-template <int STAGES>
+template <int STAGES, int BK_ = 32>
 struct SmemPair {
-  static constexpr int BN = 256, BK = 32;
+  static constexpr int BN = 256, BK = BK_;
   static constexpr int kA = TBM * BK * 4, kBh = (BN / 2) * BK * 4;  // A's rows, and this CTA's half of B's
   static constexpr int kHi = kA + kBh;
   static constexpr int kStage = 2 * kHi;  // with the lo tiles
@@ -470,11 +687,11 @@ struct SmemPair {
   static constexpr int kThreads = 512;
 };
 
-template <int EPI, int STAGES>
+template <int EPI, int STAGES, int BK_>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
     k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_blo, GemmArgs p, int* err) {
-  using L = SmemPair<STAGES>;
+  using L = SmemPair<STAGES, BK_>;
   constexpr int BN = L::BN, TBK = L::BK;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -498,7 +715,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
-      mbar_init(split + s, 256);
+      mbar_init(split + s, 2);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull + b, 1);
@@ -563,6 +780,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
         if (!ok) break;
         mma_commit_pair(smem_u32(tfull + b));
         mma_commit_pair(peer_smem(tfull + b, 1));
+
       }
     }
   } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps) {
@@ -570,51 +788,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
     const int q = warp & 3;
     const int half = ew >> 2;
     float* pad = pads + size_t(ew) * 32 * kPad;
-    const int sub = lane >> 3, c4 = (lane & 7) * 4;
     int i = 0;
     for (int t = pair; t < n_tiles; t += n_pairs, ++i) {
       const int b = i & 1;
       const int m0 = (t / tiles_n) * 2 * TBM + int(rank) * TBM, n0 = (t % tiles_n) * BN;
+      epilogue_prefetch<EPI>(p, m0 + q * 32 + lane, n0 + half * (BN / 2), BN / 2);
       if (!mbar_wait(tfull + b, (i >> 1) & 1, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t acc = tmem + uint32_t(b * BN) + (uint32_t(q * 32) << 16);
-#pragma unroll 1
-      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
-        float v[32];
-        tmem_ld32(acc + c0, v);
-        if (c0 + 32 == (half + 1) * (BN / 2)) {  // read: the leader's issuer may reuse this accumulator in both CTAs
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(peer_smem(tempty + b, 0));
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(pad + lane * kPad + (((j >> 2) ^ (lane & 7)) << 2)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        __syncwarp();
-        const int col = n0 + c0 + c4;
-        if (col < p.N) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            EpiLoad ld[4];
-            int rows[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              rows[u] = m0 + q * 32 + (h * 4 + u) * 4 + sub;
-              if (rows[u] < p.M) ld[u] = epilogue_load4<EPI>(p, rows[u], col);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              if (rows[u] < p.M) {
-                const int rr = (h * 4 + u) * 4 + sub;
-                const float4 a = *reinterpret_cast<const float4*>(pad + rr * kPad + (((lane & 7) ^ (rr & 7)) << 2));
-                const float accv[4] = {a.x, a.y, a.z, a.w};
-                epilogue_apply4<EPI>(p, rows[u], col, accv, ld[u]);
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile<EPI, BN>(p, acc, pad, m0, n0, q, half, lane, [&] { mbar_arrive_cluster(peer_smem(tempty + b, 0)); });
     }
   } else if (warp >= kSplitWarp0) {
     const int tid = threadIdx.x - kSplitWarp0 * 32;
@@ -636,7 +818,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
           lo[e] = y;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive_cluster(split0 + 8u * uint32_t(s));
+        // one arrival per CTA and stage: 128 arrivals from the odd CTA, each a transaction across the cluster, cost the
+        // leader 1.2 k clocks of waiting per stage
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid == 0) mbar_arrive_cluster(split0 + 8u * uint32_t(s));
       }
     }
   }
@@ -733,19 +918,40 @@ void launch_tc(Stream& st, const GemmArgs& a) {
   PETB_LAUNCH_CHECK(st);
 }
 
+// The ring kernel serves the 3xTF32 mode's widest tiles with pre-split weights when PET_GEMM_RING=1 (eight A slots,
+// three B slots) or 2 (four and four). It measures the same as the staged kernel, which stays the default.
+bool ring_enabled() {
+  const char* e = std::getenv("PET_GEMM_RING");
+  return e && (e[0] == '1' || e[0] == '2');
+}
+
+template <int EPI, int NA_, int NB_>
+void launch_tc_ring(Stream& st, const GemmArgs& a) {
+  using L = SmemRing<NA_, NB_>;
+  static_assert(L::kTotal <= 227 * 1024, "the rings do not fit shared memory");
+  static SmemOptIn opted;
+  auto kernel = k_gemm_tc_ring<EPI, NA_, NB_>;
+  opt_in_shared_memory(kernel, L::kTotal, opted);
+  const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM, L::BK), mb = make_map(a.B, a.N, a.K, a.ldb, L::BN, L::BK);
+  const CUtensorMap mblo = make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, L::BN, L::BK);
+  const long long tiles = (long long) cdiv(a.M, TBM) * cdiv(a.N, L::BN);
+  const int grid = int(tiles < state().sms ? tiles : state().sms);
+  kernel<<<grid, L::kThreads, L::kTotal, st.s>>>(ma, mb, mblo, a, state().err);
+  PETB_LAUNCH_CHECK(st);
+}
+
 // The pair kernel serves the 3xTF32 mode's widest tiles (N a multiple of 256, weights pre-split) when PET_GEMM_PAIR=1.
 bool pair_enabled() {  // read at every call, so that one process can compare the two kernels
   const char* e = std::getenv("PET_GEMM_PAIR");
   return e && e[0] == '1';
 }
 
-template <int EPI>
+template <int EPI, int STAGES = 3, int BK_ = 32>
 void launch_tc_pair(Stream& st, const GemmArgs& a) {
-  constexpr int STAGES = 3;
-  using L = SmemPair<STAGES>;
+  using L = SmemPair<STAGES, BK_>;
   static_assert(L::kTotal <= 227 * 1024, "the pair's tile pipeline does not fit shared memory");
   static SmemOptIn opted;
-  auto kernel = k_gemm_tc_pair<EPI, STAGES>;
+  auto kernel = k_gemm_tc_pair<EPI, STAGES, BK_>;
   opt_in_shared_memory(kernel, L::kTotal, opted);
   const CUtensorMap ma = make_map(a.A, a.M, a.K, a.lda, TBM, L::BK);
   const CUtensorMap mb = make_map(a.B, a.N, a.K, a.ldb, L::BN / 2, L::BK);
@@ -778,7 +984,16 @@ void dispatch_tc(Stream& st, const GemmArgs& a, int mode) {
   else if (a.N % 128 == 0 && mt * (a.N / 128) >= sms) bn = 128;
   else if (a.N % 64 != 0) bn = a.N % 256 == 0 ? 256 : 128;  // ragged widths: a wide tile with a zero-filled edge
   if (bn == 256) {
-    if (x3 && a.b_lo_offset && pair_enabled() && cdiv(a.M, 2 * TBM) * (a.N / 256) >= sms / 2) return launch_tc_pair<EPI>(st, a);
+    if (x3 && a.b_lo_offset && pair_enabled() && cdiv(a.M, 2 * TBM) * (a.N / 256) >= sms / 2) {
+      const char* e = std::getenv("PET_GEMM_PAIR");
+      if (e[1] == '6') return launch_tc_pair<EPI, 6, 16>(st, a);  // "16": six stages of 16 columns
+      return launch_tc_pair<EPI, 3, 32>(st, a);
+    }
+    if (x3 && a.b_lo_offset && ring_enabled()) {
+      const char* e = std::getenv("PET_GEMM_RING");
+      if (e && e[0] == '2') return launch_tc_ring<EPI, 4, 4>(st, a);
+      return launch_tc_ring<EPI, 8, 3>(st, a);
+    }
     if (b16) return launch_tc<EPI, 256, 4, TC_BF16>(st, a);
     if (x3) return fine_stages() ? launch_tc<EPI, 256, 4, TC_X3>(st, a) : launch_tc<EPI, 256, 2, TC_X3>(st, a);
     return launch_tc<EPI, 256, 4, TC_TF32>(st, a);

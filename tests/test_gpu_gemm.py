@@ -51,11 +51,13 @@ def test_native_rows_do_not_depend_on_the_batch(calc):
     assert (full[:77] == part).all()
 
 
-def test_pair_kernel_gives_the_bits_of_the_single_cta_kernel(lib_path, models, monkeypatch):
-    """The 3xTF32 product on a pair of CTAs (tcgen05.mma.cta_group::2 over a 256 x 256 tile, each CTA staging half of the
-    weight tile; PET_GEMM_PAIR=1) adds the same products in the same order as the one-CTA kernel, so it must return
-    the same bits; both are held to the fp64 product. Shapes: every row tile full, a ragged last pair (one whose second
-    CTA has no rows at all), two column tiles, a contraction that is not a multiple of the 32-column stage."""
+def test_the_three_split_product_kernels_give_the_same_bits(lib_path, models, monkeypatch):
+    """The 3xTF32 product of a pre-split weight has three kernels: stages that carry A and B together
+    (the default), A on its own deeper ring (PET_GEMM_RING=1), and a pair of CTAs sharing a 256 x 256 tile with
+    tcgen05.mma.cta_group::2, each staging half of the weight tile (PET_GEMM_PAIR=1). All add the same products in the
+    same order, so they must return the same bits; one is also held to the fp64 product. Shapes: every row tile full, a
+    ragged last tile (and a pair whose second CTA has no rows at all), two column tiles, a contraction that is not a
+    multiple of the 32-column stage, a long contraction."""
     from pet_kokkos_b200 import Calculator
     c = Calculator(*models("tiny"))
     rng = np.random.default_rng(5)
@@ -63,11 +65,15 @@ def test_pair_kernel_gives_the_bits_of_the_single_cta_kernel(lib_path, models, m
         A = rng.normal(size=(m, k)).astype(np.float32)
         W = rng.normal(size=(n, k)).astype(np.float32)
         monkeypatch.setenv("PET_GEMM_PAIR", "0")
-        one = c.gemm(A, W, "3xtf32")
+        monkeypatch.setenv("PET_GEMM_RING", "0")
+        staged = c.gemm(A, W, "3xtf32")
+        monkeypatch.setenv("PET_GEMM_RING", "1")
+        ring = c.gemm(A, W, "3xtf32")
         monkeypatch.setenv("PET_GEMM_PAIR", "1")
-        two = c.gemm(A, W, "3xtf32")
+        pair = c.gemm(A, W, "3xtf32")
         ref = A.astype(np.float64) @ W.T.astype(np.float64)
-        err = np.abs(two - ref).max() / np.abs(ref).max()
+        err = np.abs(ring - ref).max() / np.abs(ref).max()
         assert err <= 2e-6 + 0.5 * (3 * k / 8) * 2.0 ** -24, (m, n, k, err)
-        assert np.array_equal(one, two), (m, n, k, np.abs(one - two).max())
+        assert np.array_equal(staged, ring), (m, n, k, np.abs(staged - ring).max())
+        assert np.array_equal(staged, pair), (m, n, k, np.abs(staged - pair).max())
     c.close()
