@@ -53,7 +53,9 @@ METRIC = "atom_evals_per_s"
 UNIT = "atom-evals/s"
 # DRAM traffic of one weight-GEMM launch per token row (atoms + kept edges), from one ncu capture:
 # dram__bytes_read.sum + dram__bytes_write.sum averaged over seven consecutive k_gemm_tc launches of the water648
-# workload, token-row and atom-row GEMMs as they come (50.2 MB at 25 320 rows; profiles/k_gemm_tc_water648_s_3xtf32.md).
+# workload, token-row and atom-row GEMMs as they come (50.2 MB at 25 320 rows; the capture is summarised under profiles/).
+# Captured with the kernel as of commit 002f4a5; the mainloop has been re-profiled since on one 122 138-row launch
+# (201 MB, 1646 B per row for a plain 256 x 256 GEMM: the same "A once, C once"), so the figure stands.
 # A GEMM reads A once and writes C once, so it grows with the rows.
 GEMM_DRAM_BYTES_PER_TOKEN_ROW = 50.2e6 / 25320
 DTYPE_OF = {"native": "f32", "tf32": "tf32", "bf16": "bf16", "3xtf32": "f32 (3xTF32)"}
@@ -75,7 +77,13 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.first = index, None, [], 0
+
+    def mark(self):
+        """The timed region starts here: samples taken before (while nvidia-smi was starting up, during warm-up) are
+        not counted. The sampler is started before the warm-up on purpose: nvidia-smi's own start-up can hold the
+        driver for a tenth of a second or two, which inside a timed region of a few tenths doubled a step's time."""
+        self.first = len(self.lines)
 
     def start(self):
         try:
@@ -94,7 +102,7 @@ class ClockSampler:
         self.proc.terminate()
         self.t.join(timeout=2)
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        for ln in self.lines[self.first:]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -472,14 +480,16 @@ def run_ours(args):
     n_atoms = sum(s["n_atoms"] for s in systems)
 
     # ---- device-resident throughput: structures staged once, evaluated in place ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.5)  # let nvidia-smi finish starting up outside anything that is timed
     calc.stage(systems)
     for _ in range(args.warmup):
         calc.compute_staged(True)
         calc.fetch()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.mark()
     launches0 = calc.kernel_launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dev_ms = []
@@ -544,7 +554,7 @@ def run_ours(args):
                         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"],
                         "peak_source": f"{peaks['source']} cuBLAS bf16, sustained",
                         "traffic": GEMM_DRAM_BYTES_PER_TOKEN_ROW * (n_act + n_edges),
-                        "traffic_source": "ncu dram bytes per launch on water648 (profiles/k_gemm_tc_water648_s_3xtf32.md), "
+                        "traffic_source": "ncu dram bytes per launch on water648 (capture of commit 002f4a5, summarised under profiles/), "
                                           "scaled by token rows",
                         "launches": p["launches"], "avg_launch_ms": per_launch_ms}
                 # what the mode asks of the tensor cores: an fp32-accurate product is three tf32 MMAs, and tf32 runs at

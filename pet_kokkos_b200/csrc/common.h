@@ -7,6 +7,7 @@
 #include <cstddef>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <stdexcept>
 #include <string>
@@ -35,6 +36,18 @@ inline int cdiv(long long a, long long b) { return int((a + b - 1) / b); }
 // Failure injection for tests, on the host: when >= 0, the pools' cudaMalloc number g_fail_alloc_in from now reports
 // out of memory instead of allocating (once). No GPU fault is involved.
 inline long g_fail_alloc_in = -1;
+
+// PET_WS_POISON=1 (the reference's switch of the same name, include/pet/kokkos.hpp): every pool block is filled with
+// 0xFF bytes (NaNs as floats and doubles, -1 as ints) when it is allocated and again whenever the pool is reset, so
+// that a kernel reading something nobody wrote this evaluation shows up as NaNs in the results instead of passing
+// by the luck of what the memory held. A debugging aid: the fills synchronize the device.
+inline bool poison_pools() {
+  static const bool on = [] {
+    const char* e = std::getenv("PET_WS_POISON");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
 
 // Device scratch for one evaluation: a bump allocator over a few large blocks.
 // The first evaluations grow it (cudaMalloc); later ones of the same shapes
@@ -71,6 +84,7 @@ class Arena {
     if (g_fail_alloc_in >= 0 && g_fail_alloc_in-- == 0)
       throw Error(4, "cudaMalloc: out of memory (injected for a test)");
     PETB_CUDA(cudaMalloc(&b.ptr, size));
+    if (poison_pools()) PETB_CUDA(cudaMemset(b.ptr, 0xFF, size));
     b.size = size;
     b.used = bytes;
     blocks_.push_back(b);
@@ -97,6 +111,10 @@ class Arena {
       blocks_.push_back(b);
       ++generation_;
     }
+    if (poison_pools()) {
+      PETB_CUDA(cudaDeviceSynchronize());
+      for (auto& b : blocks_) PETB_CUDA(cudaMemset(b.ptr, 0xFF, b.size));
+    }
     for (auto& b : blocks_) b.used = 0;
     cur_ = 0;
     used_total_ = 0;
@@ -109,6 +127,7 @@ class Arena {
     Block b;
     if (g_fail_alloc_in >= 0 && g_fail_alloc_in-- == 0) throw Error(4, "cudaMalloc: out of memory (injected for a test)");
     PETB_CUDA(cudaMalloc(&b.ptr, bytes));
+    if (poison_pools()) PETB_CUDA(cudaMemset(b.ptr, 0xFF, bytes));
     b.size = bytes;
     blocks_.push_back(b);
     ++generation_;

@@ -163,8 +163,15 @@ def test_a_cpp_caller_gets_the_bits_the_ctypes_mirror_gets(lib_path, models, tmp
         if r is r3:
             want.append(r.edge_gradient.ravel())
     want += [r4.energy, r4.per_atom_energy, r4.forces.ravel(), r4.virial.ravel()]
+    sizes = [len(np.ravel(w)) for w in want]
     want = np.concatenate(want)
     assert got.shape == want.shape
+    at = 0
+    for k, n in enumerate(sizes):  # which block differs, for the failure message
+        if not np.array_equal(got[at:at + n], want[at:at + n]):
+            print(f"block {k} (of {len(sizes)}, {n} numbers) differs by {np.abs(got[at:at + n] - want[at:at + n]).max():.3e}; "
+                  f"first values {got[at:at + 3]} vs {want[at:at + 3]}")
+        at += n
     assert np.array_equal(got, want), np.abs(got - want).max()
     assert np.array_equal(r1.forces, r2.forces), "staged evaluation equals compute"
     c.close()

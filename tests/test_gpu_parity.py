@@ -256,3 +256,22 @@ def test_out_of_memory_is_recovered_by_smaller_pieces(models, lib_path):
     one.close()
     c.fail_alloc(-1)
     c.close()
+
+
+def test_two_devices_in_one_process(models, lib_path):
+    """pet_options.device allows calculators on several GPUs in one process: the kernels' shared-memory opt-ins, the
+    tensor-core path's error word and the SM count are per device, so the second device must work as the first does
+    (with process-wide caches its attention and tcgen05 launches were refused as invalid). Needs two GPUs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from pet_kokkos_b200 import Calculator
+    jp, sp = models("s")
+    s = st.workload("water648")
+    for gemm in ("native", "3xtf32"):
+        a, b = Calculator(jp, sp, gemm=gemm, device=0), Calculator(jp, sp, gemm=gemm, device=1)
+        ra, rb = a.compute(s), b.compute(s)
+        rb2, ra2 = b.compute(s), a.compute(s)  # interleaved: each call makes its own device current
+        for k in ("energy", "forces", "virial"):
+            assert np.array_equal(getattr(ra, k), getattr(rb, k)), (gemm, k)
+            assert np.array_equal(getattr(ra, k), getattr(ra2, k)) and np.array_equal(getattr(rb, k), getattr(rb2, k))
+        a.close(), b.close()
