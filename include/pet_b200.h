@@ -86,7 +86,10 @@ typedef struct pet_results {
  * ghost reads its partner edge's row from the rank that owns the ghost, once per message-passing layer in the
  * forward and once in the backward. Every pointer handed to the callbacks is a DEVICE pointer; `stream` is the
  * calculator's cudaStream_t. A callback either enqueues its transfers on that stream (NCCL send/recv, peer
- * copies) or synchronizes it, does the transfer its own way and returns once `in` is filled. Every rank makes the
+ * copies) or synchronizes it, does the transfer its own way and returns once `in` is filled. (The calculator's
+ * stream is non-blocking. Work a callback left on the legacy default stream, such as the tail of a blocking
+ * cudaMemcpy from pageable memory, is ordered before the calculator's next kernel by the library; work left on any
+ * other stream is the callback's to finish.) Every rank makes the
  * same sequence of calls, also with n_live = 0. Return 0, or non-zero to fail the evaluation.
  * (atoms_forward / atoms_reverse of the reference move per-atom values for the adaptive cutoff and D3; they are not
  * part of these callbacks, and an adaptive-cutoff model over an exchange is refused.) */

@@ -37,16 +37,27 @@ inline int cdiv(long long a, long long b) { return int((a + b - 1) / b); }
 // out of memory instead of allocating (once). No GPU fault is involved.
 inline long g_fail_alloc_in = -1;
 
-// PET_WS_POISON=1 (the reference's switch of the same name, include/pet/kokkos.hpp): every pool block is filled with
+// PET_WS_POISON=1 (the reference's switch of the same name, include/pet/kokkos.hpp) or PET_B200_WS_POISON=1 (this
+// library alone, for a process that also runs the reference): every pool block is filled with
 // 0xFF bytes (NaNs as floats and doubles, -1 as ints) when it is allocated and again whenever the pool is reset, so
 // that a kernel reading something nobody wrote this evaluation shows up as NaNs in the results instead of passing
 // by the luck of what the memory held. A debugging aid: the fills synchronize the device.
 inline bool poison_pools() {
   static const bool on = [] {
-    const char* e = std::getenv("PET_WS_POISON");
-    return e && e[0] == '1';
+    for (const char* name : {"PET_WS_POISON", "PET_B200_WS_POISON"})
+      if (const char* e = std::getenv(name))
+        if (e[0] == '1') return true;
+    return false;
   }();
   return on;
+}
+
+// The fill runs on the legacy stream, which the evaluators' non-blocking streams do not wait for: fence it on both
+// sides, or it lands on top of what the next kernels write.
+inline void poison_fill(void* p, size_t bytes) {
+  PETB_CUDA(cudaDeviceSynchronize());
+  PETB_CUDA(cudaMemset(p, 0xFF, bytes));
+  PETB_CUDA(cudaDeviceSynchronize());
 }
 
 // Device scratch for one evaluation: a bump allocator over a few large blocks.
@@ -84,7 +95,7 @@ class Arena {
     if (g_fail_alloc_in >= 0 && g_fail_alloc_in-- == 0)
       throw Error(4, "cudaMalloc: out of memory (injected for a test)");
     PETB_CUDA(cudaMalloc(&b.ptr, size));
-    if (poison_pools()) PETB_CUDA(cudaMemset(b.ptr, 0xFF, size));
+    if (poison_pools()) poison_fill(b.ptr, size);
     b.size = size;
     b.used = bytes;
     blocks_.push_back(b);
@@ -111,10 +122,8 @@ class Arena {
       blocks_.push_back(b);
       ++generation_;
     }
-    if (poison_pools()) {
-      PETB_CUDA(cudaDeviceSynchronize());
-      for (auto& b : blocks_) PETB_CUDA(cudaMemset(b.ptr, 0xFF, b.size));
-    }
+    if (poison_pools())
+      for (auto& b : blocks_) poison_fill(b.ptr, b.size);
     for (auto& b : blocks_) b.used = 0;
     cur_ = 0;
     used_total_ = 0;
@@ -127,7 +136,7 @@ class Arena {
     Block b;
     if (g_fail_alloc_in >= 0 && g_fail_alloc_in-- == 0) throw Error(4, "cudaMalloc: out of memory (injected for a test)");
     PETB_CUDA(cudaMalloc(&b.ptr, bytes));
-    if (poison_pools()) PETB_CUDA(cudaMemset(b.ptr, 0xFF, bytes));
+    if (poison_pools()) poison_fill(b.ptr, bytes);
     b.size = bytes;
     blocks_.push_back(b);
     ++generation_;
@@ -218,6 +227,17 @@ struct Stream {
   long long launches = 0;
   Profiler* prof = nullptr;
 };
+
+// After a caller's callback returns: what it put on the legacy default stream (a blocking cudaMemcpy from pageable
+// memory returns once the bytes are staged, before they have landed) is ordered before this stream's next work.
+// The evaluators' streams are non-blocking and would not wait for it otherwise.
+inline void order_after_legacy_stream(Stream& st) {
+  cudaEvent_t ev;
+  PETB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  PETB_CUDA(cudaEventRecord(ev, cudaStreamLegacy));
+  PETB_CUDA(cudaStreamWaitEvent(st.s, ev, 0));
+  PETB_CUDA(cudaEventDestroy(ev));
+}
 
 // Brackets the launches made in its lifetime; `flops` and `bytes` are the algorithmic work
 // of those launches (2MNK for a GEMM, the tensors an op must read and write once).

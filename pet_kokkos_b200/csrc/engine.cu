@@ -1016,6 +1016,7 @@ static StepOut session_step(Engine& I, const double* positions, bool on_device, 
     pk.n_live = n_live, pk.live_packed = live_packed, pk.remote_of = remote_of, pk.exchange = &s.exchange;
     if (s.exchange.set_live(s.exchange.user, live, n_live, static_cast<void*>(st.s)) != 0)
       throw Error(1, "pet: the exchange's set_live() failed");
+    order_after_legacy_stream(st);
   }
   I.last_B = 1, I.last_N = N;
   StepOut so;

@@ -865,6 +865,7 @@ TensorState& state() {
     if (major != 10 || s.sms <= 0) return;
     if (cudaMalloc(&s.err, sizeof(int)) != cudaSuccess) return;
     cudaMemset(s.err, 0, sizeof(int));
+    cudaStreamSynchronize(cudaStreamLegacy);  // the callers' streams do not wait for the legacy one
     if (cudaMallocHost(&s.err_host, sizeof(int)) != cudaSuccess) return;
     *s.err_host = 0;
     s.encode = reinterpret_cast<EncodeFn>(fn);

@@ -241,6 +241,9 @@ Model::Model(const Checkpoint& ck) : h_(ck.hypers), scale_(ck.energy_scale) {
     PETB_CUDA(cudaMalloc(&probes_, (probes.size() ? probes.size() : 1) * sizeof(double)));
     PETB_CUDA(cudaMemcpy(probes_, probes.data(), probes.size() * sizeof(double), cudaMemcpyHostToDevice));
   }
+  // a blocking copy from pageable memory returns once staged: fence, since the evaluations run on a stream that
+  // does not wait for the legacy one
+  PETB_CUDA(cudaDeviceSynchronize());
 }
 
 Model::~Model() {
@@ -326,6 +329,7 @@ void exchange_rows(Stream& st, const PackedEdges& pk, const float* out, float* i
   if (!ex || !ex->edges) throw Error(3, "pet: an exchanged list without an edges() callback");
   if (ex->edges(ex->user, out, in, pk.n_live, width, static_cast<void*>(st.s)) != 0)
     throw Error(1, "pet: the exchange's edges() failed");
+  order_after_legacy_stream(st);
 }
 
 struct Scope {

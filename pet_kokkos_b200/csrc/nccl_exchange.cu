@@ -314,6 +314,7 @@ int pet_nccl_exchange_create(const char* id128, int rank, int world, int device,
       PETB_CUDA(cudaMalloc(&x->reduce_buf, (7 + 3 * size_t(n_total)) * sizeof(double)));
       PETB_CUDA(cudaMallocHost(&x->reduce_host, (7 + 3 * size_t(n_total)) * sizeof(double)));
     }
+    PETB_CUDA(cudaDeviceSynchronize());  // the tables above were copied on the legacy stream; they are read on the caller's
   });
 }
 

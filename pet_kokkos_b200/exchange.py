@@ -126,6 +126,7 @@ def _rt():
             hits = glob.glob(os.path.join(os.path.dirname(torch.__file__), "..", "nvidia", "cuda_runtime", "lib", "libcudart.so*"))
             _cudart = ctypes.CDLL(hits[0])
         _cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+        _cudart.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         _cudart.cudaStreamSynchronize.argtypes = [ctypes.c_void_p]
     return _cudart
 
@@ -139,9 +140,12 @@ def _d2h(ptr, n, dtype):
     return a
 
 
-def _h2d(ptr, a):
+def _h2d(ptr, a, stream):
+    """Host rows into the calculator's buffer, on the calculator's stream. A blocking cudaMemcpy from pageable memory
+    returns once the rows are staged, before they have landed, and it runs on the legacy stream, which the
+    calculator's non-blocking stream does not wait for: the kernels launched next could read the buffer too early."""
     if a.size:
-        rc = _rt().cudaMemcpy(ptr, a.ctypes.data, a.nbytes, 1)
+        rc = _rt().cudaMemcpyAsync(ptr, a.ctypes.data, a.nbytes, 1, stream) or _rt().cudaStreamSynchronize(stream)
         if rc:
             raise RuntimeError(f"cudaMemcpy H2D failed: {rc}")
 
@@ -192,7 +196,7 @@ class ThreadExchange:
                 m = self.src_rank == q
                 if m.any():
                     got[m] = self.hub.rows[q][self.src_row[m]]
-        _h2d(in_ptr, got)
+        _h2d(in_ptr, got, stream)
         self.hub.barrier.wait()
 
 

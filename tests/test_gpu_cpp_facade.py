@@ -53,7 +53,10 @@ struct ImageExchange : pet::Exchange {
       if (src < 0) throw std::runtime_error("a live edge's partner is not live");
       for (int c = 0; c < width; ++c) got[size_t(l) * width + c] = rows[size_t(src) * width + c];
     }
-    cudaMemcpy(in, got.data(), got.size() * sizeof(float), cudaMemcpyHostToDevice);
+    // on the calculator's stream: a blocking copy from pageable memory returns once staged, before the rows have
+    // landed, and the calculator's non-blocking stream would not wait for it
+    cudaMemcpyAsync(in, got.data(), got.size() * sizeof(float), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+    cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     ++calls;
   }
 };
