@@ -281,7 +281,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
-      mbar_init(split + s, 128);
+      mbar_init(split + s, X3 ? 192 : 128);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull + b, 1);
@@ -401,10 +401,11 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
         mbar_arrive(split + s);
       }
     }
-  } else if (X3 && warp >= kSplitWarp0) {
+  } else if (X3 && (warp >= kSplitWarp0 || warp == 2 || warp == 3)) {
     // lo = x - hi(x), written beside the stage's tiles at the same swizzled positions, so the same
-    // descriptors, offset by the size of the hi tiles, address them.
-    const int tid = threadIdx.x - kSplitWarp0 * 32;
+    // descriptors, offset by the size of the hi tiles, address them. Six warps: the four splitter warps and the two
+    // that have no other role (2 % on the 1728-atom benchmark over four).
+    const int tid = warp >= kSplitWarp0 ? threadIdx.x - kSplitWarp0 * 32 : 128 + threadIdx.x - 64;
     const int n16 = (p.b_lo_offset != 0 ? L::kA : L::kHi) / 16;  // 16-byte pieces to split: A's, and B's unless they came split
     int g = 0;
     bool ok = true;
@@ -415,7 +416,7 @@ __global__ void __launch_bounds__(Smem<BN, STAGES, MODE>::kThreads, 1)
         const float4* hi = reinterpret_cast<const float4*>(tiles + size_t(s) * L::kStage);
         float4* lo = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage + L::kHi);
 #pragma unroll 8
-        for (int e = tid; e < n16; e += 128) {
+        for (int e = tid; e < n16; e += 192) {
           const float4 x = hi[e];
           float4 y;
           y.x = tf32_lo(x.x), y.y = tf32_lo(x.y), y.z = tf32_lo(x.z), y.w = tf32_lo(x.w);
