@@ -977,14 +977,23 @@ bool fine_stages() {
 template <int EPI>
 void dispatch_tc(Stream& st, const GemmArgs& a, int mode) {
   const bool x3 = mode == GEMM_TF32X3, b16 = mode == GEMM_BF16;
-  // The widest tile that still gives every SM a tile: a GEMM over the atoms' rows (a few thousand) would
-  // otherwise run on a handful of CTAs with a long, latency-bound K loop each.
+  // The tile width that finishes first. A tile's time per step of K goes with the shared-memory wavefronts it needs
+  // (operand reads, fills, the splitter, its share of the epilogue), which a narrower tile needs fewer of per tile
+  // and more of per output column; the launch takes as many rounds as its fullest CTA has tiles. The token GEMMs
+  // (thousands of row tiles) come out at 256; a GEMM over the atoms' rows (14 row tiles at 1728 atoms) at whatever
+  // gives one round: 64 for 256 columns, 128 for 1024, 256 for 2048.
   const long long mt = cdiv(a.M, TBM);
   const int sms = state().sms;
-  int bn = 64;
-  if (a.N % 256 == 0 && mt * (a.N / 256) >= sms) bn = 256;
-  else if (a.N % 128 == 0 && mt * (a.N / 128) >= sms) bn = 128;
-  else if (a.N % 64 != 0) bn = a.N % 256 == 0 ? 256 : 128;  // ragged widths: a wide tile with a zero-filled edge
+  const int widths[3] = {256, 128, 64};
+  const int wavefronts[3] = {x3 ? 550 : 300, x3 ? 350 : 185, x3 ? 270 : 125};
+  int bn = 0;
+  long long best = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (a.N % widths[i] != 0) continue;
+    const long long tiles = mt * (a.N / widths[i]), rounds = (tiles + sms - 1) / sms;
+    if (bn == 0 || rounds * wavefronts[i] < best) bn = widths[i], best = rounds * wavefronts[i];
+  }
+  if (bn == 0) bn = 128;  // ragged widths: a wide tile with a zero-filled edge
   if (bn == 256) {
     if (x3 && a.b_lo_offset && pair_enabled() && cdiv(a.M, 2 * TBM) * (a.N / 256) >= sms / 2) {
       const char* e = std::getenv("PET_GEMM_PAIR");
