@@ -72,49 +72,77 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML queries from a thread of this process
+    (the same counters `nvidia-smi --query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.*` prints), every 100 ms.
+    An `nvidia-smi -lms` child process was what this used first; on a freshly started box each of its polls could
+    hold the GPU for tens of milliseconds (every other 20 ms step took 70), which a handful of NVML calls do not.
+    Reading only: nothing is set."""
+    REASONS = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
+               ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"), ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap"))
 
     def __init__(self, index):
-        self.index, self.proc, self.lines, self.first = index, None, [], 0
+        self.index, self.samples, self.first, self.thread, self.nvml, self.handle = index, [], 0, None, None, None
+        self.stop_flag = threading.Event()
 
     def mark(self):
-        """The timed region starts here: samples taken before (while nvidia-smi was starting up, during warm-up) are
-        not counted. The sampler is started before the warm-up on purpose: nvidia-smi's own start-up can hold the
-        driver for a tenth of a second or two, which inside a timed region of a few tenths doubled a step's time."""
-        self.first = len(self.lines)
+        """The timed region starts here: samples taken before it (during warm-up) are not counted."""
+        self.first = len(self.samples)
+
+    def _open(self):
+        import pynvml
+        pynvml.nvmlInit()
+        handle = None
+        try:  # the CUDA ordinal is not NVML's index when CUDA_VISIBLE_DEVICES reorders or hides devices: go by UUID
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+        except Exception:
+            handle = None
+        if handle is None:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        return pynvml, handle
+
+    def _loop(self):
+        nv, h = self.nvml, self.handle
+        while not self.stop_flag.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.samples.append((float(sm), float(mx), int(mask)))
+            except Exception:
+                pass
+            self.stop_flag.wait(0.1)
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
-            self.t.start()
-        except OSError:
-            self.proc = None
+            self.nvml, self.handle = self._open()
+        except Exception:
+            self.nvml = None
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+
+    def wait_started(self, limit=5.0):
+        """Until the first sample has come, or `limit` seconds."""
+        t0 = time.perf_counter()
+        while self.thread and not self.samples and time.perf_counter() - t0 < limit:
+            time.sleep(0.02)
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        self.t.join(timeout=2)
-        sm, mx, reasons = [], [], set()
-        for ln in self.lines[self.first:]:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])), mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if v.lower().startswith("active"):
+        if not self.thread:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML unavailable"]}
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        taken = self.samples[self.first:]
+        reasons = set()
+        for _, _, mask in taken:
+            for name, const in self.REASONS:
+                if mask & getattr(self.nvml, const):
                     reasons.add(name)
+        sm, mx = [s[0] for s in taken], [s[1] for s in taken]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "NVML, every 100 ms"}
 
 
 _RESULT_FD = None
@@ -483,7 +511,7 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.5)  # let nvidia-smi finish starting up outside anything that is timed
+        sampler.wait_started()
     calc.stage(systems)
     for _ in range(args.warmup):
         calc.compute_staged(True)
@@ -612,7 +640,8 @@ def run_ours(args):
             cpu = {"value": na / float(np.mean(t)), "unit": UNIT, "cores": threads, "kind": kind, "sample": what}
         line = ({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": step_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": step_ms / args.steps,
+            "device_ms_each_step_rank0": [round(float(x), 3) for x in dev_ms], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": DTYPE_OF[args.gemm],
             "data": "synthetic",
             "config": {"workload": args.workload, "model": f"random-init pet-mad-{shape}-like", "atoms_per_gpu": n_atoms,

@@ -799,8 +799,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
       const uint32_t acc = tmem + uint32_t(b * BN) + (uint32_t(q * 32) << 16);
       epilogue_tile<EPI, BN>(p, acc, pad, m0, n0, q, half, lane, [&] { mbar_arrive_cluster(peer_smem(tempty + b, 0)); });
     }
-  } else if (warp >= kSplitWarp0) {
-    const int tid = threadIdx.x - kSplitWarp0 * 32;
+  } else if (warp >= kSplitWarp0 || warp == 2 || warp == 3) {  // six warps, as in k_gemm_tc
+    const int tid = warp >= kSplitWarp0 ? threadIdx.x - kSplitWarp0 * 32 : 128 + threadIdx.x - 64;
     constexpr int n16 = L::kA / 16;  // A's 16-byte pieces; B's lo half arrives split
     const uint32_t split0 = peer_smem(split, 0);  // the leader's barriers
     int g = 0;
@@ -812,7 +812,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
         const float4* hi = reinterpret_cast<const float4*>(tiles + size_t(s) * L::kStage);
         float4* lo = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage + L::kHi);
 #pragma unroll 8
-        for (int e = tid; e < n16; e += 128) {
+        for (int e = tid; e < n16; e += 192) {
           const float4 x = hi[e];
           float4 y;
           y.x = tf32_lo(x.x), y.y = tf32_lo(x.y), y.z = tf32_lo(x.z), y.w = tf32_lo(x.w);
@@ -821,7 +821,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // one arrival per CTA and stage: 128 arrivals from the odd CTA, each a transaction across the cluster, cost the
         // leader 1.2 k clocks of waiting per stage
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 192;" ::: "memory");
         if (tid == 0) mbar_arrive_cluster(split0 + 8u * uint32_t(s));
       }
     }
@@ -959,7 +959,24 @@ void launch_tc_pair(Stream& st, const GemmArgs& a) {
   const CUtensorMap mb = make_map(a.B, a.N, a.K, a.ldb, L::BN / 2, L::BK);
   const CUtensorMap mblo = make_map(a.B + a.b_lo_offset, a.N, a.K, a.ldb, L::BN / 2, L::BK);
   const long long tiles = (long long) cdiv(a.M, 2 * TBM) * cdiv(a.N, L::BN);
-  const long long pairs = std::min<long long>(tiles, state().sms / 2);
+  // as many pairs as the device can hold at once (a pair needs two SMs of one GPC: fewer than half the SMs may fit),
+  // or the kernel's last pairs would start when the first ones end
+  static PerDevice<int> resident;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int fit = resident.get(dev, [&](int& out) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(state().sms / 2 * 2)), cfg.blockDim = dim3(L::kThreads), cfg.dynamicSmemBytes = L::kTotal;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) n = state().sms / 2;
+    if (std::getenv("PET_GEMM_PAIR_VERBOSE")) std::fprintf(stderr, "pair kernel: %d clusters fit on %d SMs\n", n, state().sms);
+    out = n;
+  });
+  const long long pairs = std::min<long long>(tiles, std::min(fit, state().sms / 2));
   kernel<<<unsigned(2 * pairs), L::kThreads, L::kTotal, st.s>>>(ma, mb, mblo, a, state().err);
   PETB_LAUNCH_CHECK(st);
 }
