@@ -74,8 +74,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clocks and throttle reasons while the timed region runs: NVML queries from a thread of this process
     (the same counters `nvidia-smi --query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.*` prints), every 100 ms.
-    An `nvidia-smi -lms` child process was what this used first; on a freshly started box each of its polls could
-    hold the GPU for tens of milliseconds (every other 20 ms step took 70), which a handful of NVML calls do not.
+    An `nvidia-smi -lms` child process was what this used first; three NVML calls from a thread are lighter.
     Reading only: nothing is set."""
     REASONS = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
                ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"), ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap"))
