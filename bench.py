@@ -640,7 +640,8 @@ def run_ours(args):
         line = ({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": step_ms / args.steps,
-            "device_ms_each_step_rank0": [round(float(x), 3) for x in dev_ms], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "device_ms_each_step_rank0": [round(float(x), 3) for x in dev_ms],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": DTYPE_OF[args.gemm],
             "data": "synthetic",
             "config": {"workload": args.workload, "model": f"random-init pet-mad-{shape}-like", "atoms_per_gpu": n_atoms,

@@ -460,12 +460,31 @@ RunOptions Engine::run_options() const {
   o.budget = memory_budget;
   if (o.budget == 0 && recompute == RECOMPUTE_AUTO) {
     size_t free_b = 0, total_b = 0;
-    if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+    if (device_memory(&free_b, &total_b)) {
       const double pool = double(save_arena.capacity() + tmp_arena.capacity());
       o.budget = size_t(std::min(double(free_b) + pool, double(total_b)) * 0.9);
     }
   }
   return o;
+}
+
+// What the device has free, asked of the driver only when this engine's pools have changed size since the last
+// answer. cudaMemGetInfo goes into the kernel-mode driver, where it queues behind whoever else is talking to it
+// (a monitoring agent's NVML polls, nvidia-smi): asked at every evaluation it held one 20 ms step in ten or so up for
+// 50-100 ms on a shared box, the GPU idle meanwhile. Between two evaluations of the same shapes nothing this engine
+// does changes the answer.
+bool Engine::device_memory(size_t* free_b, size_t* total_b) const {
+  const size_t pools = save_arena.capacity() + tmp_arena.capacity() + nbr_arena.capacity() + cache_arena.capacity() +
+                       cache_spare.capacity() + session_arena.capacity() + geom_arena.capacity();
+  if (!mem_known || pools != mem_pools) {
+    if (cudaMemGetInfo(&mem_free, &mem_total) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    mem_known = true, mem_pools = pools;
+  }
+  *free_b = mem_free, *total_b = mem_total;
+  return true;
 }
 
 void Engine::run_model(const PackedEdges& pk, bool forces) {
@@ -693,7 +712,7 @@ std::vector<std::pair<int, int>> Engine::memory_runs(const pet_system* systems, 
   double budget = double(memory_budget);
   if (memory_budget == 0) {
     size_t free_b = 0, total_b = 0;
-    if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) free_b = total_b = size_t(64) << 30;
+    if (!device_memory(&free_b, &total_b)) free_b = total_b = size_t(64) << 30;
     budget = std::min(double(free_b) + pool, double(total_b)) * 0.9;
   }
   const double cap = budget / per_slot;

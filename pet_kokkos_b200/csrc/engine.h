@@ -98,6 +98,9 @@ struct Engine {
   int recompute = RECOMPUTE_AUTO;  // Options::recompute / PET_RECOMPUTE: how much of the forward the backward keeps
   int tier_floor = RECOMPUTE_NEVER;  // raised when an evaluation of one structure ran out of memory under Auto
   RunOptions run_options() const;
+  bool device_memory(size_t* free_b, size_t* total_b) const;  // cached while the pools keep their size
+  mutable bool mem_known = false;
+  mutable size_t mem_free = 0, mem_total = 0, mem_pools = 0;
   double peak_slots = 0.0;       // the most atoms x (neighbours + 1) one evaluation has held: samples bytes per slot
   long long batch_splits = 0;    // batches evaluated as more than one piece
   long long oom_recoveries = 0;  // evaluations retried after the device ran out of memory
