@@ -73,7 +73,7 @@ def measured_peaks():
 
 class ClockSampler:
     """Samples SM clocks and throttle reasons while the timed region runs: NVML queries from a thread of this process
-    (the same counters `nvidia-smi --query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.*` prints), every 100 ms.
+    (the same counters `nvidia-smi --query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.*` prints), every 50 ms.
     An `nvidia-smi -lms` child process was what this used first; three NVML calls from a thread are lighter.
     Reading only: nothing is set."""
     REASONS = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
@@ -111,7 +111,7 @@ class ClockSampler:
                 self.samples.append((float(sm), float(mx), int(mask)))
             except Exception:
                 pass
-            self.stop_flag.wait(0.1)
+            self.stop_flag.wait(0.05)
 
     def start(self):
         try:
@@ -141,7 +141,7 @@ class ClockSampler:
                     reasons.add(name)
         sm, mx = [s[0] for s in taken], [s[1] for s in taken]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm), "source": "NVML, every 100 ms"}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "NVML, every 50 ms"}
 
 
 _RESULT_FD = None

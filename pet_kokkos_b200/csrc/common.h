@@ -226,17 +226,16 @@ struct Stream {
   cudaStream_t s = nullptr;
   long long launches = 0;
   Profiler* prof = nullptr;
+  cudaEvent_t legacy_fence = nullptr;  // made at first use by order_after_legacy_stream, destroyed with the stream's owner
 };
 
 // After a caller's callback returns: what it put on the legacy default stream (a blocking cudaMemcpy from pageable
 // memory returns once the bytes are staged, before they have landed) is ordered before this stream's next work.
 // The evaluators' streams are non-blocking and would not wait for it otherwise.
 inline void order_after_legacy_stream(Stream& st) {
-  cudaEvent_t ev;
-  PETB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-  PETB_CUDA(cudaEventRecord(ev, cudaStreamLegacy));
-  PETB_CUDA(cudaStreamWaitEvent(st.s, ev, 0));
-  PETB_CUDA(cudaEventDestroy(ev));
+  if (!st.legacy_fence) PETB_CUDA(cudaEventCreateWithFlags(&st.legacy_fence, cudaEventDisableTiming));
+  PETB_CUDA(cudaEventRecord(st.legacy_fence, cudaStreamLegacy));
+  PETB_CUDA(cudaStreamWaitEvent(st.s, st.legacy_fence, 0));
 }
 
 // Brackets the launches made in its lifetime; `flops` and `bytes` are the algorithmic work

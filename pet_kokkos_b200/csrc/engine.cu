@@ -209,6 +209,7 @@ Engine::~Engine() {
   if (host_stage) cudaFreeHost(host_stage);
   if (ev0) cudaEventDestroy(ev0);
   if (ev1) cudaEventDestroy(ev1);
+  if (st.legacy_fence) cudaEventDestroy(st.legacy_fence);
   if (st.s) cudaStreamDestroy(st.s);
 }
 
