@@ -129,6 +129,17 @@ __device__ __forceinline__ void load_a(Frag (*f)[4], const float* x, int r0, int
   }
 }
 
+// One 8-wide step's A fragment, loaded where it is used: at head_dim 64 the fragments of all eight steps of two
+// operands, split, would be 128 registers by themselves.
+template <int HD, bool X3>
+__device__ __forceinline__ void load_a_step(Frag* f, const float* x, int r0, int g, int t, int ks) {
+  constexpr int P = HD + 4;
+  f[0] = split<X3>(x[(r0 + g) * P + 8 * ks + t]);
+  f[1] = split<X3>(x[(r0 + g + 8) * P + 8 * ks + t]);
+  f[2] = split<X3>(x[(r0 + g) * P + 8 * ks + t + 4]);
+  f[3] = split<X3>(x[(r0 + g + 8) * P + 8 * ks + t + 4]);
+}
+
 template <int HD, int MAXKB, bool X3>
 __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k_attn_fwd_mma(AttnArgs p) {
   constexpr int P = HD + 4, KS = HD / 8, R = 8 * MAXKB;  // R: staged token rows, the kernel's most (zero past the atom's)
@@ -237,6 +248,10 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
 template <int HD, int MAXT, bool X3>
 __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(AttnArgs p) {
   constexpr int P = HD + 4, KS = HD / 8;
+  // The A fragments stay in registers over the whole key loop up to head_dim 32. At 64 they would be 128 registers
+  // (two operands, eight steps, four values, two parts) and the compiler spilled a kilobyte per thread: there each
+  // step's fragment is loaded and split where it is used (22.3 against 32.8 ms on a 1000-atom cell of the l shape).
+  constexpr bool KEEP = HD <= 32;
   extern __shared__ __align__(16) float smem[];
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H, D = p.H * HD;
   const int e0 = p.off[n], cnt = p.off[n + 1] - e0 + 1;
@@ -284,20 +299,27 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
   const int i0 = r0 + g, i1 = r0 + g + 8;  // this lane's two rows (queries or keys)
   const size_t g0 = i0 == 0 ? size_t(n) : size_t(p.N) + e0 + i0 - 1, g1 = size_t(p.N) + e0 + i1 - 1;
   if (!keys) {
-    Frag qf[KS][4], gf[KS][4];
-    load_a<HD, X3>(qf, sq, r0, g, t);
-    load_a<HD, X3>(gf, sg, r0, g, t);
+    Frag qf[KEEP ? KS : 1][4], gf[KEEP ? KS : 1][4];
+    if (KEEP) {
+      load_a<HD, X3>(qf, sq, r0, g, t);
+      load_a<HD, X3>(gf, sg, r0, g, t);
+    }
     const float m0 = sm[i0], m1 = sm[i1], il0 = sl[i0], il1 = sl[i1], dq0 = sd[i0], dq1 = sd[i1];
     float dq[KS][4];
 #pragma unroll
     for (int db = 0; db < KS; ++db) dq[db][0] = dq[db][1] = dq[db][2] = dq[db][3] = 0.f;
     for (int kb = 0; kb < nkb; ++kb) {
+      if (!KEEP) asm volatile("" ::: "memory");  // or the fragment loads are hoisted out of the loop and live across it again
       float cs[4] = {0.f, 0.f, 0.f, 0.f}, cp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
         const Frag k0 = split<X3>(sk[(8 * kb + g) * P + 8 * ks + t]), k1 = split<X3>(sk[(8 * kb + g) * P + 8 * ks + t + 4]);
         const Frag v0 = split<X3>(sv[(8 * kb + g) * P + 8 * ks + t]), v1 = split<X3>(sv[(8 * kb + g) * P + 8 * ks + t + 4]);
-        mma3_pair<X3>(cs, qf[ks], k0, k1, cp, gf[ks], v0, v1);
+        if (!KEEP) {
+          load_a_step<HD, X3>(qf[0], sq, r0, g, t, ks);
+          load_a_step<HD, X3>(gf[0], sg, r0, g, t, ks);
+        }
+        mma3_pair<X3>(cs, qf[KEEP ? ks : 0], k0, k1, cp, gf[KEEP ? ks : 0], v0, v1);
       }
       const int key = 8 * kb + 2 * t;
       const float lc0 = slc[key], lc1 = slc[key + 1];
@@ -324,9 +346,11 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
   } else {
     // transposed: rows are keys. S^T = K Q^T and dP^T = V dO^T per block of 8 queries; the accumulator
     // fragment of dS^T (and P^T) is the A operand of dK = dS^T Q (and dV = P^T dO).
-    Frag kf[KS][4], vf[KS][4];
-    load_a<HD, X3>(kf, sk, r0, g, t);
-    load_a<HD, X3>(vf, sv, r0, g, t);
+    Frag kf[KEEP ? KS : 1][4], vf[KEEP ? KS : 1][4];
+    if (KEEP) {
+      load_a<HD, X3>(kf, sk, r0, g, t);
+      load_a<HD, X3>(vf, sv, r0, g, t);
+    }
     const float lc0 = slc[i0], lc1 = slc[i1];
     const bool on0 = !is_off(lc0), on1 = !is_off(lc1);
     float dk[KS][4], dv[KS][4], cf0 = 0.f, cf1 = 0.f;
@@ -334,12 +358,17 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
     for (int db = 0; db < KS; ++db)
       dk[db][0] = dk[db][1] = dk[db][2] = dk[db][3] = dv[db][0] = dv[db][1] = dv[db][2] = dv[db][3] = 0.f;
     for (int qb = 0; qb < nkb; ++qb) {
+      if (!KEEP) asm volatile("" ::: "memory");
       float cs[4] = {0.f, 0.f, 0.f, 0.f}, cp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
         const Frag q0 = split<X3>(sq[(8 * qb + g) * P + 8 * ks + t]), q1 = split<X3>(sq[(8 * qb + g) * P + 8 * ks + t + 4]);
         const Frag d0 = split<X3>(sg[(8 * qb + g) * P + 8 * ks + t]), d1 = split<X3>(sg[(8 * qb + g) * P + 8 * ks + t + 4]);
-        mma3_pair<X3>(cs, kf[ks], q0, q1, cp, vf[ks], d0, d1);
+        if (!KEEP) {
+          load_a_step<HD, X3>(kf[0], sk, r0, g, t, ks);
+          load_a_step<HD, X3>(vf[0], sv, r0, g, t, ks);
+        }
+        mma3_pair<X3>(cs, kf[KEEP ? ks : 0], q0, q1, cp, vf[KEEP ? ks : 0], d0, d1);
       }
       const int qa = 8 * qb + 2 * t, qc = qa + 1;  // this lane's two queries of the block
       const float ma = sm[qa], mc = sm[qc], ila = sl[qa], ilc = sl[qc], da = sd[qa], dc = sd[qc];
