@@ -300,6 +300,10 @@ long long pet_batch_splits(const pet_calc* c);
  * device allocation of the scratch pools from now (0 = the next) reports out of memory once; k < 0 disarms. */
 long long pet_oom_recoveries(const pet_calc* c);
 void pet_debug_fail_alloc(long k);
+/* Times this calculator has asked the driver how much device memory is free (for the recompute tier and the batch
+ * pieces it chooses by itself). The call goes into the kernel-mode driver and waits behind its other clients, so
+ * the answer is kept for as long as the calculator's pools keep their size: a steady loop stops asking. */
+long long pet_driver_memory_queries(const pet_calc* c);
 /* Neighbour searches run for staged batches under Options::cache_neighbors, and the evaluations the cached
  * pairs served instead (the reference's NefCache, include/pet/device_geometry.hpp:198-228). */
 long long pet_neighbor_searches(const pet_calc* c);

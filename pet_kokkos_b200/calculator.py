@@ -150,6 +150,7 @@ SIGNATURES = {
     "pet_graph_replays": (C.c_longlong, [C.c_void_p]),
     "pet_batch_splits": (C.c_longlong, [C.c_void_p]),
     "pet_oom_recoveries": (C.c_longlong, [C.c_void_p]),
+    "pet_driver_memory_queries": (C.c_longlong, [C.c_void_p]),
     "pet_debug_fail_alloc": (None, [C.c_long]),
     "pet_neighbor_searches": (C.c_longlong, [C.c_void_p]),
     "pet_neighbor_reuses": (C.c_longlong, [C.c_void_p]),
@@ -358,6 +359,11 @@ class Calculator:
     def oom_recoveries(self):
         """Evaluations retried after the device ran out of memory (pools released, the batch cut smaller)."""
         return self._lib.pet_oom_recoveries(self._h)
+
+    @property
+    def driver_memory_queries(self):
+        """Times the calculator asked the driver for the free device memory (kept while its pools keep their size)."""
+        return self._lib.pet_driver_memory_queries(self._h)
 
     def fail_alloc(self, k):
         """Test hook: the k-th device allocation of the scratch pools from now reports out of memory, once."""

@@ -210,6 +210,7 @@ int pet_recommended_batch_atoms(const pet_calc* c) {
 long long pet_kernel_launches(const pet_calc* c) { return c && c->e ? c->e->st.launches : 0; }
 long long pet_graph_replays(const pet_calc* c) { return c && c->e ? c->e->graph_replays : 0; }
 long long pet_oom_recoveries(const pet_calc* c) { return c && c->e ? c->e->oom_recoveries : 0; }
+long long pet_driver_memory_queries(const pet_calc* c) { return c && c->e ? c->e->mem_queries : 0; }
 void pet_debug_fail_alloc(long k) { petb::g_fail_alloc_in = k; }
 long long pet_batch_splits(const pet_calc* c) { return c && c->e ? c->e->batch_splits : 0; }
 long long pet_neighbor_searches(const pet_calc* c) { return c && c->e ? c->e->verlet.searches : 0; }

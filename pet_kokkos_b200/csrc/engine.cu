@@ -478,6 +478,7 @@ bool Engine::device_memory(size_t* free_b, size_t* total_b) const {
   const size_t pools = save_arena.capacity() + tmp_arena.capacity() + nbr_arena.capacity() + cache_arena.capacity() +
                        cache_spare.capacity() + session_arena.capacity() + geom_arena.capacity();
   if (!mem_known || pools != mem_pools) {
+    ++mem_queries;
     if (cudaMemGetInfo(&mem_free, &mem_total) != cudaSuccess) {
       cudaGetLastError();
       return false;

@@ -101,6 +101,7 @@ struct Engine {
   bool device_memory(size_t* free_b, size_t* total_b) const;  // cached while the pools keep their size
   mutable bool mem_known = false;
   mutable size_t mem_free = 0, mem_total = 0, mem_pools = 0;
+  mutable long long mem_queries = 0;
   double peak_slots = 0.0;       // the most atoms x (neighbours + 1) one evaluation has held: samples bytes per slot
   long long batch_splits = 0;    // batches evaluated as more than one piece
   long long oom_recoveries = 0;  // evaluations retried after the device ran out of memory

@@ -275,3 +275,25 @@ def test_two_devices_in_one_process(models, lib_path):
             assert np.array_equal(getattr(ra, k), getattr(rb, k)), (gemm, k)
             assert np.array_equal(getattr(ra, k), getattr(ra2, k)) and np.array_equal(getattr(rb, k), getattr(rb2, k))
         a.close(), b.close()
+
+
+def test_a_steady_loop_stops_asking_the_driver_for_free_memory(lib_path, models):
+    """Under Recompute::Auto every evaluation needs a memory budget. Asking the driver for it each time (cudaMemGetInfo,
+    a call into the kernel-mode driver that waits behind its other clients) held one step in ten up for 50-100 ms on a
+    shared box. The answer is kept while the calculator's pools keep their size: the same shapes again ask nothing,
+    after a larger structure has grown the pools the next evaluation asks again."""
+    from pet_kokkos_b200 import Calculator
+    c = Calculator(*models("xs", "feedforward", "n002", 0))
+    small, large = st.diamond(2, jitter=0.05, seed=0), st.diamond(3, jitter=0.05, seed=0)
+    ref = c.compute(small)
+    c.compute(small)
+    asked = c.driver_memory_queries
+    assert asked >= 1
+    for _ in range(5):
+        r = c.compute(small)
+    assert c.driver_memory_queries == asked, "same shapes, same pools: nothing to ask"
+    assert np.array_equal(r.forces, ref.forces) and r.energy[0] == ref.energy[0]
+    c.compute(large)  # the pools grow during this evaluation ...
+    c.compute(large)  # ... so the next one finds them changed and asks again
+    assert c.driver_memory_queries > asked, "the pools grew: the cached answer is stale"
+    c.close()
