@@ -618,8 +618,8 @@ __global__ void __launch_bounds__(512, 1)
 //
 // Who signals whom (every barrier exists in both CTAs at the same offset; "leader" is the even CTA):
 //   full[s]    own CTA's TMA loads landed (each CTA loads with the plain, CTA-local form; no multicast anywhere)
-//   split[s]   LEADER's: 2 arrivals, one thread of each CTA's splitter warps (the odd CTA's arrives remotely) once the
-//              four warps have written their lo tile and met at a named barrier: both CTAs' operands are then complete
+//   split[s]   LEADER's: 12 arrivals, one per splitter warp of both CTAs (the odd CTA's arrive remotely) once the warp
+//              has written its share of the lo tile: both CTAs' operands are then complete
 //   empty[s]   own CTA's: the leader's issuer commits the stage's MMAs to its own and to the odd CTA's barrier
 //   tfull[b]   own CTA's: the leader commits the finished accumulator to both
 //   tempty[b]  LEADER's: 16 arrivals, the epilogue warps of both CTAs once they have read the accumulator
@@ -716,7 +716,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
-      mbar_init(split + s, 2);
+      mbar_init(split + s, 12);  // six splitter warps in each CTA
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull + b, 1);
@@ -808,7 +808,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
     for (int t = pair; ok && t < n_tiles; t += n_pairs) {
       for (int kb = 0; kb < nkb; ++kb, ++g) {
         const int s = g % STAGES;
-        if (!(ok = mbar_wait(full + s, (g / STAGES) & 1, abort_flag))) break;
+        // a warp goes on or gives up as one, and arrives once: no barrier among the splitter warps that a warp
+        // which gave up could leave the others waiting at
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(full + s, (g / STAGES) & 1, abort_flag)))) break;
         const float4* hi = reinterpret_cast<const float4*>(tiles + size_t(s) * L::kStage);
         float4* lo = reinterpret_cast<float4*>(tiles + size_t(s) * L::kStage + L::kHi);
 #pragma unroll 8
@@ -819,10 +821,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
           lo[e] = y;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // one arrival per CTA and stage: 128 arrivals from the odd CTA, each a transaction across the cluster, cost the
-        // leader 1.2 k clocks of waiting per stage
-        asm volatile("bar.sync 1, 192;" ::: "memory");
-        if (tid == 0) mbar_arrive_cluster(split0 + 8u * uint32_t(s));
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(split0 + 8u * uint32_t(s));
       }
     }
   }
