@@ -77,3 +77,22 @@ def test_the_three_split_product_kernels_give_the_same_bits(lib_path, models, mo
         assert np.array_equal(staged, ring), (m, n, k, np.abs(staged - ring).max())
         assert np.array_equal(staged, pair), (m, n, k, np.abs(staged - pair).max())
     c.close()
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32", "bf16"])
+def test_token_row_gemm_of_the_benchmark(calc, mode):
+    """The most frequent GEMM of the 1728-atom benchmark at its full size (atoms + kept edges = 122 138 rows, d_pet 256
+    in and out), in every tensor-core mode, against the fp64 product. profiles/k_gemm_tc_122k_256_256.md is an ncu capture
+    of this test."""
+    m, n, k = 122138, 256, 256
+    rng = np.random.default_rng(0)
+    A = rng.normal(size=(m, k)).astype(np.float32)
+    W = rng.normal(size=(n, k)).astype(np.float32)
+    C = calc.gemm(A, W, mode)
+    C = calc.gemm(A, W, mode)  # the second launch is the one a profile reads: the first one loads the kernel
+    ref = A[:4096].astype(np.float64) @ W.T.astype(np.float64)
+    err = np.abs(C[:4096] - ref).max() / np.abs(ref).max()
+    tail = A[-300:].astype(np.float64) @ W.T.astype(np.float64)
+    err = max(err, np.abs(C[-300:] - tail).max() / np.abs(tail).max())
+    band = {"3xtf32": 2e-6 + 0.5 * (3 * k / 8) * 2.0 ** -24, "tf32": 2e-3, "bf16": 2e-2}[mode]
+    assert err <= band, (mode, err)
