@@ -42,6 +42,34 @@ def test_muting_the_exchange_changes_the_answer(lib_path, models):
         c.close()
 
 
+def test_a_callback_that_copies_on_the_legacy_stream_is_waited_for(lib_path, models):
+    """An engine's `edges` callback may fill `in` with a blocking cudaMemcpy from pageable memory. That call returns once
+    the rows are staged, not once they have landed, and runs on the legacy stream, which the calculator's non-blocking
+    stream does not wait for by itself: one evaluation in twelve came out 2 % wrong before the library ordered its
+    stream after the legacy stream when a callback returns. Thirty evaluations through such a callback must all give
+    the bits of the exchange that copies on the calculator's own stream."""
+    import ctypes
+    from pet_kokkos_b200 import Calculator
+
+    class LegacyStreamExchange(exchange.ThreadExchange):
+        def edges(self, out_ptr, in_ptr, n_live, width, stream):
+            rt = exchange._rt()
+            rt.cudaStreamSynchronize(stream)
+            rows = exchange._d2h(out_ptr, n_live * width, np.float32).reshape(n_live, width)
+            got = np.ascontiguousarray(rows[self.src_row])  # one rank: every partner row is this rank's own
+            assert rt.cudaMemcpy(ctypes.c_void_p(in_ptr), got.ctypes.data, got.nbytes, 1) == 0  # blocking, pageable, legacy stream
+
+    c = Calculator(*models("tiny", "feedforward", "scaled", 5))
+    s = st.diamond(3, jitter=0.05, seed=2)
+    fields, owner, _, remote = exchange.exchange_domain(s, 0, 1, c.cutoff)
+    route = exchange.route([(fields, owner, None, remote)])
+    want = c.compute_edges(exchange.view_of(fields, exchange.ThreadExchange(exchange.ThreadHub(route), 0)), True, False)
+    for _ in range(30):
+        got = c.compute_edges(exchange.view_of(fields, LegacyStreamExchange(exchange.ThreadHub(route), 0)), True, False)
+        assert got.energy[0] == want.energy[0] and np.array_equal(got.forces, want.forces)
+    c.close()
+
+
 @pytest.mark.parametrize("featurizer", ["feedforward", "residual"])
 def test_native_exchange_on_one_rank_reproduces_the_periodic_cell(lib_path, models, featurizer):
     """The library's own exchange (csrc/nccl_exchange.cu) with a single rank: every ghost is then an image of one of
