@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(32 * ((MAXKB + 1) / 2), MAXKB <= 10 ? 4 : 1) k
   extern __shared__ __align__(16) float smem[];
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H, D = p.H * HD;
   const int e0 = p.off[n], cnt = p.off[n + 1] - e0 + 1;
-  const int S16 = round16(cnt), nkb = S16 / 8;
+  // key blocks of 8 that hold a token at all: a block past them is zero rows with their cutoff off, and adds nothing
+  const int S16 = round16(cnt), nkb = (cnt + 7) / 8;
   float* sq = smem;
   float* sk = sq + R * P;
   float* sv = sk + R * P;
@@ -255,7 +256,9 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 320 ? 2 : 1) k_attn_bwd_mma(Attn
   extern __shared__ __align__(16) float smem[];
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H, D = p.H * HD;
   const int e0 = p.off[n], cnt = p.off[n + 1] - e0 + 1;
-  const int S16 = round16(cnt), nkb = S16 / 8, SM = round16(p.S);
+  // nkb: blocks of 8 keys (or, on the key side, of 8 queries) that hold a token at all; the rows past them are zero
+  // with zero weight, so leaving their block out changes no bit
+  const int S16 = round16(cnt), nkb = (cnt + 7) / 8, SM = round16(p.S);
   float* sq = smem;
   float* sk = sq + SM * P;
   float* sv = sk + SM * P;
